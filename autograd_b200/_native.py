@@ -1,0 +1,95 @@
+"""ctypes binding of the C ABI declared in include/autograd_b200.h.
+
+There is no fallback: if the shared library is missing or does not load, importing this
+module raises, and every non-zero status code becomes a `RuntimeError` carrying the
+library's own message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libautograd_b200.so")
+
+AG_OK, AG_ERR_INVALID, AG_ERR_CUDA, AG_ERR_SCRATCH, AG_ERR_DEVICE = range(5)
+AG_F32, AG_BF16 = 0, 1
+AG_STATUS_BAD_INDEX, AG_STATUS_WAIT_EXPIRED, AG_STATUS_STAGE_FALLBACK = 1, 2, 4
+AG_CE_FP32, AG_CE_3XTF32, AG_CE_BF16 = 0, 1, 2
+AG_CE_MEAN_ALL_ROWS, AG_CE_MEAN_VALID = 0, 1
+AG_CE_IGNORE_MASKED, AG_CE_IGNORE_COMPAT_UNMASKED = 0, 1
+
+
+class FlceDesc(C.Structure):
+    _fields_ = [("N", C.c_int64), ("C", C.c_int32), ("V", C.c_int32), ("vocab_chunk", C.c_int32),
+                ("precision", C.c_int32), ("reduction", C.c_int32), ("ignore_mode", C.c_int32)]
+
+
+_ctx = C.c_void_p
+_ptr = C.c_void_p
+_i64 = C.c_int64
+_int = C.c_int
+_f32 = C.c_float
+_f64 = C.c_double
+_sz = C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/autograd_b200.h one to one
+SIGNATURES = {
+    "ag_ctx_create": (_int, [_int, _ptr, C.POINTER(_ctx)]),
+    "ag_ctx_destroy": (_int, [_ctx]),
+    "ag_set_stream": (_int, [_ctx, _ptr]),
+    "ag_last_error": (C.c_char_p, [_ctx]),
+    "ag_device_info": (_int, [_ctx, C.POINTER(_int), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_int), C.POINTER(_int)]),
+    "ag_alloc": (_int, [_ctx, _sz, C.POINTER(_ptr)]),
+    "ag_free": (_int, [_ctx, _ptr]),
+    "ag_copy_h2d": (_int, [_ctx, _ptr, _ptr, _sz]),
+    "ag_copy_d2h": (_int, [_ctx, _ptr, _ptr, _sz]),
+    "ag_synchronize": (_int, [_ctx]),
+    "ag_status": (_int, [_ctx, C.POINTER(_int)]),
+    "ag_launch_count": (_i64, [_ctx]),
+    "ag_pass_begin_profiled": (_int, [_ctx]),
+    "ag_pass_end_profiled": (_int, [_ctx, C.POINTER(_f32)]),
+    "ag_fill_f32": (_int, [_ctx, _ptr, _f32, _i64]),
+    "ag_fill_pattern": (_int, [_ctx, _ptr, C.c_uint32, _int, _i64]),
+    "ag_add_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _i64]),
+    "ag_add_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _i64]),
+    "ag_add_layernorm_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _int, _f32]),
+    "ag_norm_partials_bytes": (_sz, [_ctx, _int]),
+    "ag_layernorm_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _i64, _int, _f32]),
+    "ag_rmsnorm_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _i64, _int, _f32, _int]),
+    "ag_rmsnorm_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _i64, _int, _f32, _int]),
+    "ag_gelu_forward": (_int, [_ctx, _ptr, _ptr, _i64]),
+    "ag_gelu_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _i64]),
+    "ag_swiglu_forward": (_int, [_ctx, _ptr, _ptr, _i64, _int, _int]),
+    "ag_swiglu_backward": (_int, [_ctx, _ptr, _ptr, _i64, _int, _int]),
+    "ag_rope_qk": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _int, _int, _int, _int, _int, _i64, _i64, _int, _int]),
+    "ag_gather_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _i64, _int, _int]),
+    "ag_scatter_add_scratch_bytes": (_sz, [_i64, _int, _int]),
+    "ag_gather_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _sz, _i64, _int, _int]),
+    "ag_flce_scratch_bytes": (_sz, [C.POINTER(FlceDesc)]),
+    "ag_flce_forward": (_int, [_ctx, C.POINTER(FlceDesc), _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz]),
+    "ag_flce_backward": (_int, [_ctx, C.POINTER(FlceDesc), _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz]),
+    "ag_adamw_step": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _i64, _f64, _f64, _f64, _f64, _f64, _f64, _f64]),
+}
+
+
+def load_library(path: str = LIB_PATH) -> C.CDLL:
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing: build it with `python -m autograd_b200.build` (needs nvcc). "
+            "autograd_b200 has no CPU or library fallback.")
+    lib = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = load_library()
+
+
+class AgError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"autograd_b200 error {code}: {message}")
+        self.code = code

@@ -1,0 +1,461 @@
+// Bandwidth-bound elementwise kernels: residual add, tanh-GELU, SwiGLU, AdamW.
+// All use 16-byte packets, grid-stride loops with several independent packets in flight per
+// thread, grids sized in multiples of the SM count, and IEEE math (no fast-math) so that
+// fp32 results stay within 1e-5 of the numpy reference.
+#include "ag_common.cuh"
+
+namespace {
+
+constexpr int EW_THREADS = 256;
+constexpr int EW_UNROLL = 4;
+
+inline int ew_grid(const ag_ctx* ctx, int64_t packets) {
+  int64_t want = (packets + (int64_t)EW_THREADS * EW_UNROLL - 1) / ((int64_t)EW_THREADS * EW_UNROLL);
+  int64_t cap = (int64_t)ctx->sm_count * 8;
+  if (want < 1) want = 1;
+  return (int)(want > cap ? cap : want);
+}
+
+// Generic driver: F is a functor with
+//   template<int NV> void packet(int64_t elem_index)   - process one 16-byte packet
+//   void scalar(int64_t elem_index)                    - process one element (ragged tail)
+template <int NV, typename F>
+__device__ __forceinline__ void ew_drive(int64_t n, F& f) {
+  const int64_t packets = n / NV;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + (EW_UNROLL - 1) * stride < packets; i += EW_UNROLL * stride) f.template packets<EW_UNROLL>(i, stride);
+  for (; i < packets; i += stride) f.template packets<1>(i, stride);
+  const int64_t tail = packets * NV;
+  for (int64_t j = tail + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride) f.scalar(j);
+}
+
+// ---------------------------------------------------------------------------- add
+struct AddFwd {
+  const float* x;
+  const float* y;
+  float* out;
+  template <int U>
+  __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
+    float a[U][4], b[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      Pack<float>::load_stream(x + (i + u * stride) * 4, a[u]);
+      Pack<float>::load_stream(y + (i + u * stride) * 4, b[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[u][e] += b[u][e];
+      Pack<float>::store(out + (i + u * stride) * 4, a[u]);
+    }
+  }
+  __device__ __forceinline__ void scalar(int64_t j) { out[j] = x[j] + y[j]; }
+};
+
+__global__ void __launch_bounds__(EW_THREADS) add_forward_kernel(AddFwd f, int64_t n) { ew_drive<4>(n, f); }
+
+struct AddBwd {
+  const float* g;
+  float* xg;
+  float* yg;
+  template <int U>
+  __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
+    float gv[U][4], a[U][4], b[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      Pack<float>::load(g + (i + u * stride) * 4, gv[u]);
+      if (xg) Pack<float>::load(xg + (i + u * stride) * 4, a[u]);
+      if (yg) Pack<float>::load(yg + (i + u * stride) * 4, b[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (xg) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a[u][e] += gv[u][e];
+        Pack<float>::store(xg + (i + u * stride) * 4, a[u]);
+      }
+      if (yg) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) b[u][e] += gv[u][e];
+        Pack<float>::store(yg + (i + u * stride) * 4, b[u]);
+      }
+    }
+  }
+  __device__ __forceinline__ void scalar(int64_t j) {
+    if (xg) xg[j] += g[j];
+    if (yg) yg[j] += g[j];
+  }
+};
+
+__global__ void __launch_bounds__(EW_THREADS) add_backward_kernel(AddBwd f, int64_t n) { ew_drive<4>(n, f); }
+
+// ---------------------------------------------------------------------------- GELU
+// backend.py:18-20
+constexpr float kGeluC = 0.7978845608028654f;
+constexpr float kGeluA = 0.044715f;
+constexpr float kGeluA3 = 0.134145f;
+
+__device__ __forceinline__ float gelu_inner_tanh(float x) {
+  // backend.py:380-385: ((x*x)*x)*A, + x, *C, tanh
+  float b = x * x;
+  b = b * x;
+  b = b * kGeluA;
+  b = x + b;
+  b = b * kGeluC;
+  return tanhf(b);
+}
+
+__device__ __forceinline__ float gelu_fwd1(float x) {
+  float t = gelu_inner_tanh(x);
+  return (x * (t + 1.0f)) * 0.5f;
+}
+
+__device__ __forceinline__ float gelu_grad1(float x) {
+  // backend.py:396-411
+  float t = gelu_inner_tanh(x);
+  float acc = 1.0f - t * t;
+  float d_inner = kGeluC * (1.0f + kGeluA3 * x * x);
+  acc = acc * (0.5f * x * d_inner);
+  return (t + 1.0f) * 0.5f + acc;
+}
+
+struct GeluFwd {
+  const float* x;
+  float* y;
+  template <int U>
+  __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
+    float a[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) Pack<float>::load_stream(x + (i + u * stride) * 4, a[u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[u][e] = gelu_fwd1(a[u][e]);
+      Pack<float>::store(y + (i + u * stride) * 4, a[u]);
+    }
+  }
+  __device__ __forceinline__ void scalar(int64_t j) { y[j] = gelu_fwd1(x[j]); }
+};
+
+__global__ void __launch_bounds__(EW_THREADS) gelu_forward_kernel(GeluFwd f, int64_t n) { ew_drive<4>(n, f); }
+
+struct GeluBwd {
+  const float* x;
+  const float* dy;
+  const float* dres;
+  float* dx;
+  template <int U>
+  __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
+    float a[U][4], g[U][4], r[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      Pack<float>::load_stream(x + (i + u * stride) * 4, a[u]);
+      Pack<float>::load_stream(dy + (i + u * stride) * 4, g[u]);
+      if (dres) Pack<float>::load(dres + (i + u * stride) * 4, r[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float local = g[u][e] * gelu_grad1(a[u][e]);
+        a[u][e] = dres ? r[u][e] + local : local;
+      }
+      Pack<float>::store(dx + (i + u * stride) * 4, a[u]);
+    }
+  }
+  __device__ __forceinline__ void scalar(int64_t j) {
+    float local = dy[j] * gelu_grad1(x[j]);
+    dx[j] = dres ? dres[j] + local : local;
+  }
+};
+
+__global__ void __launch_bounds__(EW_THREADS) gelu_backward_kernel(GeluBwd f, int64_t n) { ew_drive<4>(n, f); }
+
+// ---------------------------------------------------------------------------- SwiGLU
+__device__ __forceinline__ float sigmoid_ref(float g) {
+  // backend.py:1117-1120: 1 / (exp(-g) + 1)
+  return 1.0f / (expf(-g) + 1.0f);
+}
+
+// One thread handles packets of the same column range in the gate and up halves of a row.
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) swiglu_forward_kernel(const T* __restrict__ gu, T* __restrict__ hidden,
+                                                                    int64_t N, int I) {
+  constexpr int NV = Pack<T>::N;
+  const int ppr = I / NV;  // packets per row (I % NV == 0 on this path)
+  const int64_t packets = N * (int64_t)ppr;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < packets; i += 2 * stride) {
+    float g[2][NV], u[2][NV];
+    bool live[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t p = i + k * stride;
+      live[k] = p < packets;
+      if (live[k]) {
+        const int64_t row = p / ppr;
+        const int col = (int)(p - row * ppr) * NV;
+        Pack<T>::load_stream(gu + row * 2 * I + col, g[k]);
+        Pack<T>::load_stream(gu + row * 2 * I + I + col, u[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (live[k]) {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) g[k][e] = (g[k][e] * sigmoid_ref(g[k][e])) * u[k][e];
+        Pack<T>::store(hidden + (i + k * stride) * NV, g[k]);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) swiglu_forward_scalar_kernel(const T* __restrict__ gu,
+                                                                           T* __restrict__ hidden, int64_t N, int I) {
+  const int64_t total = N * (int64_t)I;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t row = i / I;
+    const int col = (int)(i - row * I);
+    const float g = Pack<T>::load1(gu + row * 2 * I + col);
+    const float u = Pack<T>::load1(gu + row * 2 * I + I + col);
+    Pack<T>::store1(hidden + i, (g * sigmoid_ref(g)) * u);
+  }
+}
+
+__device__ __forceinline__ void swiglu_bwd1(float g, float u, float dh, float& dg, float& du) {
+  // backend.py:1202-1217
+  const float s = sigmoid_ref(g);
+  float t = 1.0f - s;
+  t = t * g;
+  t = t + 1.0f;
+  t = t * s;
+  t = t * u;
+  dg = t * dh;
+  du = (g * s) * dh;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) swiglu_backward_kernel(T* __restrict__ gu, const T* __restrict__ dh,
+                                                                     int64_t N, int I) {
+  constexpr int NV = Pack<T>::N;
+  const int ppr = I / NV;
+  const int64_t packets = N * (int64_t)ppr;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < packets; i += 2 * stride) {
+    float g[2][NV], u[2][NV], d[2][NV];
+    bool live[2];
+    int64_t goff[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t p = i + k * stride;
+      live[k] = p < packets;
+      if (live[k]) {
+        const int64_t row = p / ppr;
+        const int col = (int)(p - row * ppr) * NV;
+        goff[k] = row * 2 * I + col;
+        Pack<T>::load(gu + goff[k], g[k]);
+        Pack<T>::load(gu + goff[k] + I, u[k]);
+        Pack<T>::load_stream(dh + p * NV, d[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (live[k]) {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          float dg, du;
+          swiglu_bwd1(g[k][e], u[k][e], d[k][e], dg, du);
+          g[k][e] = dg;
+          u[k][e] = du;
+        }
+        Pack<T>::store(gu + goff[k], g[k]);
+        Pack<T>::store(gu + goff[k] + I, u[k]);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) swiglu_backward_scalar_kernel(T* __restrict__ gu,
+                                                                            const T* __restrict__ dh, int64_t N,
+                                                                            int I) {
+  const int64_t total = N * (int64_t)I;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t row = i / I;
+    const int col = (int)(i - row * I);
+    T* pg = gu + row * 2 * I + col;
+    const float g = Pack<T>::load1(pg);
+    const float u = Pack<T>::load1(pg + I);
+    float dg, du;
+    swiglu_bwd1(g, u, Pack<T>::load1(dh + i), dg, du);
+    Pack<T>::store1(pg, dg);
+    Pack<T>::store1(pg + I, du);
+  }
+}
+
+// ---------------------------------------------------------------------------- AdamW
+struct AdamW {
+  float* p;
+  const float* g;
+  float* m;
+  float* v;
+  float lr_wd, lr_t, b1, b2, one_minus_b1, one_minus_b2, eps, grad_scale;
+  bool decay;
+  __device__ __forceinline__ void one(float& pp, float gg, float& mm, float& vv) const {
+    // backend.py:2021-2038, statement order kept
+    gg = gg * grad_scale;
+    if (decay) pp = pp - pp * lr_wd;
+    mm = mm * b1 + gg * one_minus_b1;
+    vv = vv * b2 + (gg * gg) * one_minus_b2;
+    pp = pp - (mm / (sqrtf(vv) + eps)) * lr_t;
+  }
+  template <int U>
+  __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
+    float pv[U][4], gv[U][4], mv[U][4], vv[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t o = (i + u * stride) * 4;
+      Pack<float>::load(p + o, pv[u]);
+      Pack<float>::load_stream(g + o, gv[u]);
+      Pack<float>::load(m + o, mv[u]);
+      Pack<float>::load(v + o, vv[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t o = (i + u * stride) * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) one(pv[u][e], gv[u][e], mv[u][e], vv[u][e]);
+      Pack<float>::store(p + o, pv[u]);
+      Pack<float>::store(m + o, mv[u]);
+      Pack<float>::store(v + o, vv[u]);
+    }
+  }
+  __device__ __forceinline__ void scalar(int64_t j) { one(p[j], g[j], m[j], v[j]); }
+};
+
+__global__ void __launch_bounds__(EW_THREADS) adamw_kernel(AdamW f, int64_t n) { ew_drive<4>(n, f); }
+
+template <typename... P>
+bool all_aligned16(P... p) {
+  return (ag_aligned16(p) && ...);
+}
+
+}  // namespace
+
+// =========================================================================================
+extern "C" int ag_add_forward(ag_ctx* ctx, const float* x, const float* y, float* out, int64_t n) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, x && y && out && n > 0, "ag_add_forward: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(x, y, out), "ag_add_forward: pointers must be 16-byte aligned");
+  add_forward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(AddFwd{x, y, out}, n);
+  AG_LAUNCHED(ctx, "add_forward_kernel");
+  return AG_OK;
+}
+
+extern "C" int ag_add_backward(ag_ctx* ctx, const float* g, float* xgrad, float* ygrad, int64_t n) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0 || (!xgrad && !ygrad)) return AG_OK;
+  AG_REQUIRE(ctx, g && n > 0, "ag_add_backward: null g or negative n");
+  AG_REQUIRE(ctx, all_aligned16(g, xgrad, ygrad), "ag_add_backward: pointers must be 16-byte aligned");
+  add_backward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(AddBwd{g, xgrad, ygrad}, n);
+  AG_LAUNCHED(ctx, "add_backward_kernel");
+  return AG_OK;
+}
+
+extern "C" int ag_gelu_forward(ag_ctx* ctx, const float* x, float* y, int64_t n) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, x && y && n > 0, "ag_gelu_forward: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(x, y), "ag_gelu_forward: pointers must be 16-byte aligned");
+  gelu_forward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(GeluFwd{x, y}, n);
+  AG_LAUNCHED(ctx, "gelu_forward_kernel");
+  return AG_OK;
+}
+
+extern "C" int ag_gelu_backward(ag_ctx* ctx, const float* x, const float* dy, const float* dres, float* dx,
+                                int64_t n) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, x && dy && dx && n > 0, "ag_gelu_backward: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(x, dy, dres, dx), "ag_gelu_backward: pointers must be 16-byte aligned");
+  gelu_backward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(GeluBwd{x, dy, dres, dx}, n);
+  AG_LAUNCHED(ctx, "gelu_backward_kernel");
+  return AG_OK;
+}
+
+template <typename T>
+static int swiglu_forward_t(ag_ctx* ctx, const void* gu, void* hidden, int64_t N, int I) {
+  constexpr int NV = Pack<T>::N;
+  if (I % NV == 0 && all_aligned16(gu, hidden)) {
+    const int64_t packets = N * (int64_t)(I / NV);
+    swiglu_forward_kernel<T><<<ew_grid(ctx, packets * 2), EW_THREADS, 0, ctx->stream>>>(
+        static_cast<const T*>(gu), static_cast<T*>(hidden), N, I);
+    AG_LAUNCHED(ctx, "swiglu_forward_kernel");
+  } else {
+    swiglu_forward_scalar_kernel<T><<<ew_grid(ctx, N * (int64_t)I), EW_THREADS, 0, ctx->stream>>>(
+        static_cast<const T*>(gu), static_cast<T*>(hidden), N, I);
+    AG_LAUNCHED(ctx, "swiglu_forward_scalar_kernel");
+  }
+  return AG_OK;
+}
+
+template <typename T>
+static int swiglu_backward_t(ag_ctx* ctx, void* gu, const void* dh, int64_t N, int I) {
+  constexpr int NV = Pack<T>::N;
+  if (I % NV == 0 && all_aligned16(gu, dh)) {
+    const int64_t packets = N * (int64_t)(I / NV);
+    swiglu_backward_kernel<T><<<ew_grid(ctx, packets * 2), EW_THREADS, 0, ctx->stream>>>(
+        static_cast<T*>(gu), static_cast<const T*>(dh), N, I);
+    AG_LAUNCHED(ctx, "swiglu_backward_kernel");
+  } else {
+    swiglu_backward_scalar_kernel<T><<<ew_grid(ctx, N * (int64_t)I), EW_THREADS, 0, ctx->stream>>>(
+        static_cast<T*>(gu), static_cast<const T*>(dh), N, I);
+    AG_LAUNCHED(ctx, "swiglu_backward_scalar_kernel");
+  }
+  return AG_OK;
+}
+
+extern "C" int ag_swiglu_forward(ag_ctx* ctx, const void* gu, void* hidden, int64_t N, int I, int dtype) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (N == 0 || I == 0) return AG_OK;
+  AG_REQUIRE(ctx, gu && hidden && N > 0 && I > 0, "ag_swiglu_forward: null pointer or negative size");
+  AG_REQUIRE(ctx, dtype == AG_F32 || dtype == AG_BF16, "ag_swiglu_forward: unknown dtype %d", dtype);
+  return dtype == AG_F32 ? swiglu_forward_t<float>(ctx, gu, hidden, N, I)
+                         : swiglu_forward_t<__nv_bfloat16>(ctx, gu, hidden, N, I);
+}
+
+extern "C" int ag_swiglu_backward(ag_ctx* ctx, void* gu, const void* dhidden, int64_t N, int I, int dtype) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (N == 0 || I == 0) return AG_OK;
+  AG_REQUIRE(ctx, gu && dhidden && N > 0 && I > 0, "ag_swiglu_backward: null pointer or negative size");
+  AG_REQUIRE(ctx, dtype == AG_F32 || dtype == AG_BF16, "ag_swiglu_backward: unknown dtype %d", dtype);
+  return dtype == AG_F32 ? swiglu_backward_t<float>(ctx, gu, dhidden, N, I)
+                         : swiglu_backward_t<__nv_bfloat16>(ctx, gu, dhidden, N, I);
+}
+
+extern "C" int ag_adamw_step(ag_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, double lr,
+                             double lr_t, double b1, double b2, double eps, double weight_decay,
+                             double grad_scale) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, p && g && m && v && n > 0, "ag_adamw_step: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(p, g, m, v), "ag_adamw_step: pointers must be 16-byte aligned");
+  AdamW f;
+  f.p = p; f.g = g; f.m = m; f.v = v;
+  // the reference multiplies fp32 arrays by python doubles: the scalar expression is
+  // evaluated in double, then rounded once to fp32 (backend.py:2022, :2026, :2031)
+  f.lr_wd = (float)(lr * weight_decay);
+  f.lr_t = (float)lr_t; f.b1 = (float)b1; f.b2 = (float)b2;
+  f.one_minus_b1 = (float)(1.0 - b1);
+  f.one_minus_b2 = (float)(1.0 - b2);
+  f.eps = (float)eps; f.grad_scale = (float)grad_scale;
+  f.decay = weight_decay > 0.0;
+  adamw_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(f, n);
+  AG_LAUNCHED(ctx, "adamw_kernel");
+  return AG_OK;
+}

@@ -1,0 +1,15 @@
+// Internal interface between the fused linear+CE driver (ag_flce.cu) and the tcgen05
+// tensor-core panels (ag_flce_tc.cu).
+#pragma once
+
+#include "ag_common.cuh"
+
+// True when the tensor-core path takes this problem (shape/alignment constraints).
+bool ag_flce_tc_supported(const ag_flce_desc* d);
+// Extra workspace (split / converted operands) the tensor-core path needs.
+size_t ag_flce_tc_scratch_bytes(const ag_flce_desc* d);
+// Converts X and W into the operand format of d->precision inside tc_scratch.
+int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch);
+// panel[rows, vc] (row stride ld) = X[r0:r0+rows] . W[v0:v0+vc]^T from the prepared operands.
+int ag_flce_tc_logits(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
+                      float* panel, int64_t ld);

@@ -1,0 +1,654 @@
+// (residual add +) LayerNorm and RMSNorm, forward and backward.
+//
+// Layout: one warp owns one row at a time and keeps the whole row in registers
+// (KP 16-byte packets per lane, packet p of lane l covers columns (p*32+l)*NV ..+NV), so a
+// row is read from HBM exactly once per kernel even though the statistics are two-pass
+// (mean, then centred variance - the reference's formulation, backend.py:423-429).
+// gamma/beta are staged once per CTA in shared memory by the bulk-copy (TMA) engine.
+// Rows are distributed grid-stride over a persistent grid (a multiple of the SM count).
+//
+// Backward column sums (dgamma, dbeta) use no atomics: every lane accumulates its own
+// columns over the rows its warp visits, the CTA folds its warps through shared memory in
+// warp order and writes one partial row, and a second kernel adds the partial rows in
+// index order into dgamma/dbeta.  The summation order is therefore fixed by (N, C, grid).
+//
+// Shapes that do not fit the register layout (C not a multiple of the packet width, or a
+// row longer than 16 packets per lane) take a CTA-per-row kernel with scalar accesses.
+#include "ag_common.cuh"
+
+namespace {
+
+constexpr int NORM_WARPS = 8;
+constexpr int NORM_THREADS = NORM_WARPS * 32;
+
+enum NormKind { kLayerNorm = 0, kRmsNorm = 1 };
+
+// ---------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------
+template <typename T, int KP, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_forward_kernel(const T* x, const T* r, const float* __restrict__ gamma,
+                    const float* __restrict__ beta, T* h, T* __restrict__ y, float* __restrict__ stat0,
+                    float* __restrict__ stat1, int64_t N, int C, float eps, int* status) {
+  constexpr int NV = Pack<T>::N;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* s_gamma = reinterpret_cast<float*>(smem_raw);
+  float* s_beta = s_gamma + C;
+  __shared__ __align__(8) uint64_t s_bar;
+  if (gamma) ag_stage_vectors(s_gamma, gamma, s_beta, (KIND == kLayerNorm) ? beta : nullptr, C, &s_bar, status);
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const float inv_c = 1.0f / (float)C;
+
+  for (int64_t row = (int64_t)blockIdx.x * NORM_WARPS + warp; row < N; row += (int64_t)gridDim.x * NORM_WARPS) {
+    float v[KP][NV];
+    const T* xr = x + row * C;
+#pragma unroll
+    for (int p = 0; p < KP; ++p) {
+      const int col = (p * 32 + lane) * NV;
+      if (col < C) {
+        Pack<T>::load_stream(xr + col, v[p]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) v[p][e] = 0.0f;
+      }
+    }
+    if (r) {
+      const T* rr = r + row * C;
+#pragma unroll
+      for (int p = 0; p < KP; ++p) {
+        const int col = (p * 32 + lane) * NV;
+        if (col < C) {
+          float t[NV];
+          Pack<T>::load_stream(rr + col, t);
+#pragma unroll
+          for (int e = 0; e < NV; ++e) v[p][e] += t[e];
+        }
+      }
+    }
+    if (h) {
+      T* hr = h + row * C;
+#pragma unroll
+      for (int p = 0; p < KP; ++p) {
+        const int col = (p * 32 + lane) * NV;
+        if (col < C) Pack<T>::store(hr + col, v[p]);
+      }
+    }
+    float mean = 0.0f, scale;
+    if (KIND == kLayerNorm) {
+      float s = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) s += v[p][e];
+      mean = ag_warp_sum(s) * inv_c;
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP; ++p) {
+        const int col = (p * 32 + lane) * NV;
+        if (col < C) {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) {
+            v[p][e] -= mean;
+            q += v[p][e] * v[p][e];
+          }
+        }
+      }
+      scale = 1.0f / sqrtf(ag_warp_sum(q) * inv_c + eps);
+    } else {
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) q += v[p][e] * v[p][e];
+      scale = 1.0f / sqrtf(ag_warp_sum(q) * inv_c + eps);
+    }
+    if (lane == 0) {
+      if (KIND == kLayerNorm) {
+        if (stat0) stat0[row] = mean;
+        if (stat1) stat1[row] = scale;
+      } else if (stat0) {
+        stat0[row] = scale;
+      }
+    }
+    T* yr = y + row * C;
+#pragma unroll
+    for (int p = 0; p < KP; ++p) {
+      const int col = (p * 32 + lane) * NV;
+      if (col < C) {
+        float o[NV];
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          float t = v[p][e] * scale;
+          if (gamma) t = t * s_gamma[col + e];
+          if (KIND == kLayerNorm) t = t + s_beta[col + e];
+          o[e] = t;
+        }
+        Pack<T>::store_stream(yr + col, o);
+      }
+    }
+  }
+}
+
+// CTA-per-row fallback for arbitrary C (scalar, row re-read from L1/L2 between passes).
+template <typename T, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_forward_generic_kernel(const T* x, const T* r, const float* __restrict__ gamma,
+                            const float* __restrict__ beta, T* h, T* __restrict__ y,
+                            float* __restrict__ stat0, float* __restrict__ stat1, int64_t N, int C, float eps) {
+  __shared__ float s_red[NORM_WARPS];
+  __shared__ float s_bcast;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto block_sum = [&](float v) -> float {
+    v = ag_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.0f;
+      for (int w = 0; w < NORM_WARPS; ++w) t += s_red[w];
+      s_bcast = t;
+    }
+    __syncthreads();
+    return s_bcast;
+  };
+  const float inv_c = 1.0f / (float)C;
+  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+    const T* xr = x + row * C;
+    const T* rr = r ? r + row * C : nullptr;
+    auto val = [&](int c) -> float {
+      float t = Pack<T>::load1(xr + c);
+      if (rr) t += Pack<T>::load1(rr + c);
+      return t;
+    };
+    float mean = 0.0f, scale;
+    if (KIND == kLayerNorm) {
+      float s = 0.0f;
+      for (int c = threadIdx.x; c < C; c += NORM_THREADS) s += val(c);
+      mean = block_sum(s) * inv_c;
+      float q = 0.0f;
+      for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+        float d = val(c) - mean;
+        q += d * d;
+      }
+      scale = 1.0f / sqrtf(block_sum(q) * inv_c + eps);
+    } else {
+      float q = 0.0f;
+      for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+        float d = val(c);
+        q += d * d;
+      }
+      scale = 1.0f / sqrtf(block_sum(q) * inv_c + eps);
+    }
+    if (threadIdx.x == 0) {
+      if (KIND == kLayerNorm) {
+        if (stat0) stat0[row] = mean;
+        if (stat1) stat1[row] = scale;
+      } else if (stat0) {
+        stat0[row] = scale;
+      }
+    }
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+      const float hv = val(c);
+      float t = (hv - mean) * scale;
+      if (gamma) t = t * gamma[c];
+      if (KIND == kLayerNorm) t = t + beta[c];
+      if (h) Pack<T>::store1(h + row * C + c, hv);
+      Pack<T>::store1(y + row * C + c, t);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------
+// partials layout: [gridDim.x][2][C] floats (slot 0: dgamma, slot 1: dbeta; RMSNorm leaves
+// slot 1 unwritten and unread).
+template <typename T, int KP, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
+                     const T* dres, T* dx, float* __restrict__ partials, int want_dgamma, int want_dbeta, int64_t N,
+                     int C, float eps, int* status) {
+  constexpr int NV = Pack<T>::N;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* s_gamma = reinterpret_cast<float*>(smem_raw);  // C floats
+  float* s_acc = s_gamma + C;                           // NORM_WARPS * C floats
+  __shared__ __align__(8) uint64_t s_bar;
+  if (gamma) ag_stage_vectors(s_gamma, gamma, nullptr, nullptr, C, &s_bar, status);
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const float inv_c = 1.0f / (float)C;
+
+  float acc_g[KP][NV], acc_b[KP][NV];
+#pragma unroll
+  for (int p = 0; p < KP; ++p)
+#pragma unroll
+    for (int e = 0; e < NV; ++e) acc_g[p][e] = acc_b[p][e] = 0.0f;
+
+  for (int64_t row = (int64_t)blockIdx.x * NORM_WARPS + warp; row < N; row += (int64_t)gridDim.x * NORM_WARPS) {
+    float v[KP][NV], g[KP][NV];
+    const T* xr = x + row * C;
+    const T* gr = dy + row * C;
+#pragma unroll
+    for (int p = 0; p < KP; ++p) {
+      const int col = (p * 32 + lane) * NV;
+      if (col < C) {
+        Pack<T>::load_stream(xr + col, v[p]);
+        Pack<T>::load_stream(gr + col, g[p]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) v[p][e] = g[p][e] = 0.0f;
+      }
+    }
+    // statistics, recomputed from the saved input exactly as in forward
+    float scale;
+    if (KIND == kLayerNorm) {
+      float s = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) s += v[p][e];
+      const float mean = ag_warp_sum(s) * inv_c;
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP; ++p) {
+        const int col = (p * 32 + lane) * NV;
+        if (col < C) {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) {
+            v[p][e] -= mean;
+            q += v[p][e] * v[p][e];
+          }
+        }
+      }
+      scale = 1.0f / sqrtf(ag_warp_sum(q) * inv_c + eps);
+    } else {
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) q += v[p][e] * v[p][e];
+      scale = 1.0f / sqrtf(ag_warp_sum(q) * inv_c + eps);
+    }
+    // v <- xhat ; column sums ; g <- dy*gamma ; row sums
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int p = 0; p < KP; ++p) {
+      const int col = (p * 32 + lane) * NV;
+      if (col < C) {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          const float xh = v[p][e] * scale;
+          v[p][e] = xh;
+          acc_g[p][e] += g[p][e] * xh;
+          if (KIND == kLayerNorm) acc_b[p][e] += g[p][e];
+          const float dg = gamma ? g[p][e] * s_gamma[col + e] : g[p][e];
+          g[p][e] = dg;
+          s1 += dg;
+          s2 += dg * xh;
+        }
+      }
+    }
+    float m1 = 0.0f;
+    if (KIND == kLayerNorm) m1 = (ag_warp_sum(s1) * inv_c) * scale;
+    const float m2 = (ag_warp_sum(s2) * inv_c) * scale;
+    if (dx == nullptr) continue;  // only the column sums were asked for
+    T* dxr = dx + row * C;
+    const T* drr = dres ? dres + row * C : nullptr;
+#pragma unroll
+    for (int p = 0; p < KP; ++p) {
+      const int col = (p * 32 + lane) * NV;
+      if (col < C) {
+        float o[NV];
+        if (drr) {
+          Pack<T>::load(drr + col, o);
+        } else {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) o[e] = 0.0f;
+        }
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          // backend.py:475-487: xg += dyg*rstd; xg -= m1; xg -= xhat*m2
+          float t = o[e] + g[p][e] * scale;
+          if (KIND == kLayerNorm) t = t - m1;
+          o[e] = t - v[p][e] * m2;
+        }
+        Pack<T>::store(dxr + col, o);
+      }
+    }
+  }
+
+  // fold the warps' column accumulators in warp order, one slot at a time
+  const int n_slots = (KIND == kLayerNorm) ? 2 : 1;
+  for (int slot = 0; slot < n_slots; ++slot) {
+    const bool wanted = slot == 0 ? (want_dgamma != 0) : (want_dbeta != 0);
+    if (!wanted) continue;  // uniform across the CTA
+    __syncthreads();
+#pragma unroll
+    for (int p = 0; p < KP; ++p) {
+      const int col = (p * 32 + lane) * NV;
+      if (col < C) {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) s_acc[warp * C + col + e] = slot == 0 ? acc_g[p][e] : acc_b[p][e];
+      }
+    }
+    __syncthreads();
+    float* out = partials + ((int64_t)blockIdx.x * 2 + slot) * C;
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < NORM_WARPS; ++w) t += s_acc[w * C + c];
+      out[c] = t;
+    }
+  }
+}
+
+// CTA-per-row fallback: per-thread column accumulators for columns c = tid + k*THREADS are
+// kept in shared memory rows (one per CTA), rows visited grid-stride.
+template <typename T, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_backward_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
+                             const T* dres, T* dx, float* __restrict__ partials, int want_dgamma, int want_dbeta,
+                             int64_t N, int C, float eps) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* s_g = reinterpret_cast<float*>(smem_raw);  // C floats: dgamma accumulators
+  float* s_b = s_g + C;                             // C floats: dbeta accumulators
+  __shared__ float s_red[NORM_WARPS];
+  __shared__ float s_bcast;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto block_sum = [&](float v) -> float {
+    v = ag_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.0f;
+      for (int w = 0; w < NORM_WARPS; ++w) t += s_red[w];
+      s_bcast = t;
+    }
+    __syncthreads();
+    return s_bcast;
+  };
+  for (int c = threadIdx.x; c < C; c += NORM_THREADS) s_g[c] = s_b[c] = 0.0f;
+  const float inv_c = 1.0f / (float)C;
+  for (int64_t row = blockIdx.x; row < N; row += gridDim.x) {
+    const T* xr = x + row * C;
+    const T* gr = dy + row * C;
+    float mean = 0.0f, scale;
+    if (KIND == kLayerNorm) {
+      float s = 0.0f;
+      for (int c = threadIdx.x; c < C; c += NORM_THREADS) s += Pack<T>::load1(xr + c);
+      mean = block_sum(s) * inv_c;
+      float q = 0.0f;
+      for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+        float d = Pack<T>::load1(xr + c) - mean;
+        q += d * d;
+      }
+      scale = 1.0f / sqrtf(block_sum(q) * inv_c + eps);
+    } else {
+      float q = 0.0f;
+      for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+        float d = Pack<T>::load1(xr + c);
+        q += d * d;
+      }
+      scale = 1.0f / sqrtf(block_sum(q) * inv_c + eps);
+    }
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+      const float xh = (Pack<T>::load1(xr + c) - mean) * scale;
+      const float g = Pack<T>::load1(gr + c);
+      s_g[c] += g * xh;  // column c is always visited by the same thread
+      if (KIND == kLayerNorm) s_b[c] += g;
+      const float dg = gamma ? g * gamma[c] : g;
+      s1 += dg;
+      s2 += dg * xh;
+    }
+    float m1 = 0.0f;
+    if (KIND == kLayerNorm) m1 = (block_sum(s1) * inv_c) * scale;
+    const float m2 = (block_sum(s2) * inv_c) * scale;
+    for (int c = threadIdx.x; dx != nullptr && c < C; c += NORM_THREADS) {
+      const float xh = (Pack<T>::load1(xr + c) - mean) * scale;
+      const float g = Pack<T>::load1(gr + c);
+      const float dg = gamma ? g * gamma[c] : g;
+      float t = (dres ? Pack<T>::load1(dres + row * C + c) : 0.0f) + dg * scale;
+      if (KIND == kLayerNorm) t = t - m1;
+      Pack<T>::store1(dx + row * C + c, t - xh * m2);
+    }
+  }
+  for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+    if (want_dgamma) partials[((int64_t)blockIdx.x * 2 + 0) * C + c] = s_g[c];
+    if (KIND == kLayerNorm && want_dbeta) partials[((int64_t)blockIdx.x * 2 + 1) * C + c] = s_b[c];
+  }
+}
+
+// Second pass: dgamma[c] += sum_p partials[p][0][c], dbeta[c] += sum_p partials[p][1][c].
+// Block = 32 columns x 32 partial-row groups; group y adds rows y, y+32, ... in order, the
+// 32 group sums are then added in group order.  Fixed order, no atomics.
+__global__ void __launch_bounds__(1024)
+norm_partials_reduce_kernel(const float* __restrict__ partials, int P, int C, float* dgamma, float* dbeta) {
+  __shared__ float s[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  const int slot = blockIdx.y;
+  float* out = slot == 0 ? dgamma : dbeta;
+  if (!out) return;  // uniform per block
+  float t = 0.0f;
+  if (c < C)
+    for (int p = threadIdx.y; p < P; p += 32) t += partials[((int64_t)p * 2 + slot) * C + c];
+  s[threadIdx.y][threadIdx.x] = t;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    float tot = 0.0f;
+#pragma unroll
+    for (int y = 0; y < 32; ++y) tot += s[y][threadIdx.x];
+    out[c] += tot;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host-side dispatch
+// ---------------------------------------------------------------------------------------
+inline int pick_kp(int packets_per_row) {
+  const int need = (packets_per_row + 31) / 32;
+  static const int kChoices[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
+  for (int k : kChoices)
+    if (k >= need) return k;
+  return 0;
+}
+
+// Persistent grid: exactly the number of CTAs that are resident at once (occupancy x SMs),
+// so that no partial second wave forms; fewer when there are not enough rows.
+inline int persistent_grid(const ag_ctx* ctx, int64_t N, int ctas_per_sm) {
+  int64_t want = (N + NORM_WARPS - 1) / NORM_WARPS;
+  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  if (ctas_per_sm > 8) ctas_per_sm = 8;
+  int64_t cap = (int64_t)ctx->sm_count * ctas_per_sm;
+  return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+}
+
+// Resident CTAs per SM of one kernel instantiation at a given dynamic shared-memory size;
+// queried once per (kernel, smem) and cached (single host thread per context).
+template <typename K>
+int resident_ctas(ag_ctx* ctx, K kern, size_t smem, int* cache, size_t* cache_smem) {
+  if (*cache > 0 && *cache_smem == smem) return *cache;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return -1;
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NORM_THREADS, smem) != cudaSuccess) return -1;
+  *cache = occ < 1 ? 1 : occ;
+  *cache_smem = smem;
+  (void)ctx;
+  return *cache;
+}
+
+template <typename T, int KIND, int KP>
+int launch_fwd_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const float* beta, T* h, T* y, float* s0,
+                  float* s1, int64_t N, int C, float eps) {
+  const size_t smem = (size_t)2 * C * sizeof(float);
+  auto kern = norm_forward_kernel<T, KP, KIND>;
+  static int occ_cache = 0;
+  static size_t occ_smem = 0;
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
+  if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_forward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
+  kern<<<persistent_grid(ctx, N, occ), NORM_THREADS, smem, ctx->stream>>>(x, r, gamma, beta, h, y, s0, s1, N, C, eps,
+                                                                          ctx->d_status);
+  AG_LAUNCHED(ctx, "norm_forward_kernel");
+  return AG_OK;
+}
+
+template <typename T, int KIND>
+int launch_fwd(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const float* beta, T* h, T* y, float* s0,
+               float* s1, int64_t N, int C, float eps) {
+  constexpr int NV = Pack<T>::N;
+  const bool vec_ok = (C % NV == 0) && ag_aligned16(x) && ag_aligned16(r) && ag_aligned16(h) && ag_aligned16(y);
+  const int kp = vec_ok ? pick_kp(C / NV) : 0;
+#define AG_FWD_CASE(K) \
+  case K:              \
+    return launch_fwd_kp<T, KIND, K>(ctx, x, r, gamma, beta, h, y, s0, s1, N, C, eps);
+  switch (kp) {
+    AG_FWD_CASE(1) AG_FWD_CASE(2) AG_FWD_CASE(3) AG_FWD_CASE(4) AG_FWD_CASE(5) AG_FWD_CASE(6) AG_FWD_CASE(8)
+    AG_FWD_CASE(10) AG_FWD_CASE(12) AG_FWD_CASE(16)
+    default:
+      break;
+  }
+#undef AG_FWD_CASE
+  int64_t cap = (int64_t)ctx->sm_count * 8;
+  int grid = (int)(N < cap ? N : cap);
+  norm_forward_generic_kernel<T, KIND><<<grid, NORM_THREADS, 0, ctx->stream>>>(x, r, gamma, beta, h, y, s0, s1, N, C, eps);
+  AG_LAUNCHED(ctx, "norm_forward_generic_kernel");
+  return AG_OK;
+}
+
+// Largest grid any backward launch may use: bounds the partials workspace.
+inline int max_partial_rows(const ag_ctx* ctx) { return ctx->sm_count * 8; }
+
+template <typename T, int KIND, int KP>
+int launch_bwd_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T* dres, T* dx, float* partials,
+                  int wg, int wb, int64_t N, int C, float eps, int* grid_out) {
+  const size_t smem = (size_t)(1 + NORM_WARPS) * C * sizeof(float);
+  auto kern = norm_backward_kernel<T, KP, KIND>;
+  static int occ_cache = 0;
+  static size_t occ_smem = 0;
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
+  if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
+  const int grid = persistent_grid(ctx, N, occ);
+  kern<<<grid, NORM_THREADS, smem, ctx->stream>>>(dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, ctx->d_status);
+  AG_LAUNCHED(ctx, "norm_backward_kernel");
+  *grid_out = grid;
+  return AG_OK;
+}
+
+template <typename T, int KIND>
+int launch_bwd(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T* dres, T* dx, float* dgamma,
+               float* dbeta, void* partials_v, size_t partials_bytes, int64_t N, int C, float eps) {
+  constexpr int NV = Pack<T>::N;
+  float* partials = static_cast<float*>(partials_v);
+  const int wg = dgamma != nullptr, wb = (KIND == kLayerNorm) && dbeta != nullptr;
+  if (wg || wb) {
+    if (!partials || partials_bytes < ag_norm_partials_bytes(ctx, C))
+      AG_FAIL(ctx, AG_ERR_SCRATCH, "norm backward: partials workspace has %zu bytes, needs %zu", partials_bytes,
+              ag_norm_partials_bytes(ctx, C));
+    AG_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(partials) & 3u) == 0, "norm backward: partials not 4-byte aligned");
+  }
+  const bool vec_ok = (C % NV == 0) && ag_aligned16(dy) && ag_aligned16(x) && ag_aligned16(dres) && ag_aligned16(dx);
+  const int kp = vec_ok ? pick_kp(C / NV) : 0;
+  int grid = 0;
+  int rc = -1;
+#define AG_BWD_CASE(K)                                                                                  \
+  case K:                                                                                               \
+    rc = launch_bwd_kp<T, KIND, K>(ctx, dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, &grid);    \
+    break;
+  switch (kp) {
+    AG_BWD_CASE(1) AG_BWD_CASE(2) AG_BWD_CASE(3) AG_BWD_CASE(4) AG_BWD_CASE(5) AG_BWD_CASE(6) AG_BWD_CASE(8)
+    AG_BWD_CASE(10) AG_BWD_CASE(12) AG_BWD_CASE(16)
+    default:
+      break;
+  }
+#undef AG_BWD_CASE
+  if (rc > 0) return rc;
+  if (rc < 0) {
+    const size_t smem = (size_t)2 * C * sizeof(float);
+    auto kern = norm_backward_generic_kernel<T, KIND>;
+    if (smem > 48 * 1024)
+      AG_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t cap = (int64_t)ctx->sm_count * 4;
+    grid = (int)(N < cap ? N : cap);
+    kern<<<grid, NORM_THREADS, smem, ctx->stream>>>(dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps);
+    AG_LAUNCHED(ctx, "norm_backward_generic_kernel");
+  }
+  if (wg || wb) {
+    dim3 rgrid((C + 31) / 32, KIND == kLayerNorm ? 2 : 1);
+    norm_partials_reduce_kernel<<<rgrid, dim3(32, 32), 0, ctx->stream>>>(partials, grid, C, wg ? dgamma : nullptr,
+                                                                         wb ? dbeta : nullptr);
+    AG_LAUNCHED(ctx, "norm_partials_reduce_kernel");
+  }
+  return AG_OK;
+}
+
+}  // namespace
+
+// =========================================================================================
+extern "C" size_t ag_norm_partials_bytes(ag_ctx* ctx, int C) {
+  if (!ctx || C <= 0) return 0;
+  return (size_t)max_partial_rows(ctx) * 2 * (size_t)C * sizeof(float);
+}
+
+extern "C" int ag_add_layernorm_forward(ag_ctx* ctx, const float* x, const float* r, const float* gamma,
+                                        const float* beta, float* h, float* y, float* mean, float* rstd, int64_t N,
+                                        int C, float eps) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (N == 0) return AG_OK;
+  AG_REQUIRE(ctx, x && gamma && beta && y, "ag_add_layernorm_forward: null pointer");
+  AG_REQUIRE(ctx, N > 0 && C > 0, "ag_add_layernorm_forward: bad shape N=%lld C=%d", (long long)N, C);
+  AG_REQUIRE(ctx, (size_t)2 * C * 4 <= 200 * 1024, "ag_add_layernorm_forward: C=%d too large", C);
+  return launch_fwd<float, kLayerNorm>(ctx, x, r, gamma, beta, h, y, mean, rstd, N, C, eps);
+}
+
+extern "C" int ag_layernorm_backward(ag_ctx* ctx, const float* dy, const float* x, const float* gamma,
+                                     const float* dres, float* dx, float* dgamma, float* dbeta, void* partials,
+                                     size_t partials_bytes, int64_t N, int C, float eps) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (N == 0) return AG_OK;
+  AG_REQUIRE(ctx, dy && x && gamma, "ag_layernorm_backward: null pointer");
+  AG_REQUIRE(ctx, N > 0 && C > 0, "ag_layernorm_backward: bad shape N=%lld C=%d", (long long)N, C);
+  AG_REQUIRE(ctx, (size_t)(1 + NORM_WARPS) * C * 4 <= 200 * 1024, "ag_layernorm_backward: C=%d too large", C);
+  return launch_bwd<float, kLayerNorm>(ctx, dy, x, gamma, dres, dx, dgamma, dbeta, partials, partials_bytes, N, C, eps);
+}
+
+extern "C" int ag_rmsnorm_forward(ag_ctx* ctx, const void* x, const float* gamma, void* y, float* inv_rms, int64_t N,
+                                  int C, float eps, int dtype) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (N == 0) return AG_OK;
+  AG_REQUIRE(ctx, x && y, "ag_rmsnorm_forward: null pointer");
+  AG_REQUIRE(ctx, N > 0 && C > 0, "ag_rmsnorm_forward: bad shape N=%lld C=%d", (long long)N, C);
+  AG_REQUIRE(ctx, dtype == AG_F32 || dtype == AG_BF16, "ag_rmsnorm_forward: unknown dtype %d", dtype);
+  AG_REQUIRE(ctx, (size_t)2 * C * 4 <= 200 * 1024, "ag_rmsnorm_forward: C=%d too large", C);
+  if (dtype == AG_F32)
+    return launch_fwd<float, kRmsNorm>(ctx, static_cast<const float*>(x), nullptr, gamma, nullptr, nullptr,
+                                       static_cast<float*>(y), inv_rms, nullptr, N, C, eps);
+  return launch_fwd<__nv_bfloat16, kRmsNorm>(ctx, static_cast<const __nv_bfloat16*>(x), nullptr, gamma, nullptr,
+                                             nullptr, static_cast<__nv_bfloat16*>(y), inv_rms, nullptr, N, C, eps);
+}
+
+extern "C" int ag_rmsnorm_backward(ag_ctx* ctx, const void* dz, const void* x, const float* gamma, const void* dres,
+                                   void* dx, float* dgamma, void* partials, size_t partials_bytes, int64_t N, int C,
+                                   float eps, int dtype) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (N == 0) return AG_OK;
+  AG_REQUIRE(ctx, dz && x, "ag_rmsnorm_backward: null pointer");
+  AG_REQUIRE(ctx, N > 0 && C > 0, "ag_rmsnorm_backward: bad shape N=%lld C=%d", (long long)N, C);
+  AG_REQUIRE(ctx, dtype == AG_F32 || dtype == AG_BF16, "ag_rmsnorm_backward: unknown dtype %d", dtype);
+  AG_REQUIRE(ctx, gamma || !dgamma, "ag_rmsnorm_backward: dgamma requested without gamma");
+  AG_REQUIRE(ctx, (size_t)(1 + NORM_WARPS) * C * 4 <= 200 * 1024, "ag_rmsnorm_backward: C=%d too large", C);
+  if (dtype == AG_F32)
+    return launch_bwd<float, kRmsNorm>(ctx, static_cast<const float*>(dz), static_cast<const float*>(x), gamma,
+                                       static_cast<const float*>(dres), static_cast<float*>(dx), dgamma, nullptr,
+                                       partials, partials_bytes, N, C, eps);
+  return launch_bwd<__nv_bfloat16, kRmsNorm>(ctx, static_cast<const __nv_bfloat16*>(dz),
+                                             static_cast<const __nv_bfloat16*>(x), gamma,
+                                             static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx),
+                                             dgamma, nullptr, partials, partials_bytes, N, C, eps);
+}

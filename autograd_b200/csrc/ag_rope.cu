@@ -1,0 +1,136 @@
+// Rotate-half RoPE applied in place to q (B,T,H,D) and k (B,T,HKV,D).
+//
+// One CTA handles one token (b,t): its cos/sin row (D/2 floats each) is staged in shared
+// memory once and reused by all H+HKV heads.  A thread owns one 16-byte packet of the low
+// half of a head together with the matching packet of the high half, so both halves are
+// read once and written once.  All loads of a thread's heads are issued before the first
+// store.  Shapes where D/2 is not a multiple of the packet width use a scalar kernel.
+#include "ag_common.cuh"
+
+namespace {
+
+constexpr int ROPE_THREADS = 256;
+constexpr int ROPE_MAX_ITEMS = 4;  // packets pairs per thread kept in flight
+
+template <typename T>
+__global__ void __launch_bounds__(ROPE_THREADS)
+rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int T_len, int H, int HKV,
+            int D, int64_t q_stride, int64_t k_stride, float sgn, int* status) {
+  constexpr int NV = Pack<T>::N;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int d2 = D >> 1;
+  float* s_cos = reinterpret_cast<float*>(smem_raw);
+  float* s_sin = s_cos + d2;
+  __shared__ __align__(8) uint64_t s_bar;
+  const int64_t tok = blockIdx.x;  // b*T + t
+  const int t = (int)(tok % T_len);
+  ag_stage_vectors(s_cos, cos_tab + (int64_t)t * d2, s_sin, sin_tab + (int64_t)t * d2, d2, &s_bar, status);
+
+  const int ppd = d2 / NV;              // packets per half head
+  const int items = (H + HKV) * ppd;    // packet pairs of this token
+  T* qt = q + tok * q_stride;
+  T* kt = k ? k + tok * k_stride : nullptr;
+
+  for (int base = threadIdx.x; base < items; base += ROPE_THREADS * ROPE_MAX_ITEMS) {
+    float lo[ROPE_MAX_ITEMS][NV], hi[ROPE_MAX_ITEMS][NV];
+    T* ptr[ROPE_MAX_ITEMS];
+    int col[ROPE_MAX_ITEMS];
+#pragma unroll
+    for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
+      const int it = base + u * ROPE_THREADS;
+      ptr[u] = nullptr;
+      if (it < items) {
+        const int head = it / ppd;
+        col[u] = (it - head * ppd) * NV;
+        T* hp = head < H ? qt + (int64_t)head * D : (kt ? kt + (int64_t)(head - H) * D : nullptr);
+        if (hp) {
+          ptr[u] = hp + col[u];
+          Pack<T>::load(ptr[u], lo[u]);
+          Pack<T>::load(ptr[u] + d2, hi[u]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
+      if (ptr[u]) {
+        float olo[NV], ohi[NV];
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          const float c = s_cos[col[u] + e];
+          const float s = sgn * s_sin[col[u] + e];
+          // sgn=+1: lo*c - hi*s , lo*s + hi*c   (backend.py:1413-1414)
+          // sgn=-1: lo*c + hi*s , -lo*s + hi*c  (backend.py:1396-1397)
+          olo[e] = lo[u][e] * c - hi[u][e] * s;
+          ohi[e] = lo[u][e] * s + hi[u][e] * c;
+        }
+        Pack<T>::store(ptr[u], olo);
+        Pack<T>::store(ptr[u] + d2, ohi);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROPE_THREADS)
+rope_scalar_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int T_len, int H,
+                   int HKV, int D, int64_t q_stride, int64_t k_stride, float sgn) {
+  const int d2 = D >> 1;
+  const int64_t tok = blockIdx.x;
+  const int t = (int)(tok % T_len);
+  const int items = (H + HKV) * d2;
+  for (int it = threadIdx.x; it < items; it += ROPE_THREADS) {
+    const int head = it / d2;
+    const int c0 = it - head * d2;
+    T* hp = head < H ? q + tok * q_stride + (int64_t)head * D : (k ? k + tok * k_stride + (int64_t)(head - H) * D : nullptr);
+    if (!hp) continue;
+    const float c = cos_tab[(int64_t)t * d2 + c0];
+    const float s = sgn * sin_tab[(int64_t)t * d2 + c0];
+    const float lo = Pack<T>::load1(hp + c0), hi = Pack<T>::load1(hp + c0 + d2);
+    Pack<T>::store1(hp + c0, lo * c - hi * s);
+    Pack<T>::store1(hp + c0 + d2, lo * s + hi * c);
+  }
+}
+
+template <typename T>
+int rope_t(ag_ctx* ctx, void* qv, void* kv, const float* cos_tab, const float* sin_tab, int B, int T_len, int H,
+           int HKV, int D, int64_t qs, int64_t ks, int sin_sign) {
+  constexpr int NV = Pack<T>::N;
+  T* q = static_cast<T*>(qv);
+  T* k = static_cast<T*>(kv);
+  const int d2 = D / 2;
+  const int64_t tokens = (int64_t)B * T_len;
+  const float sgn = sin_sign >= 0 ? 1.0f : -1.0f;
+  const bool vec_ok = (d2 % NV == 0) && ag_aligned16(q) && ag_aligned16(k) && (qs % NV == 0) && (ks % NV == 0);
+  if (vec_ok) {
+    const size_t smem = (size_t)D * sizeof(float);
+    rope_kernel<T><<<(unsigned)tokens, ROPE_THREADS, smem, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H, k ? HKV : 0,
+                                                                          D, qs, ks, sgn, ctx->d_status);
+    AG_LAUNCHED(ctx, "rope_kernel");
+  } else {
+    rope_scalar_kernel<T><<<(unsigned)tokens, ROPE_THREADS, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H,
+                                                                              k ? HKV : 0, D, qs, ks, sgn);
+    AG_LAUNCHED(ctx, "rope_scalar_kernel");
+  }
+  return AG_OK;
+}
+
+}  // namespace
+
+extern "C" int ag_rope_qk(ag_ctx* ctx, void* q, void* k, const float* cos_tab, const float* sin_tab, int B, int T,
+                          int H, int HKV, int D, int64_t q_token_stride, int64_t k_token_stride, int sin_sign,
+                          int dtype) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (B == 0 || T == 0) return AG_OK;
+  AG_REQUIRE(ctx, q && cos_tab && sin_tab, "ag_rope_qk: null pointer");
+  AG_REQUIRE(ctx, B > 0 && T > 0 && H > 0 && D > 0 && (D % 2) == 0 && (k == nullptr || HKV > 0),
+             "ag_rope_qk: bad shape B=%d T=%d H=%d HKV=%d D=%d", B, T, H, HKV, D);
+  AG_REQUIRE(ctx, dtype == AG_F32 || dtype == AG_BF16, "ag_rope_qk: unknown dtype %d", dtype);
+  AG_REQUIRE(ctx, q_token_stride >= (int64_t)H * D && (k == nullptr || k_token_stride >= (int64_t)HKV * D),
+             "ag_rope_qk: token stride smaller than heads*D");
+  AG_REQUIRE(ctx, (int64_t)B * T < (1ll << 31), "ag_rope_qk: too many tokens");
+  AG_REQUIRE(ctx, D <= 8192, "ag_rope_qk: D=%d too large", D);
+  return dtype == AG_F32
+             ? rope_t<float>(ctx, q, k, cos_tab, sin_tab, B, T, H, HKV, D, q_token_stride, k_token_stride, sin_sign)
+             : rope_t<__nv_bfloat16>(ctx, q, k, cos_tab, sin_tab, B, T, H, HKV, D, q_token_stride, k_token_stride,
+                                     sin_sign);
+}

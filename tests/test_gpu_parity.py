@@ -1,0 +1,501 @@
+"""GPU parity: CUDA kernels (through the backend callables -> C ABI) against the committed
+reference-generated golden vectors and, at larger sizes, against the numpy oracle."""
+import numpy as np
+import pytest
+
+import gpu_util as G
+from conftest import TOL_BF16, TOL_BWD, TOL_FWD, assert_close
+from oracle import fused_layers as O
+
+pytestmark = pytest.mark.gpu
+
+
+# ------------------------------------------------------------------------------ context
+def test_context_reports_b200():
+    ctx, _, _ = G.env()
+    assert ctx.compute_capability[0] == 10
+    assert ctx.sm_count > 0 and ctx.l2_bytes > 0
+
+
+def test_fill_and_copy_roundtrip():
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(0)
+    for n in (1, 3, 4, 5, 1023, 4096 + 7):
+        a = rng.standard_normal(n).astype(np.float32)
+        t = G.up(a)
+        assert np.array_equal(G.down(t), a)
+        be.fill(t, 2.5)
+        assert np.array_equal(G.down(t), np.full(n, 2.5, np.float32))
+        be.fill(t, 0.0)
+        assert np.array_equal(G.down(t), np.zeros(n, np.float32))
+        G.free(t)
+    # odd alignment of a view: fill must not touch neighbours
+    base = G.up(np.zeros(64, np.float32))
+    view = type(base)((13,), np.float32)
+    view.storage = alloc.view(base.storage, 4 * 3, (13,), np.float32)
+    be.fill(view, 7.0)
+    got = G.down(base)
+    exp = np.zeros(64, np.float32)
+    exp[3:16] = 7.0
+    assert np.array_equal(got, exp)
+    # int32 and bf16 storages
+    ti = G.up(np.arange(10, dtype=np.int32), requires_grad=False)
+    be.fill_storage2(ti.storage, 0)
+    assert np.array_equal(G.down(ti), np.zeros(10, np.int32))
+    tb = G.empty((9,), np.uint16)
+    be.fill_storage2(tb.storage, 1.0)
+    assert np.array_equal(G.down(tb), np.ones(9, np.float32))
+    G.free(base, ti, tb)
+
+
+# ------------------------------------------------------------------------------ add + layernorm
+def _ln_case(g, c):
+    return {k: g[f"{c}.{k}"] for k in ("x", "r", "gamma", "beta", "dy", "y", "dx", "dr", "dgamma", "dbeta", "resid",
+                                       "dh_with_resid")}, float(g[f"{c}.eps"])
+
+
+@pytest.mark.parametrize("case", ["probe", "c384", "ragged", "c100", "c1280"])
+def test_add_layernorm_golden_unfused(golden, case):
+    """AddOp node then LayerNormOp node, as the reference graph runs them."""
+    ctx, alloc, be = G.env()
+    d, eps = _ln_case(golden("add_layernorm"), case)
+    x, r = G.up(d["x"], grad=0), G.up(d["r"], grad=0)
+    gamma, beta = G.up(d["gamma"], grad=0), G.up(d["beta"], grad=0)
+    h = G.empty(d["x"].shape, grad=0)
+    y = G.empty(d["x"].shape, grad=d["dy"])
+    add = G.node("AddOp", (x, r), (h,))
+    ln = G.node("LayerNormOp", (h, gamma, beta), (y,), eps=eps, normalized_dim=-1)
+    be.bind_add_forward(add)(add.inputs, add.outputs)
+    G.run_forward(ln)
+    assert_close(G.down(y), d["y"], TOL_FWD, "y")
+    G.run_backward(ln)
+    be.bind_add_backward(add)(add.inputs, add.outputs)
+    assert_close(G.down(x.grad), d["dx"], TOL_BWD, "dx")
+    assert_close(G.down(r.grad), d["dr"], TOL_BWD, "dr")
+    assert_close(G.down(gamma.grad), d["dgamma"], TOL_BWD, "dgamma")
+    assert_close(G.down(beta.grad), d["dbeta"], TOL_BWD, "dbeta")
+    G.check_clean_status()
+    G.free(x, r, gamma, beta, h, y)
+
+
+@pytest.mark.parametrize("case", ["probe", "c384", "ragged", "c100", "c1280"])
+def test_add_layernorm_golden_fused(golden, case):
+    """One fused kernel for add + LayerNorm; backward with a pre-loaded residual gradient
+    (the reference's own test of the fused residual-grad add, debug/check_qwen_kernel.py:471-487)."""
+    ctx, alloc, be = G.env()
+    d, eps = _ln_case(golden("add_layernorm"), case)
+    shape = d["x"].shape
+    rows = int(np.prod(shape[:-1]))
+    x, r = G.up(d["x"]), G.up(d["r"])
+    gamma, beta = G.up(d["gamma"], grad=0), G.up(d["beta"], grad=0)
+    h = G.empty(shape, grad=d["resid"])
+    y = G.empty(shape, grad=d["dy"])
+    mean, rstd = G.empty((rows,)), G.empty((rows,))
+    be.fused_add_layernorm_forward(x, r, gamma, beta, h, y, eps, mean, rstd)
+    h_ref, y_ref, mean_ref, rstd_ref = O.add_layernorm_forward(d["x"], d["r"], d["gamma"], d["beta"], eps)
+    assert np.array_equal(G.down(h), h_ref)
+    assert_close(G.down(y), d["y"], TOL_FWD, "y")
+    assert_close(G.down(mean).reshape(mean_ref.shape), mean_ref, TOL_FWD, "mean")
+    assert_close(G.down(rstd).reshape(rstd_ref.shape), rstd_ref, TOL_FWD, "rstd")
+    ln = G.node("LayerNormOp", (h, gamma, beta), (y,), eps=eps, normalized_dim=-1)
+    G.run_backward(ln)
+    assert_close(G.down(h.grad), d["dh_with_resid"], TOL_BWD, "dh")
+    assert_close(G.down(gamma.grad), d["dgamma"], TOL_BWD, "dgamma")
+    assert_close(G.down(beta.grad), d["dbeta"], TOL_BWD, "dbeta")
+    # accumulation into dgamma/dbeta: a second backward doubles them
+    be.fill(h.grad, 0.0)
+    G.run_backward(ln)
+    assert_close(G.down(gamma.grad), 2 * d["dgamma"], TOL_BWD, "dgamma x2")
+    G.check_clean_status()
+    G.free(x, r, gamma, beta, h, y, mean, rstd)
+
+
+def _cfg1_inputs(N=16384, C=384, seed=1234):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((N, C), dtype=np.float32)
+    r = rng.standard_normal((N, C), dtype=np.float32)
+    gamma = (1 + 0.02 * rng.standard_normal(C)).astype(np.float32)
+    beta = (0.02 * rng.standard_normal(C)).astype(np.float32)
+    dy = rng.standard_normal((N, C), dtype=np.float32)
+    return x, r, gamma, beta, dy
+
+
+@pytest.mark.parametrize("N,C", [(16384, 384), (4096, 1280), (1000, 1536), (777, 2048), (300, 4100)])
+def test_add_layernorm_full_size_vs_oracle(N, C):
+    """Config 1 (16384 x 384, eps 1e-5) and the other row widths of the path."""
+    ctx, alloc, be = G.env()
+    eps = 1e-5
+    x_, r_, g_, b_, dy_ = _cfg1_inputs(N, C)
+    x, r = G.up(x_), G.up(r_)
+    gamma, beta = G.up(g_, grad=0), G.up(b_, grad=0)
+    h, y = G.empty((N, C), grad=0), G.empty((N, C), grad=dy_)
+    mean, rstd = G.empty((N,)), G.empty((N,))
+    be.fused_add_layernorm_forward(x, r, gamma, beta, h, y, eps, mean, rstd)
+    h_ref, y_ref, mean_ref, rstd_ref = O.add_layernorm_forward(x_, r_, g_, b_, eps)
+    assert np.array_equal(G.down(h), h_ref)
+    assert_close(G.down(y), y_ref, TOL_FWD, "y")
+    assert_close(G.down(mean), mean_ref, TOL_FWD, "mean")
+    assert_close(G.down(rstd), rstd_ref, TOL_FWD, "rstd")
+    ln = G.node("LayerNormOp", (h, gamma, beta), (y,), eps=eps, normalized_dim=-1)
+    G.run_backward(ln)
+    z = np.zeros_like(x_)
+    dh_ref, dg_ref, db_ref = O.layernorm_backward(h_ref, g_, dy_, eps, z, np.zeros_like(g_), np.zeros_like(b_))
+    assert_close(G.down(h.grad), dh_ref, TOL_BWD, "dh")
+    assert_close(G.down(gamma.grad), dg_ref, TOL_BWD, "dgamma")
+    assert_close(G.down(beta.grad), db_ref, TOL_BWD, "dbeta")
+    # fixed summation order: a repeat gives identical bits
+    first = G.down(gamma.grad).copy()
+    be.fill(gamma.grad, 0.0)
+    be.fill(beta.grad, 0.0)
+    be.fill(h.grad, 0.0)
+    G.run_backward(ln)
+    assert np.array_equal(G.down(gamma.grad), first)
+    G.check_clean_status()
+    G.free(x, r, gamma, beta, h, y, mean, rstd)
+
+
+# ------------------------------------------------------------------------------ GELU
+@pytest.mark.parametrize("case", ["probe", "ragged", "wide"])
+def test_gelu_golden(golden, case):
+    g = golden("gelu")
+    x_, dy_, pre_ = g[f"{case}.x"], g[f"{case}.dy"], g[f"{case}.pre"]
+    x = G.up(x_, grad=pre_)
+    y = G.empty(x_.shape, grad=dy_)
+    n = G.node("GELUOp", (x,), (y,))
+    G.run_forward(n)
+    assert_close(G.down(y), g[f"{case}.y"], TOL_FWD, "y")
+    G.run_backward(n)
+    assert_close(G.down(x.grad), g[f"{case}.dx"], TOL_BWD, "dx")
+    G.free(x, y)
+
+
+def test_gelu_full_size_vs_oracle():
+    rng = np.random.default_rng(1239)
+    x_ = (2.0 * rng.standard_normal((16384, 1536), dtype=np.float32)).astype(np.float32)
+    x_[0, :8] = [0.0, -0.0, 30.0, -30.0, 1e-20, -1e-20, 9.0, -9.0]
+    dy_ = rng.standard_normal(x_.shape, dtype=np.float32)
+    x = G.up(x_, grad=0)
+    y = G.empty(x_.shape, grad=dy_)
+    n = G.node("GELUOp", (x,), (y,))
+    G.run_forward(n)
+    assert_close(G.down(y), O.gelu_forward(x_), TOL_FWD, "y")
+    G.run_backward(n)
+    assert_close(G.down(x.grad), O.gelu_backward(x_, dy_, np.zeros_like(x_)), TOL_BWD, "dx")
+    G.free(x, y)
+
+
+# ------------------------------------------------------------------------------ RMSNorm / SwiGLU
+@pytest.mark.parametrize("case", ["qwenish", "nogamma", "ragged"])
+def test_rmsnorm_swiglu_golden(golden, case):
+    ctx, alloc, be = G.env()
+    g = golden("rmsnorm_swiglu")
+    x_, eps = g[f"{case}.x"], float(g[f"{case}.eps"])
+    has_gamma = f"{case}.gamma" in g
+    x = G.up(x_, grad=g[f"{case}.resid"])
+    gamma = G.up(g[f"{case}.gamma"], grad=0) if has_gamma else None
+    y = G.empty(x_.shape)
+    inv = G.empty((x_.shape[0],))
+    be.rmsnorm_forward(x, gamma, y, eps, inv)
+    assert_close(G.down(inv), g[f"{case}.inv_rms"], TOL_FWD, "inv_rms")
+    assert_close(G.down(y), g[f"{case}.x_norm"], TOL_FWD, "x_norm")
+    dz = G.up(g[f"{case}.dz"])
+    be.rmsnorm_backward(dz, x, gamma, eps, x.grad, gamma.grad if has_gamma else None, dres=x.grad)
+    assert_close(G.down(x.grad), g[f"{case}.dx_with_resid"], TOL_BWD, "dx")
+    if has_gamma:
+        assert_close(G.down(gamma.grad), g[f"{case}.dgamma"], TOL_BWD, "dgamma")
+    gu = G.up(g[f"{case}.gu"])
+    hidden = G.empty(g[f"{case}.hidden"].shape)
+    be.swiglu_forward(gu, hidden)
+    assert_close(G.down(hidden), g[f"{case}.hidden"], TOL_FWD, "hidden")
+    dh = G.up(g[f"{case}.dhidden"])
+    be.swiglu_backward(gu, dh)
+    assert_close(G.down(gu), g[f"{case}.dgu"], TOL_BWD, "dgu")
+    G.check_clean_status()
+    G.free(x, gamma, y, inv, dz, gu, hidden, dh)
+
+
+def _bf16(a):
+    return O.round_to_bf16(a)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_qwen_path_config3_reduced(dtype):
+    """Config 3 shapes (C 1536, 12/2 heads x 128, I 8960, eps 1e-6, theta 1e6) at a reduced
+    token count, fp32 and bf16 storage, against the fp32 oracle."""
+    ctx, alloc, be = G.env()
+    B, T, C, H, HKV, D, I, eps = 2, 192, 1536, 12, 2, 128, 8960, 1e-6
+    N = B * T
+    rng = np.random.default_rng(1236)
+    bf = dtype == "bf16"
+    tol_f, tol_b = (TOL_BF16, TOL_BF16) if bf else (TOL_FWD, TOL_BWD)
+    st = np.uint16 if bf else np.float32
+
+    def dev(a):
+        if not bf:
+            return G.up(a)
+        t = G.empty(a.shape, np.uint16)
+        be.copy_from_host(t, a)
+        return t
+
+    def prep(a):
+        return _bf16(a) if bf else a
+
+    x_ = prep(rng.standard_normal((N, C), dtype=np.float32))
+    gamma_ = (1 + 0.02 * rng.standard_normal(C)).astype(np.float32)
+    dz_ = prep(rng.standard_normal((N, C), dtype=np.float32))
+    resid_ = prep(rng.standard_normal((N, C), dtype=np.float32))
+    # RMSNorm
+    x, dz, dxt = dev(x_), dev(dz_), dev(resid_)
+    gamma = G.up(gamma_, grad=0)
+    y = G.empty((N, C), st)
+    inv = G.empty((N,))
+    be.rmsnorm_forward(x, gamma, y, eps, inv)
+    z_ref, inv_ref = O.rmsnorm_forward(x_, gamma_, eps)
+    assert_close(G.down(inv), inv_ref, TOL_FWD, "inv_rms")
+    assert_close(G.down(y), z_ref, tol_f, "rmsnorm y")
+    be.rmsnorm_backward(dz, x, gamma, eps, dxt, gamma.grad, dres=dxt)
+    dx_ref, dg_ref = O.rmsnorm_backward(x_, gamma_, dz_, eps, resid_, np.zeros_like(gamma_))
+    assert_close(G.down(dxt), dx_ref, tol_b, "rmsnorm dx")
+    assert_close(G.down(gamma.grad), dg_ref, TOL_BWD if not bf else TOL_BF16, "rmsnorm dgamma")
+    G.free(x, dz, dxt, gamma, y, inv)
+    # RoPE, rope_sign=+1 forward then its transpose as backward
+    q_ = prep(rng.standard_normal((B, T, H, D), dtype=np.float32))
+    k_ = prep(rng.standard_normal((B, T, HKV, D), dtype=np.float32))
+    cos_, sin_ = O.rope_tables(T, D, 1e6)
+    q, k, cos, sin = dev(q_), dev(k_), G.up(cos_), G.up(sin_)
+    be.rope_qk(q, k, cos, sin, sin_sign=+1)
+    q_ref, k_ref = O.rope_apply(q_, cos_, sin_, +1), O.rope_apply(k_, cos_, sin_, +1)
+    assert_close(G.down(q), q_ref, tol_f, "rope q")
+    assert_close(G.down(k), k_ref, tol_f, "rope k")
+    be.rope_qk(q, k, cos, sin, sin_sign=-1)
+    assert_close(G.down(q), q_, 2 * tol_f, "rope q roundtrip")
+    G.free(q, k, cos, sin)
+    # SwiGLU
+    gu_ = prep(rng.standard_normal((N, 2 * I), dtype=np.float32))
+    dh_ = prep(rng.standard_normal((N, I), dtype=np.float32))
+    gu, dh = dev(gu_), dev(dh_)
+    hidden = G.empty((N, I), st)
+    be.swiglu_forward(gu, hidden)
+    assert_close(G.down(hidden), O.swiglu_forward(gu_), tol_f, "swiglu hidden")
+    be.swiglu_backward(gu, dh)
+    assert_close(G.down(gu), O.swiglu_backward(gu_, dh_), tol_b, "swiglu dgu")
+    G.check_clean_status()
+    G.free(gu, dh, hidden)
+
+
+# ------------------------------------------------------------------------------ RoPE
+@pytest.mark.parametrize("case", ["qwen", "gpt", "tiny"])
+def test_rope_golden(golden, case):
+    ctx, alloc, be = G.env()
+    g = golden("rope")
+    q_, k_, cos_, sin_ = (g[f"{case}.{n}"] for n in ("q", "k", "cos", "sin"))
+    for sign, tag in ((+1, "pos"), (-1, "neg")):
+        q, k, cos, sin = G.up(q_), G.up(k_), G.up(cos_), G.up(sin_)
+        be.rope_qk(q, k, cos, sin, sin_sign=sign)
+        assert_close(G.down(q), g[f"{case}.q_{tag}"], TOL_FWD, f"q {tag}")
+        assert_close(G.down(k), g[f"{case}.k_{tag}"], TOL_FWD, f"k {tag}")
+        G.free(q, k, cos, sin)
+    # q only
+    q, cos, sin = G.up(q_), G.up(cos_), G.up(sin_)
+    be.rope_qk(q, None, cos, sin, sin_sign=+1)
+    assert_close(G.down(q), g[f"{case}.q_pos"], TOL_FWD, "q only")
+    G.check_clean_status()
+    G.free(q, cos, sin)
+
+
+# ------------------------------------------------------------------------------ gather / scatter-add
+@pytest.mark.parametrize("case", ["small", "collide", "wide"])
+def test_gather_golden(golden, case):
+    g = golden("gather")
+    ids_, table_, dout_ = g[f"{case}.ids"], g[f"{case}.table"], g[f"{case}.dout"]
+    ids = G.up(ids_, requires_grad=False)
+    table = G.up(table_, grad=0)
+    out = G.empty(dout_.shape, grad=dout_)
+    n = G.node("GatherOp", (ids, table), (out,))
+    G.run_forward(n)
+    assert np.array_equal(G.down(out), g[f"{case}.out"])  # bit-exact
+    G.run_backward(n)
+    got = G.down(table.grad)
+    assert_close(got, g[f"{case}.dtable"], TOL_BWD, "dtable")
+    # rows nobody indexed stay exactly zero
+    untouched = np.setdiff1d(np.arange(table_.shape[0]), ids_.ravel())
+    assert not got[untouched].any()
+    G.check_clean_status()
+    G.free(ids, table, out)
+
+
+def _zipf_ids(rng, V, n, s=1.1):
+    p = 1.0 / np.arange(1, V + 1) ** s
+    p /= p.sum()
+    return rng.choice(V, size=n, p=p).astype(np.int32)
+
+
+@pytest.mark.parametrize("V,C,n", [(151936, 1536, 65536), (5000, 100, 4099), (32768, 1280, 32768)])
+def test_gather_scatter_full_size(V, C, n):
+    """Config 4: 65536 Zipf(1.1) ids over a 151936 x 1536 table; forward bit-exact, backward
+    within tolerance of np.add.at, bit-reproducible, and bit-exact for rows whose occurrences
+    fall inside one summation group."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(1237)
+    ids_ = _zipf_ids(rng, V, n).reshape(1, n) if V != 32768 else rng.integers(0, V, size=(1, n)).astype(np.int32)
+    table_ = (0.02 * rng.standard_normal((V, C), dtype=np.float32)).astype(np.float32)
+    dout_ = rng.standard_normal((1, n, C), dtype=np.float32)
+    ids = G.up(ids_, requires_grad=False)
+    table = G.up(table_, grad=0)
+    out = G.empty(dout_.shape, grad=dout_)
+    node = G.node("GatherOp", (ids, table), (out,))
+    G.run_forward(node)
+    assert np.array_equal(G.down(out), O.gather_forward(ids_, table_))
+    G.run_backward(node)
+    got = G.down(table.grad)
+    ref = O.gather_backward(ids_, dout_, np.zeros_like(table_))
+    assert_close(got, ref, TOL_BWD, "dtable")
+    counts = np.bincount(ids_.ravel(), minlength=V)
+    assert not got[counts == 0].any()
+    singles = counts == 1
+    assert np.array_equal(got[singles], ref[singles])
+    be.fill(table.grad, 0.0)
+    G.run_backward(node)
+    assert np.array_equal(G.down(table.grad), got)  # deterministic
+    # accumulate on top of an existing gradient
+    G.run_backward(node)
+    assert_close(G.down(table.grad), 2 * ref, TOL_BWD, "dtable x2")
+    G.check_clean_status()
+    G.free(ids, table, out)
+
+
+def test_gather_bad_index_sets_status_not_fault():
+    ctx, alloc, be = G.env()
+    table_ = np.arange(12, dtype=np.float32).reshape(3, 4)
+    ids = G.up(np.array([[0, 5, -1, 2]], np.int32), requires_grad=False)
+    table = G.up(table_, grad=0)
+    out = G.empty((1, 4, 4), grad=np.ones((1, 4, 4), np.float32))
+    n = G.node("GatherOp", (ids, table), (out,))
+    G.run_forward(n)
+    got = G.down(out)
+    assert np.array_equal(got[0, 0], table_[0]) and np.array_equal(got[0, 3], table_[2])
+    assert not got[0, 1].any() and not got[0, 2].any()
+    assert ctx.status() & 1
+    G.run_backward(n)
+    assert ctx.status() & 1
+    exp = np.zeros_like(table_)
+    exp[0] = 1
+    exp[2] = 1
+    assert np.array_equal(G.down(table.grad), exp)
+    assert ctx.status() == 0
+    G.free(ids, table, out)
+
+
+# ------------------------------------------------------------------------------ fused linear + CE
+def _run_flce(be, X_, W_, Y_, precision, ignore_mode, reduction=0, chunk=4096, dloss=1.0):
+    import autograd_b200 as ag
+    be.ce_precision, be.ce_ignore_mode, be.ce_reduction, be.ce_vocab_chunk = precision, ignore_mode, reduction, chunk
+    x = G.up(X_, grad=0)
+    w = G.up(W_, grad=0)
+    y = G.up(Y_, requires_grad=False)
+    loss = G.empty((1,), grad=np.array([dloss], np.float32))
+    n = G.node("FusedLinearCrossEntropyOp", (x, w, y), (loss,), ignore_index=-1)
+    G.run_forward(n)
+    G.run_backward(n)
+    res = float(G.down(loss)[0]), G.down(x.grad), G.down(w.grad)
+    G.free(x, w, y, loss)
+    be.ce_precision, be.ce_ignore_mode, be.ce_reduction, be.ce_vocab_chunk = ag.AG_CE_3XTF32, 0, 0, 4096
+    return res
+
+
+@pytest.mark.parametrize("case", ["small", "ragged", "multi_chunk"])
+@pytest.mark.parametrize("precision", [0, 1])
+def test_flce_golden(golden, case, precision):
+    ctx, alloc, be = G.env()
+    g = golden("flce")
+    X_, W_, Y_ = g[f"{case}.X"], g[f"{case}.W"], g[f"{case}.Y"]
+    N = Y_.size
+    # (1) verbatim reference semantics: ignored rows still contribute softmax*scale
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, precision, ignore_mode=1, chunk=128)
+    assert abs(loss - float(g[f"{case}.loss"][0])) <= TOL_FWD * abs(loss)
+    assert_close(dX, g[f"{case}.dX"], TOL_BWD, "dX compat")
+    assert_close(dW, g[f"{case}.dW"], TOL_BWD, "dW compat")
+    # (2) masked default == the reference run on the valid rows, rescaled by N_valid/N
+    keep = g[f"{case}.valid_rows"]
+    f = len(keep) / N
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, precision, ignore_mode=0, chunk=128)
+    assert abs(loss - f * float(g[f"{case}.loss_valid_only"][0])) <= TOL_FWD * abs(loss)
+    exp_dX = np.zeros((N, X_.shape[-1]), np.float32)
+    exp_dX[keep] = f * g[f"{case}.dX_valid_only"].reshape(len(keep), -1)
+    assert_close(dX.reshape(exp_dX.shape), exp_dX, TOL_BWD, "dX masked")
+    assert_close(dW, f * g[f"{case}.dW_valid_only"], TOL_BWD, "dW masked")
+    assert not dX.reshape(exp_dX.shape)[np.setdiff1d(np.arange(N), keep)].any()  # ignore handling is exact
+    # (3) mean over valid rows
+    loss_v, dXv, _ = _run_flce(be, X_, W_, Y_, precision, ignore_mode=0, reduction=1, chunk=128)
+    assert abs(loss_v - float(g[f"{case}.loss_valid_only"][0])) <= TOL_FWD * abs(loss_v)
+    G.check_clean_status()
+
+
+@pytest.mark.parametrize("N,C,V,precision", [(2048, 384, 8192, 0), (2048, 384, 8192, 1), (1024, 1280, 8192, 1)])
+def test_flce_mid_size_vs_oracle(N, C, V, precision):
+    """Config 2 shapes at a reduced token / vocab count, vocab chunk 4096 (two panels)."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(1235)
+    X_ = (rng.standard_normal((1, N, C)) / np.sqrt(C)).astype(np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C))).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(1, N)).astype(np.int32)
+    Y_[rng.random((1, N)) < 0.05] = -1
+    ref = O.flce_masked(X_[0], W_, Y_[0], dloss=0.5)
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, precision, ignore_mode=0, chunk=4096, dloss=0.5)
+    assert abs(loss - float(ref["loss"])) <= TOL_FWD * abs(loss)
+    assert_close(dX[0], ref["dX"], TOL_BWD, "dX")
+    assert_close(dW, ref["dW"], TOL_BWD, "dW")
+    G.check_clean_status()
+
+
+@pytest.mark.parametrize("case", ["plain", "row_scaled"])
+def test_rmsnorm_flce_golden(golden, case):
+    ctx, alloc, be = G.env()
+    g = golden("rmsnorm_flce")
+    be.ce_precision, be.ce_vocab_chunk = 0, 64
+    x = G.up(g[f"{case}.X"], grad=0)
+    w = G.up(g[f"{case}.W"], grad=0)
+    gam = G.up(g[f"{case}.G"], grad=0)
+    y = G.up(g[f"{case}.Y"], requires_grad=False)
+    inputs = [x, w, gam, y]
+    if f"{case}.row_scale" in g:
+        inputs.append(G.up(g[f"{case}.row_scale"], requires_grad=False))
+    loss = G.empty((1,), grad=np.array([1.0], np.float32))
+    n = G.node("FusedRMSNormLinearCrossEntropyOp", inputs, (loss,), eps=float(g[f"{case}.eps"]))
+    G.run_forward(n)
+    G.run_backward(n)
+    got = float(G.down(loss)[0])
+    assert abs(got - float(g[f"{case}.loss"][0])) <= TOL_FWD * abs(got)
+    assert_close(G.down(x.grad), g[f"{case}.dX"], TOL_BWD, "dX")
+    assert_close(G.down(w.grad), g[f"{case}.dW"], TOL_BWD, "dW")
+    assert_close(G.down(gam.grad), g[f"{case}.dG"], TOL_BWD, "dG")
+    be.ce_precision, be.ce_vocab_chunk = 1, 4096
+    G.check_clean_status()
+    G.free(*inputs, loss)
+
+
+# ------------------------------------------------------------------------------ AdamW
+def test_adamw_golden(golden):
+    ctx, alloc, be = G.env()
+    g = golden("adamw_bf16")
+    lr, lr_t, b1, b2, eps, wd = (float(v) for v in g["hp"])
+    p, gr, m, v = G.up(g["p"]), G.up(g["g"]), G.up(g["m"]), G.up(g["v"])
+    be.adamw_step(p.storage, gr.storage, m.storage, v.storage, None, lr, lr_t, b1, b2, eps, wd, grad_scale=1.0)
+    assert_close(G.down(p), g["p_out"], TOL_FWD, "p")
+    assert_close(G.down(m), g["m_out"], TOL_FWD, "m")
+    assert_close(G.down(v), g["v_out"], TOL_FWD, "v")
+    G.free(p, gr, m, v)
+
+
+def test_errors_are_exceptions_not_aborts():
+    import autograd_b200 as ag
+    ctx, alloc, be = G.env()
+    x = G.up(np.zeros((4, 8), np.float32))
+    with pytest.raises(ag.AgError):  # workspace too small
+        ctx.layernorm_backward(x.storage.ptr.address, x.storage.ptr.address, x.storage.ptr.address, 0,
+                               x.storage.ptr.address, x.storage.ptr.address, x.storage.ptr.address,
+                               x.storage.ptr.address, 16, 4, 8, 1e-5)
+    with pytest.raises(ag.AgError):  # null input
+        ctx.gelu_forward(0, x.storage.ptr.address, 32)
+    ctx.synchronize()
+    G.free(x)
