@@ -49,6 +49,10 @@ SIGNATURES = {
     "ag_launch_count": (_i64, [_ctx]),
     "ag_pass_begin_profiled": (_int, [_ctx]),
     "ag_pass_end_profiled": (_int, [_ctx, C.POINTER(_f32)]),
+    "ag_event_record": (_int, [_ctx, _int]),
+    "ag_event_elapsed": (_int, [_ctx, _int, _int, C.POINTER(_f32)]),
+    "ag_alloc_host": (_int, [_ctx, _sz, C.POINTER(_ptr)]),
+    "ag_free_host": (_int, [_ctx, _ptr]),
     "ag_fill_f32": (_int, [_ctx, _ptr, _f32, _i64]),
     "ag_fill_pattern": (_int, [_ctx, _ptr, C.c_uint32, _int, _i64]),
     "ag_add_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _i64]),

@@ -40,12 +40,13 @@ def _ag_dtype(dtype):
 
 def f32_to_bf16_bits(a):
     """Round-to-nearest-even fp32 -> bf16 bit patterns, NaN kept quiet (utils.py:20-27)."""
-    bits = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
-    rounded = (bits + 0x7FFF + ((bits >> 16) & 1)) >> 16
-    special = (bits & 0x7F800000) == 0x7F800000
-    nan = special & ((bits & 0x007FFFFF) != 0)
-    special_bits = (bits >> 16) | np.where(nan, 0x0040, 0)
-    return np.where(special, special_bits, rounded).astype(np.uint16)
+    u = np.uint64
+    bits = np.atleast_1d(np.ascontiguousarray(a, dtype=np.float32)).view(np.uint32).astype(u)
+    rounded = (bits + u(0x7FFF) + ((bits >> u(16)) & u(1))) >> u(16)
+    special = (bits & u(0x7F800000)) == u(0x7F800000)
+    nan = special & ((bits & u(0x007FFFFF)) != u(0))
+    special_bits = (bits >> u(16)) | np.where(nan, u(0x0040), u(0))
+    return np.where(special, special_bits, rounded).astype(np.uint16).reshape(np.shape(a))
 
 
 def bf16_bits_to_f32(b):

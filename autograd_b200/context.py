@@ -98,6 +98,22 @@ class CudaContext:
         self._check(lib.ag_pass_end_profiled(self._h, C.byref(ms)))
         return ms.value
 
+    def event_record(self, index: int):
+        self._check(lib.ag_event_record(self._h, int(index)))
+
+    def event_elapsed_ms(self, start_index: int, end_index: int) -> float:
+        ms = C.c_float()
+        self._check(lib.ag_event_elapsed(self._h, int(start_index), int(end_index), C.byref(ms)))
+        return ms.value
+
+    def alloc_host(self, nbytes: int) -> int:
+        out = C.c_void_p()
+        self._check(lib.ag_alloc_host(self._h, int(nbytes), C.byref(out)))
+        return int(out.value or 0)
+
+    def free_host(self, addr: int):
+        self._check(lib.ag_free_host(self._h, _p(addr)))
+
     # ------------------------------------------------------------------ kernels
     def fill_f32(self, dst, value, n):
         self._check(lib.ag_fill_f32(self._h, _p(dst), float(value), int(n)))

@@ -20,6 +20,8 @@ struct ag_ctx {
   int* d_status;  // device status word (AG_STATUS_* bits), set by kernels with atomicOr
   int* h_status;  // pinned mirror
   cudaEvent_t ev_begin, ev_end;
+  cudaEvent_t* ev_pool;  // ag_event_record / ag_event_elapsed
+  int ev_pool_size;
   int64_t launches;
   char err[512];
 };

@@ -3,6 +3,7 @@
 // every kernel of this library is enqueued on that stream in call order.
 #include "ag_common.cuh"
 
+#include <stdlib.h>
 #include <string.h>
 
 static thread_local char g_create_err[512] = "";
@@ -72,6 +73,8 @@ extern "C" int ag_ctx_destroy(ag_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   cudaEventDestroy(ctx->ev_begin);
   cudaEventDestroy(ctx->ev_end);
+  for (int i = 0; i < ctx->ev_pool_size; ++i) cudaEventDestroy(ctx->ev_pool[i]);
+  free(ctx->ev_pool);
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
@@ -168,6 +171,51 @@ extern "C" int ag_pass_end_profiled(ag_ctx* ctx, float* ms) {
   AG_CUDA(ctx, cudaEventRecord(ctx->ev_end, ctx->stream));
   AG_CUDA(ctx, cudaEventSynchronize(ctx->ev_end));
   AG_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_begin, ctx->ev_end));
+  return AG_OK;
+}
+
+extern "C" int ag_event_record(ag_ctx* ctx, int index) {
+  if (!ctx) return AG_ERR_INVALID;
+  AG_REQUIRE(ctx, index >= 0 && index < (1 << 22), "ag_event_record: bad index %d", index);
+  if (index >= ctx->ev_pool_size) {
+    int n = ctx->ev_pool_size ? ctx->ev_pool_size : 256;
+    while (n <= index) n *= 2;
+    cudaEvent_t* p = (cudaEvent_t*)realloc(ctx->ev_pool, sizeof(cudaEvent_t) * n);
+    if (!p) AG_FAIL(ctx, AG_ERR_INVALID, "ag_event_record: out of host memory");
+    ctx->ev_pool = p;
+    for (int i = ctx->ev_pool_size; i < n; ++i) {
+      cudaError_t e = cudaEventCreate(&ctx->ev_pool[i]);
+      if (e != cudaSuccess) {
+        ctx->ev_pool_size = i;
+        AG_FAIL(ctx, AG_ERR_CUDA, "cudaEventCreate failed: %s", cudaGetErrorString(e));
+      }
+    }
+    ctx->ev_pool_size = n;
+  }
+  AG_CUDA(ctx, cudaEventRecord(ctx->ev_pool[index], ctx->stream));
+  return AG_OK;
+}
+
+extern "C" int ag_event_elapsed(ag_ctx* ctx, int start_index, int end_index, float* ms) {
+  if (!ctx || !ms) return AG_ERR_INVALID;
+  AG_REQUIRE(ctx, start_index >= 0 && end_index >= 0 && start_index < ctx->ev_pool_size && end_index < ctx->ev_pool_size,
+             "ag_event_elapsed: event not recorded");
+  AG_CUDA(ctx, cudaEventSynchronize(ctx->ev_pool[end_index]));
+  AG_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_pool[start_index], ctx->ev_pool[end_index]));
+  return AG_OK;
+}
+
+extern "C" int ag_alloc_host(ag_ctx* ctx, size_t bytes, void** out) {
+  if (!ctx || !out) return AG_ERR_INVALID;
+  *out = nullptr;
+  if (bytes == 0) return AG_OK;
+  AG_CUDA(ctx, cudaHostAlloc(out, bytes, cudaHostAllocDefault));
+  return AG_OK;
+}
+
+extern "C" int ag_free_host(ag_ctx* ctx, void* ptr) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (ptr) AG_CUDA(ctx, cudaFreeHost(ptr));
   return AG_OK;
 }
 

@@ -1,0 +1,406 @@
+"""Benchmark of the fused-layer step (data-parallel over token rows).
+
+    python bench.py --gpus N --steps K --warmup W          # this backend, one rank per GPU
+    python bench.py --impl reference ...                   # the CPU path on the host cores
+
+Workload (N=1 and per GPU at N>1): the full fused-layer step of a random-init depth-20 GPT
+(n_embd 1280, 10 heads x 128, seq 2048, vocab 32768, 16 sequences per GPU, LayerNorm + GELU
+MLP + RoPE + tied embedding + fused linear+CE), synthetic seeded data.  One "step" = every fused
+layer kernel of a training step, forward and backward, plus the gradient allreduce at N>1.
+
+Prints ONE JSON line on rank 0.  `value` is tokens/s of the whole job with inputs resident in
+HBM; `e2e` is the same metric with the step's token ids and targets copied from pinned host
+memory and the loss read back inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fused_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--ce-precision", default="3xtf32", choices=["fp32", "3xtf32", "bf16"])
+    # reduced shapes for profiler captures and tests; the defaults are the benchmark workload
+    ap.add_argument("--layers", type=int, default=20)
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--vocab", type=int, default=32768)
+    ap.add_argument("--n-embd", type=int, default=1280)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=2048)
+    ap.add_argument("--cpu-sample-layers", type=int, default=2)
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def workload_name(a):
+    return (f"gpt_fused_layer_step depth{a.layers} n_embd{a.n_embd} heads{a.n_embd // 128}x128 seq{a.seq_len} "
+            f"vocab{a.vocab} batch{a.batch}/gpu")
+
+
+# --------------------------------------------------------------------------------------
+# CPU path: the numpy restatement of the reference's CPU backend, on a bounded sample
+# --------------------------------------------------------------------------------------
+def cpu_sample_step(a, tokens, layers, seed=1238):
+    """One fused-layer step on the host for `tokens` token rows and `layers` of the a.layers
+    layers; the per-layer time is scaled to the full depth.  Returns (seconds_full_depth,
+    description)."""
+    from oracle import fused_layers as O
+    C, V, I, H, D = a.n_embd, a.vocab, 4 * a.n_embd, a.n_embd // 128, 128
+    T = min(a.seq_len, tokens)
+    B = max(tokens // T, 1)
+    n = B * T
+    rng = np.random.default_rng(seed)
+    f = np.float32
+    ids = rng.integers(0, V, size=(B, T)).astype(np.int32)
+    tg = rng.integers(0, V, size=n).astype(np.int32)
+    table = (0.02 * rng.standard_normal((V, C), dtype=f)).astype(f)
+    gam = (1 + 0.02 * rng.standard_normal(C)).astype(f)
+    bet = (0.02 * rng.standard_normal(C)).astype(f)
+    r = rng.standard_normal((n, C), dtype=f)
+    u = rng.standard_normal((n, I), dtype=f)
+    q = rng.standard_normal((B, T, H, D), dtype=f)
+    kk = rng.standard_normal((B, T, H, D), dtype=f)
+    dy = rng.standard_normal((n, C), dtype=f)
+    dg = rng.standard_normal((n, I), dtype=f)
+    cos, sin = O.rope_tables(T, D, 1e5)
+    zc = np.zeros(C, f)
+
+    t0 = time.perf_counter()
+    x = O.gather_forward(ids, table).reshape(n, C)
+    t_head = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    hs = []
+    for _ in range(layers):
+        h1, y1, _, _ = O.add_layernorm_forward(x, r, gam, bet, 1e-5)
+        O.rope_apply(q, cos, sin, -1); O.rope_apply(kk, cos, sin, -1)
+        h2, y2, _, _ = O.add_layernorm_forward(h1, r, gam, bet, 1e-5)
+        O.gelu_forward(u)
+        hs.append((h1, h2))
+        x = h2
+    t_layers = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    hf, yf, _, _ = O.add_layernorm_forward(x, r, gam, bet, 1e-5)
+    res = O.flce_masked(yf, table, tg)                      # forward and backward of the head
+    dh, _, _ = O.layernorm_backward(hf, gam, res["dX"], 1e-5, np.zeros_like(hf), zc, zc)
+    t_head += time.perf_counter() - t0
+    t0 = time.perf_counter()
+    for h1, h2 in reversed(hs):
+        O.gelu_backward(u, dg, np.zeros_like(u))
+        dh, _, _ = O.layernorm_backward(h2, gam, dy, 1e-5, dh, zc, zc)
+        O.rope_apply(q, cos, sin, +1); O.rope_apply(kk, cos, sin, +1)
+        dh, _, _ = O.layernorm_backward(h1, gam, dy, 1e-5, dh, zc, zc)
+    t_layers += time.perf_counter() - t0
+    t0 = time.perf_counter()
+    O.gather_backward(ids, dh.reshape(B, T, C), res["dW"])
+    t_head += time.perf_counter() - t0
+    total = t_head + t_layers * (a.layers / layers)
+    desc = (f"{n} token rows, {layers} of {a.layers} layers timed and scaled x{a.layers / layers:g}, head "
+            f"(gather, final LN, fused linear+CE fwd+bwd, scatter-add) at full vocab {V}")
+    return n, total, desc
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    for _ in range(a.warmup):
+        cpu_sample_step(a, a.cpu_sample_tokens, a.cpu_sample_layers)
+    times = []
+    n = a.cpu_sample_tokens
+    for _ in range(a.steps):
+        n, t, desc = cpu_sample_step(a, a.cpu_sample_tokens, a.cpu_sample_layers)
+        times.append(t)
+    ms = 1e3 * sum(times) / len(times)
+    value = n / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "sample": desc},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": desc + "; numpy restatement of the reference CPU backend (oracle/), numpy "
+                                   f"{np.__version__}, BLAS threads unrestricted"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.gpu_index = gpu_index
+        self.path = f"/tmp/ag_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()      # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for ln in f:
+                    p = [x.strip() for x in ln.split(",")]
+                    if len(p) < 9:
+                        continue
+                    try:
+                        sm.append(float(p[1])); mx.append(float(p[2]))
+                    except ValueError:
+                        continue
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                       p[5:9]):
+                        if v.lower().startswith("active"):
+                            reasons.add(name)
+            os.remove(self.path)
+        except Exception:
+            pass
+        # the busiest half of the samples is "under load"
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+def run_b200(a):
+    import torch
+    import torch.distributed as dist
+
+    import autograd_b200 as ag
+    from autograd_b200 import dp
+    from autograd_b200.step import FusedLayerStep, StepConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx, alloc, be = ag.create(local, stream.cuda_stream)
+    peaks = load_peaks()
+
+    prec = {"fp32": ag.AG_CE_FP32, "3xtf32": ag.AG_CE_3XTF32, "bf16": ag.AG_CE_BF16}[a.ce_precision]
+    cfg = StepConfig(n_layer=a.layers, n_embd=a.n_embd, n_head=a.n_embd // 128, head_dim=128, seq_len=a.seq_len,
+                     vocab=a.vocab, batch=a.batch, ce_precision=prec)
+
+    def fill_normal(addr, n, seed, std):
+        g = torch.Generator(device=f"cuda:{local}")
+        g.manual_seed(seed * 1000 + rank)
+        dp.as_torch(addr, n, local).normal_(0.0, std, generator=g)
+
+    step = FusedLayerStep(ctx, alloc, be, cfg, seed=1238 + rank, fill_normal=fill_normal)
+    Nn = cfg.tokens
+    buckets = [dp.as_torch(addr, n, local) for addr, n in step.grad_buckets()]
+    reducer = dp.GradAllReducer(buckets) if world > 1 else None
+    loss_t = dp.as_torch(step.loss, 1, local)
+    if reducer is not None:
+        ctx.fill_f32(step.dloss, reducer.grad_scale, 1)
+
+    # pinned host batches (distinct per step so that nothing is cached across steps)
+    n_batches = max(a.steps, 1)
+    host = ctx.alloc_host(n_batches * 2 * Nn * 4)
+    host_np = np.ctypeslib.as_array(ctypes.cast(host, ctypes.POINTER(ctypes.c_int32)), shape=(n_batches, 2, Nn))
+    rng = np.random.default_rng(4242 + rank)
+    host_np[:] = rng.integers(0, cfg.vocab, size=host_np.shape, dtype=np.int32)
+
+    def load(i):
+        b = i % n_batches
+        step.load_batch(host + (b * 2) * Nn * 4, host + (b * 2 + 1) * Nn * 4)
+
+    def one_step(i, e2e):
+        if e2e:
+            load(i)
+        step.step()
+        if reducer is not None:
+            reducer.reduce()
+            reducer.mean_loss(loss_t)
+        if e2e:
+            return step.read_loss()
+        return None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    load(0)
+    for i in range(a.warmup):
+        one_step(i, e2e=True)
+    ctx.check_status()
+
+    EV0, EV1 = (1 << 20), (1 << 20) + 1   # event indices outside the family timer's range
+    sampler = ClockSampler(local)
+
+    # ---- device-resident timing with per-family events inside the timed region
+    step.timer.reset()
+    step.timer.enabled = True
+    barrier()
+    sampler.start()
+    launches0 = ctx.launch_count
+    ctx.event_record(EV0)
+    for i in range(a.steps):
+        one_step(i, e2e=False)
+    ctx.event_record(EV1)
+    barrier()
+    ms_dev = ctx.event_elapsed_ms(EV0, EV1)
+    launches = ctx.launch_count - launches0
+    step.timer.enabled = False
+    fam = step.timer.totals_ms()
+
+    # ---- end-to-end timing: h2d of ids/targets and d2h of the loss every step
+    barrier()
+    ctx.event_record(EV0)
+    t_wall = time.perf_counter()
+    last_loss = None
+    for i in range(a.steps):
+        last_loss = one_step(i, e2e=True)
+    ctx.event_record(EV1)
+    barrier()
+    t_wall = time.perf_counter() - t_wall
+    ms_e2e = max(ctx.event_elapsed_ms(EV0, EV1), 1e3 * t_wall)
+    clocks = sampler.stop()
+    ctx.check_status()
+
+    if world > 1:
+        t = torch.tensor([ms_dev, ms_e2e], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        tokens = Nn * world
+        ms_step = ms_dev / a.steps
+        value = tokens / (ms_step / 1e3)
+        e2e_value = tokens / (ms_e2e / a.steps / 1e3)
+        alg = step.algorithmic_bytes()
+        useful, executed = step.flce_flops()
+        kernels = {}
+        for name, (count, total_ms) in sorted(fam.items()):
+            per_step_ms = total_ms / a.steps
+            ent = {"launch_groups_per_step": count // a.steps, "ms_per_step": round(per_step_ms, 4)}
+            if name in alg:
+                gbs = alg[name] / (per_step_ms / 1e3) / 1e9
+                ent.update({"bound": "hbm", "achieved_gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4)})
+            elif name in ("flce_fwd", "flce_bwd"):
+                share = 1.0 if name == "flce_fwd" else 3.0
+                u = useful * (share / 4.0) if name == "flce_bwd" else useful / 3.0
+                tf = u / (per_step_ms / 1e3) / 1e12
+                ent.update({"bound": "tensor", "useful_tflops": round(tf, 2)})
+            kernels[name] = ent
+        # dominant kernel family by time
+        dom = max(fam.items(), key=lambda kv: kv[1][1])[0] if fam else None
+        if dom in ("flce_fwd", "flce_bwd"):
+            t_flce = (fam.get("flce_fwd", (0, 0))[1] + fam.get("flce_bwd", (0, 0))[1]) / a.steps / 1e3
+            ach = useful / t_flce / 1e12
+            peak = peaks["bf16_tflops_sustained"]
+            roofline = {"bound": "tensor", "kernel": "fused_linear_cross_entropy (fwd+bwd panels)",
+                        "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
+                        "traffic": None, "peak_source": peaks["source"] + " bf16 sustained; TF32 issue rate is half",
+                        "executed_tflops": round(executed / t_flce / 1e12, 2), "precision": a.ce_precision}
+        elif dom is not None and dom in alg:
+            per = fam[dom][1] / a.steps / 1e3
+            ach = alg[dom] / per / 1e9
+            roofline = {"bound": "hbm", "kernel": dom, "achieved": round(ach, 1), "peak": peaks["hbm_gbs"],
+                        "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": None,
+                        "peak_source": peaks["source"]}
+        else:
+            roofline = None
+        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+        if roofline is not None and os.path.exists(traffic_path):
+            with open(traffic_path) as f:
+                roofline["traffic"] = json.load(f).get(roofline["kernel"])
+
+        cpu = None
+        if world == 1 and not a.no_cpu_baseline:
+            n, t, desc = cpu_sample_step(a, a.cpu_sample_tokens, a.cpu_sample_layers)
+            cpu = {"value": n / t, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                   "sample": desc + f"; numpy {np.__version__}, one run"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32" if a.ce_precision != "bf16" else "f32 (bf16 tensor-core operands in the CE GEMMs)",
+            "data": "synthetic",
+            "config": {"workload": workload_name(a), "tokens_per_gpu": Nn, "ce_precision": a.ce_precision,
+                       "vocab_chunk": cfg.ce_vocab_chunk, "parallelism": f"dp{world} token-row sharded",
+                       "l2": "every streamed buffer is larger than the L2 cache; no flush needed",
+                       "device_bytes": step.device_bytes,
+                       "allreduce_bytes_per_step": reducer.bytes_per_step if reducer else 0},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * Nn * 4, "d2h_bytes_per_step": 4,
+                    "ms_per_step": ms_e2e / a.steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": roofline,
+            "kernels": kernels,
+            "cpu_baseline": cpu,
+            "loss": last_loss,
+        }
+        print(json.dumps(line), flush=True)
+    step.close()
+    ctx.free_host(host)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_b200(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -73,6 +73,15 @@ int64_t ag_launch_count(const ag_ctx* ctx);
  * bracket on the context stream; end returns the elapsed milliseconds after syncing. */
 int ag_pass_begin_profiled(ag_ctx* ctx);
 int ag_pass_end_profiled(ag_ctx* ctx, float* ms);
+/* Per-dispatch timing (replaces the per-dispatch proxies of debug/timing_ops_v2.py:479-543):
+ * a pool of CUDA events owned by the context.  ag_event_record enqueues event `index` on the
+ * context stream (the pool grows on demand); ag_event_elapsed waits for both events and
+ * returns the milliseconds between them. */
+int ag_event_record(ag_ctx* ctx, int index);
+int ag_event_elapsed(ag_ctx* ctx, int start_index, int end_index, float* ms);
+/* Pinned host memory for staging inputs (cudaHostAlloc / cudaFreeHost). */
+int ag_alloc_host(ag_ctx* ctx, size_t bytes, void** out);
+int ag_free_host(ag_ctx* ctx, void* ptr);
 
 /* Replaces: backend.py:5069-5080 fill_storage / fill_storage2 (fill_scalar_kernel,
  * fill_scalar_kernel2 in metal_ops.metal:122-137). */
