@@ -324,6 +324,18 @@ def test_gather_golden(golden, case):
     G.free(ids, table, out)
 
 
+def _assert_rows_close(got, ref, tol, what):
+    """Every table row is an independent sum with its own scale (a hot row collects thousands
+    of addends, most rows none): |got-ref| <= tol * (rms(row of ref) + |ref|), rows that
+    received nothing must be exactly equal."""
+    ref64, got64 = ref.astype(np.float64), got.astype(np.float64)
+    row_rms = np.sqrt(np.mean(ref64 * ref64, axis=1, keepdims=True))
+    quiet = row_rms[:, 0] == 0
+    assert np.array_equal(got[quiet], ref[quiet]), f"{what}: untouched rows differ"
+    e = np.max(np.abs(got64 - ref64)[~quiet] / (row_rms[~quiet] + np.abs(ref64[~quiet])))
+    assert e <= tol, f"{what}: per-row max |d|/(rms_row+|ref|) = {e:.3e} > {tol:.1e}"
+
+
 def _zipf_ids(rng, V, n, s=1.1):
     p = 1.0 / np.arange(1, V + 1) ** s
     p /= p.sum()
@@ -349,7 +361,12 @@ def test_gather_scatter_full_size(V, C, n):
     G.run_backward(node)
     got = G.down(table.grad)
     ref = O.gather_backward(ids_, dout_, np.zeros_like(table_))
-    assert_close(got, ref, TOL_BWD, "dtable")
+    _assert_rows_close(got, ref, TOL_BWD, "dtable")
+    # distance to the fp64 sum: the fixed-order grouped sum is no further from it than
+    # numpy's sequential fp32 np.add.at (hot rows collect thousands of addends)
+    truth = np.zeros(table_.shape, np.float64)
+    np.add.at(truth, ids_.ravel().astype(np.int64), dout_.reshape(-1, C).astype(np.float64))
+    assert np.max(np.abs(got - truth)) <= 2.0 * np.max(np.abs(ref - truth)) + 1e-12
     counts = np.bincount(ids_.ravel(), minlength=V)
     assert not got[counts == 0].any()
     singles = counts == 1
@@ -359,7 +376,7 @@ def test_gather_scatter_full_size(V, C, n):
     assert np.array_equal(G.down(table.grad), got)  # deterministic
     # accumulate on top of an existing gradient
     G.run_backward(node)
-    assert_close(G.down(table.grad), 2 * ref, TOL_BWD, "dtable x2")
+    _assert_rows_close(G.down(table.grad), 2 * ref, TOL_BWD, "dtable x2")
     G.check_clean_status()
     G.free(ids, table, out)
 
