@@ -139,6 +139,12 @@ class CudaContext:
                                               _p(dbeta), _p(partials), int(partials_bytes), int(N_), int(C_),
                                               float(eps)))
 
+    def layernorm_backward_noalloc(self, dy, x, gamma, dres, dx, dgamma, dbeta, N_, C_, eps):
+        """LayerNorm backward whose partial-sum workspace lives inside the library: for callers
+        that cannot hand over (or allocate) scratch memory.  C_ <= 4096."""
+        self._check(lib.ag_layernorm_backward_noalloc(self._h, _p(dy), _p(x), _p(gamma), _p(dres), _p(dx),
+                                                      _p(dgamma), _p(dbeta), int(N_), int(C_), float(eps)))
+
     def rmsnorm_forward(self, x, gamma, y, inv_rms, N_, C_, eps, dtype=N.AG_F32):
         self._check(lib.ag_rmsnorm_forward(self._h, _p(x), _p(gamma), _p(y), _p(inv_rms), int(N_), int(C_), float(eps),
                                            int(dtype)))

@@ -652,3 +652,123 @@ extern "C" int ag_rmsnorm_backward(ag_ctx* ctx, const void* dz, const void* x, c
                                              static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx),
                                              dgamma, nullptr, partials, partials_bytes, N, C, eps);
 }
+
+// =========================================================================================
+// LayerNorm backward for callers that cannot allocate device memory.
+//
+// Some hosts of this library hand it only the tensors of the op: a runtime whose arena was
+// sized before this backend was registered, a plugin slot with no allocator callback, or a
+// caller inside a region where cudaMalloc is forbidden.  ag_layernorm_backward needs a
+// workspace for its per-CTA dgamma/dbeta partial rows; this variant keeps that workspace in
+// a fixed array inside the library image instead.  Nothing is allocated or freed here, and
+// no allocating library routine is called.
+//
+// The array costs AG_LN_NOALLOC_SCRATCH_BYTES of device memory on every GPU that loads the
+// library, until the process exits.  It is shared by all calls: two calls whose kernels
+// overlap on the GPU (different streams or contexts) race on it; calls on one stream are
+// safe.  Nothing in it has to start at zero - every partial row the second pass reads is
+// written in full by the first pass of the same call - so stale contents are harmless.
+//
+// In host code the array's name is only a stand-in for the symbol, not a device address.
+// The address comes from cudaGetSymbolAddress, looked up once per device with that device
+// current, on the first call made on that device; do that first call outside any stream
+// capture.
+// =========================================================================================
+namespace {
+
+constexpr size_t kLnNoallocScratchBytes = (size_t)AG_LN_NOALLOC_SCRATCH_BYTES;
+constexpr int kLnNoallocMaxDevices = 64;
+
+static __device__ __align__(256) float g_ln_noalloc_scratch[kLnNoallocScratchBytes / sizeof(float)];
+
+float* g_ln_noalloc_addr[kLnNoallocMaxDevices] = {};
+
+int ln_noalloc_scratch(ag_ctx* ctx, float** out) {
+  AG_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kLnNoallocMaxDevices, "device ordinal %d out of range", ctx->device);
+  if (!g_ln_noalloc_addr[ctx->device]) {
+    int current = -1;
+    AG_CUDA(ctx, cudaGetDevice(&current));
+    if (current != ctx->device) AG_CUDA(ctx, cudaSetDevice(ctx->device));
+    void* p = nullptr;
+    AG_CUDA(ctx, cudaGetSymbolAddress(&p, g_ln_noalloc_scratch));
+    if (current != ctx->device && current >= 0) AG_CUDA(ctx, cudaSetDevice(current));
+    g_ln_noalloc_addr[ctx->device] = static_cast<float*>(p);
+  }
+  *out = g_ln_noalloc_addr[ctx->device];
+  return AG_OK;
+}
+
+// Same kernels as ag_layernorm_backward, with the persistent grid capped so that its partial
+// rows fit the fixed array.
+template <int KP>
+int ln_noalloc_launch_kp(ag_ctx* ctx, const float* dy, const float* x, const float* gamma, const float* dres, float* dx,
+                         float* partials, int wg, int wb, int64_t N, int C, float eps, int max_grid, int* grid_out) {
+  const size_t smem = (size_t)(1 + NORM_WARPS) * C * sizeof(float);
+  auto kern = norm_backward_kernel<float, KP, kLayerNorm>;
+  static int occ_cache = 0;
+  static size_t occ_smem = 0;
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
+  if (occ < 0)
+    AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
+  int grid = persistent_grid(ctx, N, occ);
+  if (grid > max_grid) grid = max_grid;
+  kern<<<grid, NORM_THREADS, smem, ctx->stream>>>(dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, ctx->d_status);
+  AG_LAUNCHED(ctx, "norm_backward_kernel");
+  *grid_out = grid;
+  return AG_OK;
+}
+
+}  // namespace
+
+extern "C" int ag_layernorm_backward_noalloc(ag_ctx* ctx, const float* dy, const float* x, const float* gamma,
+                                             const float* dres, float* dx, float* dgamma, float* dbeta, int64_t N,
+                                             int C, float eps) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (N == 0) return AG_OK;
+  AG_REQUIRE(ctx, dy && x && gamma, "ag_layernorm_backward_noalloc: null pointer");
+  AG_REQUIRE(ctx, N > 0 && C > 0, "ag_layernorm_backward_noalloc: bad shape N=%lld C=%d", (long long)N, C);
+  if (C > AG_LN_NOALLOC_MAX_C)
+    AG_FAIL(ctx, AG_ERR_INVALID,
+            "ag_layernorm_backward_noalloc: C=%d exceeds the built-in workspace limit of %d columns; use "
+            "ag_layernorm_backward with a caller-provided workspace",
+            C, AG_LN_NOALLOC_MAX_C);
+  float* partials = nullptr;
+  int rc = ln_noalloc_scratch(ctx, &partials);
+  if (rc) return rc;
+  const int max_grid = (int)(kLnNoallocScratchBytes / ((size_t)2 * C * sizeof(float)));
+  const int wg = dgamma != nullptr, wb = dbeta != nullptr;
+  const bool vec_ok = (C % 4 == 0) && ag_aligned16(dy) && ag_aligned16(x) && ag_aligned16(dres) && ag_aligned16(dx);
+  const int kp = vec_ok ? pick_kp(C / 4) : 0;
+  int grid = 0;
+  rc = -1;
+#define AG_NA_CASE(K)                                                                                           \
+  case K:                                                                                                       \
+    rc = ln_noalloc_launch_kp<K>(ctx, dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, max_grid, &grid);    \
+    break;
+  switch (kp) {
+    AG_NA_CASE(1) AG_NA_CASE(2) AG_NA_CASE(3) AG_NA_CASE(4) AG_NA_CASE(5) AG_NA_CASE(6) AG_NA_CASE(8) AG_NA_CASE(10)
+    AG_NA_CASE(12) AG_NA_CASE(16)
+    default:
+      break;
+  }
+#undef AG_NA_CASE
+  if (rc > 0) return rc;
+  if (rc < 0) {
+    const size_t smem = (size_t)2 * C * sizeof(float);
+    auto kern = norm_backward_generic_kernel<float, kLayerNorm>;
+    if (smem > 48 * 1024)
+      AG_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int64_t cap = (int64_t)ctx->sm_count * 4;
+    grid = (int)(N < cap ? N : cap);
+    if (grid > max_grid) grid = max_grid;
+    kern<<<grid, NORM_THREADS, smem, ctx->stream>>>(dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps);
+    AG_LAUNCHED(ctx, "norm_backward_generic_kernel");
+  }
+  if (wg || wb) {
+    dim3 rgrid((C + 31) / 32, 2);
+    norm_partials_reduce_kernel<<<rgrid, dim3(32, 32), 0, ctx->stream>>>(partials, grid, C, wg ? dgamma : nullptr,
+                                                                         wb ? dbeta : nullptr);
+    AG_LAUNCHED(ctx, "norm_partials_reduce_kernel");
+  }
+  return AG_OK;
+}

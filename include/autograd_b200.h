@@ -113,6 +113,24 @@ size_t ag_norm_partials_bytes(ag_ctx* ctx, int C);
 int ag_layernorm_backward(ag_ctx* ctx, const float* dy, const float* x, const float* gamma,
                           const float* dres, float* dx, float* dgamma, float* dbeta,
                           void* partials, size_t partials_bytes, int64_t N, int C, float eps);
+/* No counterpart in the reference.  Same result as ag_layernorm_backward for callers that
+ * have no way to provide the partial-sum workspace: a runtime whose arena was planned without
+ * this backend's scratch slots, a plugin interface that passes only the op's tensors, or code
+ * running where device allocation is not permitted.  The workspace is a fixed array of
+ * AG_LN_NOALLOC_SCRATCH_BYTES inside the library image (held on every GPU that loads the
+ * library until the process exits), so this call allocates and frees nothing.
+ *   - C must not exceed AG_LN_NOALLOC_MAX_C; larger rows are rejected with AG_ERR_INVALID.
+ *   - The first call on a device resolves the array's device address; make that call before
+ *     any stream capture begins.
+ *   - All calls share the one array.  Calls on the same stream are ordered and safe; calls
+ *     whose kernels may overlap on the GPU race on it.  Its previous contents never matter.
+ *   - dgamma/dbeta are summed over a grid that may be smaller than the one
+ *     ag_layernorm_backward uses, so they agree with it to rounding, not bit for bit. */
+#define AG_LN_NOALLOC_SCRATCH_BYTES (8u << 20)
+#define AG_LN_NOALLOC_MAX_C 4096
+int ag_layernorm_backward_noalloc(ag_ctx* ctx, const float* dy, const float* x, const float* gamma,
+                                  const float* dres, float* dx, float* dgamma, float* dbeta,
+                                  int64_t N, int C, float eps);
 
 /* ---- a4 RMSNorm -----------------------------------------------------------------------
  * Replaces: the RMSNorm stage of backend.py:1097-1108 / :1228-1251 (also :741-749,
