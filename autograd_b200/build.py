@@ -69,7 +69,7 @@ def build(force=False, verbose=False, ptxas_info=False):
         for _, log in results:
             if log:
                 sys.stderr.write(log)
-    cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart", "-lcuda"]
+    cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

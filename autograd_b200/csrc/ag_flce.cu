@@ -293,7 +293,7 @@ extern "C" int ag_flce_forward(ag_ctx* ctx, const ag_flce_desc* d, const float* 
   const bool tc = d->precision != AG_CE_FP32 && ag_flce_tc_supported(d);
   void* tc_scratch = base + p.total;
   if (tc) {
-    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch);
+    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch, false);
     if (rc) return rc;
   }
   AG_CUDA(ctx, cudaMemsetAsync(tgt, 0, (size_t)d->N * 4, ctx->stream));
@@ -337,7 +337,7 @@ extern "C" int ag_flce_backward(ag_ctx* ctx, const ag_flce_desc* d, const float*
   const bool tc = d->precision != AG_CE_FP32 && ag_flce_tc_supported(d);
   void* tc_scratch = base + p.total;
   if (tc) {
-    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch);
+    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch, true);
     if (rc) return rc;
   }
   ce_denominator_kernel<<<1, 1024, 0, ctx->stream>>>(targets, d->N, d->V, d->reduction, denom);
@@ -352,6 +352,12 @@ extern "C" int ag_flce_backward(ag_ctx* ctx, const ag_flce_desc* d, const float*
       else
         rc = sgemm(ctx, X + r0 * C, C, 1, W + (int64_t)v0 * C, 1, C, panel, vc, rows, vc, C, false);
       if (rc) return rc;
+      if (tc) {
+        rc = ag_flce_tc_grads(ctx, d, tc_scratch, r0, rows, v0, vc, panel, vc, targets, lse, row_scale, dloss, denom,
+                              dX, dW);
+        if (rc) return rc;
+        continue;
+      }
       ce_panel_dlogits_kernel<<<rows, CE_THREADS, 0, ctx->stream>>>(panel, vc, vc, v0, targets + r0, lse + r0,
                                                                     row_scale ? row_scale + r0 : nullptr, dloss, denom,
                                                                     V, d->ignore_mode);

@@ -4,12 +4,20 @@
 
 #include "ag_common.cuh"
 
-// True when the tensor-core path takes this problem (shape/alignment constraints).
+// True when the tensor-core path takes this problem (precision mode, shape, alignment).
 bool ag_flce_tc_supported(const ag_flce_desc* d);
-// Extra workspace (split / converted operands) the tensor-core path needs.
+// Extra workspace (split / converted / transposed operands) the tensor-core path needs.
 size_t ag_flce_tc_scratch_bytes(const ag_flce_desc* d);
-// Converts X and W into the operand format of d->precision inside tc_scratch.
-int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch);
+// Converts X and W into the operand format of d->precision inside tc_scratch; `backward` also
+// produces the transposed copies the gradient GEMMs read.
+int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch,
+                       bool backward);
 // panel[rows, vc] (row stride ld) = X[r0:r0+rows] . W[v0:v0+vc]^T from the prepared operands.
 int ag_flce_tc_logits(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
                       float* panel, int64_t ld);
+// From a logits panel: dlogits in operand form, then dX[r0:r0+rows] += dl . W[v0:v0+vc] and
+// dW[v0:v0+vc] += dl^T . X[r0:r0+rows] (either output may be null).  targets / lse / row_scale
+// are the full-length arrays (indexed from r0 inside).
+int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
+                     const float* panel, int64_t ld, const int32_t* targets, const float* lse, const float* row_scale,
+                     const float* dloss, const float* denom, float* dX, float* dW);

@@ -206,32 +206,49 @@ norm_forward_generic_kernel(const T* x, const T* r, const float* __restrict__ ga
 // ---------------------------------------------------------------------------------------
 // partials layout: [gridDim.x][2][C] floats (slot 0: dgamma, slot 1: dbeta; RMSNorm leaves
 // slot 1 unwritten and unread).
+// Shared memory: gamma (C floats) + per-warp column accumulators [warp][slot][C].  The column
+// sums live in shared memory rather than registers so that the registers can hold x, dy AND the
+// incoming residual gradient of a row at once: all three are requested from HBM up front, in
+// one burst per row, instead of a second dependent load phase after the row reductions.
+template <int KIND>
+__host__ __device__ constexpr int norm_bwd_slots() { return KIND == kLayerNorm ? 2 : 1; }
+
 template <typename T, int KP, int KIND>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
                      const T* dres, T* dx, float* __restrict__ partials, int want_dgamma, int want_dbeta, int64_t N,
                      int C, float eps, int* status) {
   constexpr int NV = Pack<T>::N;
+  constexpr int SLOTS = norm_bwd_slots<KIND>();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* s_gamma = reinterpret_cast<float*>(smem_raw);  // C floats
-  float* s_acc = s_gamma + C;                           // NORM_WARPS * C floats
+  float* s_acc = s_gamma + C;                           // NORM_WARPS * SLOTS * C floats
   __shared__ __align__(8) uint64_t s_bar;
   if (gamma) ag_stage_vectors(s_gamma, gamma, nullptr, nullptr, C, &s_bar, status);
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const float inv_c = 1.0f / (float)C;
-
-  float acc_g[KP][NV], acc_b[KP][NV];
+  float* my_g = s_acc + (size_t)warp * SLOTS * C;
+  float* my_b = my_g + C;  // LayerNorm only
+  // each lane zeroes exactly the columns it will accumulate into: no cross-lane hazard
 #pragma unroll
-  for (int p = 0; p < KP; ++p)
+  for (int p = 0; p < KP; ++p) {
+    const int col = (p * 32 + lane) * NV;
+    if (col < C) {
 #pragma unroll
-    for (int e = 0; e < NV; ++e) acc_g[p][e] = acc_b[p][e] = 0.0f;
+      for (int e = 0; e < NV; ++e) {
+        my_g[col + e] = 0.0f;
+        if (KIND == kLayerNorm) my_b[col + e] = 0.0f;
+      }
+    }
+  }
 
   for (int64_t row = (int64_t)blockIdx.x * NORM_WARPS + warp; row < N; row += (int64_t)gridDim.x * NORM_WARPS) {
-    float v[KP][NV], g[KP][NV];
+    float v[KP][NV], g[KP][NV], o[KP][NV];
     const T* xr = x + row * C;
     const T* gr = dy + row * C;
+    const T* drr = (dres && dx) ? dres + row * C : nullptr;
 #pragma unroll
     for (int p = 0; p < KP; ++p) {
       const int col = (p * 32 + lane) * NV;
@@ -241,6 +258,16 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       } else {
 #pragma unroll
         for (int e = 0; e < NV; ++e) v[p][e] = g[p][e] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < KP; ++p) {
+      const int col = (p * 32 + lane) * NV;
+      if (drr && col < C) {
+        Pack<T>::load(drr + col, o[p]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) o[p][e] = 0.0f;
       }
     }
     // statistics, recomputed from the saved input exactly as in forward
@@ -280,15 +307,26 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       const int col = (p * 32 + lane) * NV;
       if (col < C) {
 #pragma unroll
-        for (int e = 0; e < NV; ++e) {
-          const float xh = v[p][e] * scale;
-          v[p][e] = xh;
-          acc_g[p][e] += g[p][e] * xh;
-          if (KIND == kLayerNorm) acc_b[p][e] += g[p][e];
-          const float dg = gamma ? g[p][e] * s_gamma[col + e] : g[p][e];
-          g[p][e] = dg;
-          s1 += dg;
-          s2 += dg * xh;
+        for (int e4 = 0; e4 < NV; e4 += 4) {
+          float4 ag = *reinterpret_cast<float4*>(my_g + col + e4);
+          float4 ab = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (KIND == kLayerNorm) ab = *reinterpret_cast<float4*>(my_b + col + e4);
+          float* agp = reinterpret_cast<float*>(&ag);
+          float* abp = reinterpret_cast<float*>(&ab);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = e4 + j;
+            const float xh = v[p][e] * scale;
+            v[p][e] = xh;
+            agp[j] += g[p][e] * xh;
+            if (KIND == kLayerNorm) abp[j] += g[p][e];
+            const float dg = gamma ? g[p][e] * s_gamma[col + e] : g[p][e];
+            g[p][e] = dg;
+            s1 += dg;
+            s2 += dg * xh;
+          }
+          *reinterpret_cast<float4*>(my_g + col + e4) = ag;
+          if (KIND == kLayerNorm) *reinterpret_cast<float4*>(my_b + col + e4) = ab;
         }
       }
     }
@@ -297,50 +335,32 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     const float m2 = (ag_warp_sum(s2) * inv_c) * scale;
     if (dx == nullptr) continue;  // only the column sums were asked for
     T* dxr = dx + row * C;
-    const T* drr = dres ? dres + row * C : nullptr;
 #pragma unroll
     for (int p = 0; p < KP; ++p) {
       const int col = (p * 32 + lane) * NV;
       if (col < C) {
-        float o[NV];
-        if (drr) {
-          Pack<T>::load(drr + col, o);
-        } else {
-#pragma unroll
-          for (int e = 0; e < NV; ++e) o[e] = 0.0f;
-        }
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
           // backend.py:475-487: xg += dyg*rstd; xg -= m1; xg -= xhat*m2
-          float t = o[e] + g[p][e] * scale;
+          float t = o[p][e] + g[p][e] * scale;
           if (KIND == kLayerNorm) t = t - m1;
-          o[e] = t - v[p][e] * m2;
+          o[p][e] = t - v[p][e] * m2;
         }
-        Pack<T>::store(dxr + col, o);
+        Pack<T>::store(dxr + col, o[p]);
       }
     }
   }
 
-  // fold the warps' column accumulators in warp order, one slot at a time
-  const int n_slots = (KIND == kLayerNorm) ? 2 : 1;
-  for (int slot = 0; slot < n_slots; ++slot) {
+  // fold the warps' column accumulators in warp order
+  __syncthreads();
+  for (int slot = 0; slot < SLOTS; ++slot) {
     const bool wanted = slot == 0 ? (want_dgamma != 0) : (want_dbeta != 0);
     if (!wanted) continue;  // uniform across the CTA
-    __syncthreads();
-#pragma unroll
-    for (int p = 0; p < KP; ++p) {
-      const int col = (p * 32 + lane) * NV;
-      if (col < C) {
-#pragma unroll
-        for (int e = 0; e < NV; ++e) s_acc[warp * C + col + e] = slot == 0 ? acc_g[p][e] : acc_b[p][e];
-      }
-    }
-    __syncthreads();
     float* out = partials + ((int64_t)blockIdx.x * 2 + slot) * C;
     for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
       float t = 0.0f;
 #pragma unroll
-      for (int w = 0; w < NORM_WARPS; ++w) t += s_acc[w * C + c];
+      for (int w = 0; w < NORM_WARPS; ++w) t += s_acc[((size_t)w * SLOTS + slot) * C + c];
       out[c] = t;
     }
   }
@@ -522,13 +542,18 @@ int launch_fwd(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const fl
   return AG_OK;
 }
 
+// Shared memory of the row-in-registers backward kernel, and whether it fits an SM.
+template <int KIND>
+size_t norm_bwd_smem(int C) { return (size_t)(1 + NORM_WARPS * norm_bwd_slots<KIND>()) * C * sizeof(float); }
+constexpr size_t kNormSmemLimit = 200 * 1024;
+
 // Largest grid any backward launch may use: bounds the partials workspace.
 inline int max_partial_rows(const ag_ctx* ctx) { return ctx->sm_count * 8; }
 
 template <typename T, int KIND, int KP>
 int launch_bwd_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T* dres, T* dx, float* partials,
                   int wg, int wb, int64_t N, int C, float eps, int* grid_out) {
-  const size_t smem = (size_t)(1 + NORM_WARPS) * C * sizeof(float);
+  const size_t smem = norm_bwd_smem<KIND>(C);
   auto kern = norm_backward_kernel<T, KP, KIND>;
   static int occ_cache = 0;
   static size_t occ_smem = 0;
@@ -553,7 +578,8 @@ int launch_bwd(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T
               ag_norm_partials_bytes(ctx, C));
     AG_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(partials) & 3u) == 0, "norm backward: partials not 4-byte aligned");
   }
-  const bool vec_ok = (C % NV == 0) && ag_aligned16(dy) && ag_aligned16(x) && ag_aligned16(dres) && ag_aligned16(dx);
+  const bool vec_ok = (C % NV == 0) && ag_aligned16(dy) && ag_aligned16(x) && ag_aligned16(dres) && ag_aligned16(dx) &&
+                      norm_bwd_smem<KIND>(C) <= kNormSmemLimit;
   const int kp = vec_ok ? pick_kp(C / NV) : 0;
   int grid = 0;
   int rc = -1;
@@ -614,7 +640,7 @@ extern "C" int ag_layernorm_backward(ag_ctx* ctx, const float* dy, const float* 
   if (N == 0) return AG_OK;
   AG_REQUIRE(ctx, dy && x && gamma, "ag_layernorm_backward: null pointer");
   AG_REQUIRE(ctx, N > 0 && C > 0, "ag_layernorm_backward: bad shape N=%lld C=%d", (long long)N, C);
-  AG_REQUIRE(ctx, (size_t)(1 + NORM_WARPS) * C * 4 <= 200 * 1024, "ag_layernorm_backward: C=%d too large", C);
+  AG_REQUIRE(ctx, (size_t)2 * C * 4 <= kNormSmemLimit, "ag_layernorm_backward: C=%d too large", C);
   return launch_bwd<float, kLayerNorm>(ctx, dy, x, gamma, dres, dx, dgamma, dbeta, partials, partials_bytes, N, C, eps);
 }
 
@@ -642,7 +668,7 @@ extern "C" int ag_rmsnorm_backward(ag_ctx* ctx, const void* dz, const void* x, c
   AG_REQUIRE(ctx, N > 0 && C > 0, "ag_rmsnorm_backward: bad shape N=%lld C=%d", (long long)N, C);
   AG_REQUIRE(ctx, dtype == AG_F32 || dtype == AG_BF16, "ag_rmsnorm_backward: unknown dtype %d", dtype);
   AG_REQUIRE(ctx, gamma || !dgamma, "ag_rmsnorm_backward: dgamma requested without gamma");
-  AG_REQUIRE(ctx, (size_t)(1 + NORM_WARPS) * C * 4 <= 200 * 1024, "ag_rmsnorm_backward: C=%d too large", C);
+  AG_REQUIRE(ctx, (size_t)2 * C * 4 <= kNormSmemLimit, "ag_rmsnorm_backward: C=%d too large", C);
   if (dtype == AG_F32)
     return launch_bwd<float, kRmsNorm>(ctx, static_cast<const float*>(dz), static_cast<const float*>(x), gamma,
                                        static_cast<const float*>(dres), static_cast<float*>(dx), dgamma, nullptr,
@@ -703,7 +729,7 @@ int ln_noalloc_scratch(ag_ctx* ctx, float** out) {
 template <int KP>
 int ln_noalloc_launch_kp(ag_ctx* ctx, const float* dy, const float* x, const float* gamma, const float* dres, float* dx,
                          float* partials, int wg, int wb, int64_t N, int C, float eps, int max_grid, int* grid_out) {
-  const size_t smem = (size_t)(1 + NORM_WARPS) * C * sizeof(float);
+  const size_t smem = norm_bwd_smem<kLayerNorm>(C);
   auto kern = norm_backward_kernel<float, KP, kLayerNorm>;
   static int occ_cache = 0;
   static size_t occ_smem = 0;
@@ -737,7 +763,8 @@ extern "C" int ag_layernorm_backward_noalloc(ag_ctx* ctx, const float* dy, const
   if (rc) return rc;
   const int max_grid = (int)(kLnNoallocScratchBytes / ((size_t)2 * C * sizeof(float)));
   const int wg = dgamma != nullptr, wb = dbeta != nullptr;
-  const bool vec_ok = (C % 4 == 0) && ag_aligned16(dy) && ag_aligned16(x) && ag_aligned16(dres) && ag_aligned16(dx);
+  const bool vec_ok = (C % 4 == 0) && ag_aligned16(dy) && ag_aligned16(x) && ag_aligned16(dres) && ag_aligned16(dx) &&
+                      norm_bwd_smem<kLayerNorm>(C) <= kNormSmemLimit;
   const int kp = vec_ok ? pick_kp(C / 4) : 0;
   int grid = 0;
   rc = -1;

@@ -1,10 +1,11 @@
 // Rotate-half RoPE applied in place to q (B,T,H,D) and k (B,T,HKV,D).
 //
-// One CTA handles one token (b,t): its cos/sin row (D/2 floats each) is staged in shared
-// memory once and reused by all H+HKV heads.  A thread owns one 16-byte packet of the low
-// half of a head together with the matching packet of the high half, so both halves are
-// read once and written once.  All loads of a thread's heads are issued before the first
-// store.  Shapes where D/2 is not a multiple of the packet width use a scalar kernel.
+// One CTA handles one token (b,t).  A thread owns one 16-byte packet of the low half of a head
+// together with the matching packet of the high half, so both halves are read once and written
+// once; its cos/sin entries come straight from the (L2-resident) tables.  All loads of a thread
+// are issued in one burst before the first store: there is no shared-memory stage and no
+// barrier in the kernel.  Shapes where D/2 is not a multiple of the packet width use a scalar
+// kernel.
 #include "ag_common.cuh"
 
 namespace {
@@ -15,38 +16,42 @@ constexpr int ROPE_MAX_ITEMS = 4;  // packets pairs per thread kept in flight
 template <typename T>
 __global__ void __launch_bounds__(ROPE_THREADS)
 rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int T_len, int H, int HKV,
-            int D, int64_t q_stride, int64_t k_stride, float sgn, int* status) {
+            int D, int64_t q_stride, int64_t k_stride, float sgn) {
   constexpr int NV = Pack<T>::N;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int d2 = D >> 1;
-  float* s_cos = reinterpret_cast<float*>(smem_raw);
-  float* s_sin = s_cos + d2;
-  __shared__ __align__(8) uint64_t s_bar;
   const int64_t tok = blockIdx.x;  // b*T + t
   const int t = (int)(tok % T_len);
-  ag_stage_vectors(s_cos, cos_tab + (int64_t)t * d2, s_sin, sin_tab + (int64_t)t * d2, d2, &s_bar, status);
-
   const int ppd = d2 / NV;              // packets per half head
   const int items = (H + HKV) * ppd;    // packet pairs of this token
   T* qt = q + tok * q_stride;
   T* kt = k ? k + tok * k_stride : nullptr;
+  const float* crow = cos_tab + (int64_t)t * d2;
+  const float* srow = sin_tab + (int64_t)t * d2;
 
   for (int base = threadIdx.x; base < items; base += ROPE_THREADS * ROPE_MAX_ITEMS) {
-    float lo[ROPE_MAX_ITEMS][NV], hi[ROPE_MAX_ITEMS][NV];
+    float lo[ROPE_MAX_ITEMS][NV], hi[ROPE_MAX_ITEMS][NV], c[ROPE_MAX_ITEMS][NV], s[ROPE_MAX_ITEMS][NV];
     T* ptr[ROPE_MAX_ITEMS];
-    int col[ROPE_MAX_ITEMS];
+    // every load of this thread - activations and the table entries (L2-resident, the table is
+    // T*D/2 floats) - is issued before the first dependent use
 #pragma unroll
     for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
       const int it = base + u * ROPE_THREADS;
       ptr[u] = nullptr;
       if (it < items) {
         const int head = it / ppd;
-        col[u] = (it - head * ppd) * NV;
+        const int col = (it - head * ppd) * NV;
         T* hp = head < H ? qt + (int64_t)head * D : (kt ? kt + (int64_t)(head - H) * D : nullptr);
         if (hp) {
-          ptr[u] = hp + col[u];
+          ptr[u] = hp + col;
           Pack<T>::load(ptr[u], lo[u]);
           Pack<T>::load(ptr[u] + d2, hi[u]);
+#pragma unroll
+          for (int e = 0; e < NV; e += 4) {
+            const float4 cv = __ldg(reinterpret_cast<const float4*>(crow + col + e));
+            const float4 sv = __ldg(reinterpret_cast<const float4*>(srow + col + e));
+            c[u][e] = cv.x; c[u][e + 1] = cv.y; c[u][e + 2] = cv.z; c[u][e + 3] = cv.w;
+            s[u][e] = sv.x; s[u][e + 1] = sv.y; s[u][e + 2] = sv.z; s[u][e + 3] = sv.w;
+          }
         }
       }
     }
@@ -56,12 +61,12 @@ rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restri
         float olo[NV], ohi[NV];
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
-          const float c = s_cos[col[u] + e];
-          const float s = sgn * s_sin[col[u] + e];
+          const float cc = c[u][e];
+          const float ss = sgn * s[u][e];
           // sgn=+1: lo*c - hi*s , lo*s + hi*c   (backend.py:1413-1414)
           // sgn=-1: lo*c + hi*s , -lo*s + hi*c  (backend.py:1396-1397)
-          olo[e] = lo[u][e] * c - hi[u][e] * s;
-          ohi[e] = lo[u][e] * s + hi[u][e] * c;
+          olo[e] = lo[u][e] * cc - hi[u][e] * ss;
+          ohi[e] = lo[u][e] * ss + hi[u][e] * cc;
         }
         Pack<T>::store(ptr[u], olo);
         Pack<T>::store(ptr[u] + d2, ohi);
@@ -100,11 +105,11 @@ int rope_t(ag_ctx* ctx, void* qv, void* kv, const float* cos_tab, const float* s
   const int d2 = D / 2;
   const int64_t tokens = (int64_t)B * T_len;
   const float sgn = sin_sign >= 0 ? 1.0f : -1.0f;
-  const bool vec_ok = (d2 % NV == 0) && ag_aligned16(q) && ag_aligned16(k) && (qs % NV == 0) && (ks % NV == 0);
+  const bool vec_ok = (d2 % NV == 0) && ag_aligned16(q) && ag_aligned16(k) && (qs % NV == 0) && (ks % NV == 0) &&
+                      ag_aligned16(cos_tab) && ag_aligned16(sin_tab);
   if (vec_ok) {
-    const size_t smem = (size_t)D * sizeof(float);
-    rope_kernel<T><<<(unsigned)tokens, ROPE_THREADS, smem, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H, k ? HKV : 0,
-                                                                          D, qs, ks, sgn, ctx->d_status);
+    rope_kernel<T><<<(unsigned)tokens, ROPE_THREADS, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H, k ? HKV : 0, D,
+                                                                       qs, ks, sgn);
     AG_LAUNCHED(ctx, "rope_kernel");
   } else {
     rope_scalar_kernel<T><<<(unsigned)tokens, ROPE_THREADS, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H,

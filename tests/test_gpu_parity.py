@@ -465,6 +465,42 @@ def test_flce_mid_size_vs_oracle(N, C, V, precision):
     G.check_clean_status()
 
 
+@pytest.mark.parametrize("N,C,V", [(2048, 384, 8192), (1000, 1280, 4104)])
+def test_flce_bf16_mode_vs_oracle(N, C, V):
+    """The stated bf16 tensor-core mode of the CE GEMMs: 2e-2 against the fp32 oracle."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(1240)
+    X_ = (rng.standard_normal((1, N, C)) / np.sqrt(C)).astype(np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C))).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(1, N)).astype(np.int32)
+    Y_[rng.random((1, N)) < 0.05] = -1
+    ref = O.flce_masked(X_[0], W_, Y_[0])
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, 2, ignore_mode=0, chunk=4096)
+    assert abs(loss - float(ref["loss"])) <= TOL_BF16 * abs(loss)
+    assert_close(dX[0], ref["dX"], TOL_BF16, "dX")
+    assert_close(dW, ref["dW"], TOL_BF16, "dW")
+    assert not dX[0][Y_[0] < 0].any()
+    G.check_clean_status()
+
+
+def test_flce_tensor_core_path_is_taken_and_deterministic():
+    """3xTF32 panels: identical bits on a repeat, and different bits from the exact-fp32 FFMA
+    panels (which proves the tensor-core kernel, not the FFMA one, produced them)."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(1241)
+    N, C, V = 1536, 256, 4096
+    X_ = (rng.standard_normal((1, N, C)) / np.sqrt(C)).astype(np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C))).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(1, N)).astype(np.int32)
+    a = _run_flce(be, X_, W_, Y_, 1, ignore_mode=0, chunk=2048)
+    b = _run_flce(be, X_, W_, Y_, 1, ignore_mode=0, chunk=2048)
+    c = _run_flce(be, X_, W_, Y_, 0, ignore_mode=0, chunk=2048)
+    assert a[0] == b[0] and np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])
+    assert not np.array_equal(a[2], c[2])
+    assert_close(a[2], c[2], TOL_BWD, "dW 3xtf32 vs fp32")
+    G.check_clean_status()
+
+
 @pytest.mark.parametrize("case", ["plain", "row_scaled"])
 def test_rmsnorm_flce_golden(golden, case):
     ctx, alloc, be = G.env()
