@@ -28,14 +28,15 @@ rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restri
   const float* crow = cos_tab + (int64_t)t * d2;
   const float* srow = sin_tab + (int64_t)t * d2;
 
-  for (int base = threadIdx.x; base < items; base += ROPE_THREADS * ROPE_MAX_ITEMS) {
+  const int nthreads = blockDim.x;
+  for (int base = threadIdx.x; base < items; base += nthreads * ROPE_MAX_ITEMS) {
     float lo[ROPE_MAX_ITEMS][NV], hi[ROPE_MAX_ITEMS][NV], c[ROPE_MAX_ITEMS][NV], s[ROPE_MAX_ITEMS][NV];
     T* ptr[ROPE_MAX_ITEMS];
     // every load of this thread - activations and the table entries (L2-resident, the table is
     // T*D/2 floats) - is issued before the first dependent use
 #pragma unroll
     for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
-      const int it = base + u * ROPE_THREADS;
+      const int it = base + u * nthreads;
       ptr[u] = nullptr;
       if (it < items) {
         const int head = it / ppd;
@@ -108,7 +109,13 @@ int rope_t(ag_ctx* ctx, void* qv, void* kv, const float* cos_tab, const float* s
   const bool vec_ok = (d2 % NV == 0) && ag_aligned16(q) && ag_aligned16(k) && (qs % NV == 0) && (ks % NV == 0) &&
                       ag_aligned16(cos_tab) && ag_aligned16(sin_tab);
   if (vec_ok) {
-    rope_kernel<T><<<(unsigned)tokens, ROPE_THREADS, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H, k ? HKV : 0, D,
+    // block size such that every thread owns the same number of packet pairs (e.g. 20 heads x 16
+    // packets = 320 pairs -> 160 threads x 2, not 256 threads of which 64 do double work)
+    const int items = (H + (k ? HKV : 0)) * (d2 / NV);
+    const int per_thread = (items + ROPE_THREADS - 1) / ROPE_THREADS;
+    int threads = ((items + per_thread - 1) / per_thread + 31) / 32 * 32;
+    if (threads > ROPE_THREADS) threads = ROPE_THREADS;
+    rope_kernel<T><<<(unsigned)tokens, threads, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H, k ? HKV : 0, D,
                                                                        qs, ks, sgn);
     AG_LAUNCHED(ctx, "rope_kernel");
   } else {
