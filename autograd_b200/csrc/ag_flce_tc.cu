@@ -20,7 +20,7 @@
 //   dW     += dl^T. X         A = dl^T[vc,rows]  B = X^T[C,rows]
 // Every output tile has exactly one writer, so accumulation order is fixed.
 // Every mbarrier wait is bounded; on expiry the CTA raises AG_STATUS_WAIT_EXPIRED, all roles
-// leave their loops, TMEM is released and the kernel returns.  No multicast, no clusters.
+// leave their loops, TMEM is released and the kernel returns.  Every CTA loads its own tiles; no thread-block clusters.
 #include <cuda.h>
 
 #include "ag_flce.cuh"

@@ -18,9 +18,9 @@ class DeviceArrayView:
     """A device address seen through `__cuda_array_interface__`, so that torch can alias it
     without a copy (torch.as_tensor(view, device="cuda"))."""
 
-    def __init__(self, address: int, n_floats: int):
+    def __init__(self, address: int, n_items: int, typestr: str = "<f4"):
         self.__cuda_array_interface__ = {
-            "shape": (int(n_floats),), "typestr": "<f4", "data": (int(address), False), "version": 3, "strides": None,
+            "shape": (int(n_items),), "typestr": typestr, "data": (int(address), False), "version": 3, "strides": None,
         }
 
 

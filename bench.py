@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--vocab", type=int, default=32768)
     ap.add_argument("--n-embd", type=int, default=1280)
+    ap.add_argument("--workload", default="step", choices=["step", "kernels"],
+                    help="step: the fused-layer step (the benchmark); kernels: one JSON line per fused layer "
+                         "kernel at the shapes of BASELINE configs 1-4, each against its own roofline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=2048)
     ap.add_argument("--cpu-sample-layers", type=int, default=2)
@@ -394,10 +397,186 @@ def run_b200(a):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------
+# per-kernel measurements at the shapes of BASELINE configs 1-4
+# --------------------------------------------------------------------------------------
+def run_kernels(a):
+    """Each kernel alone, CUDA events around `steps` launches after `warmup`, operands rotated
+    through enough copies that consecutive launches never find their inputs in L2."""
+    import torch
+
+    import autograd_b200 as ag
+    from autograd_b200 import dp
+
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx, alloc, be = ag.create(0, stream.cuda_stream)
+    peaks = load_peaks()
+    L2 = ctx.l2_bytes
+    bufs = []
+
+    def dev(n_elems, dtype=np.float32, std=1.0, ints=None):
+        st = alloc.alloc((int(n_elems),), dtype)
+        bufs.append(st)
+        addr = st.ptr.address
+        if ints is not None:
+            ctx.copy_from_host(addr, ints.astype(np.int32))
+        elif np.dtype(dtype) == np.dtype(np.float32):
+            dp.as_torch(addr, n_elems, 0).normal_(0.0, std)
+        else:  # bf16 bit patterns of N(0, std), written through an int16 alias of the buffer
+            t = torch.empty(int(n_elems), device="cuda", dtype=torch.bfloat16).normal_(0.0, std)
+            dst = torch.as_tensor(dp.DeviceArrayView(addr, n_elems, "<i2"), device="cuda")
+            dst.copy_(t.view(torch.int16))
+        return addr
+
+    def free_all():
+        ctx.synchronize()
+        for st in bufs:
+            alloc.free(st)
+        bufs.clear()
+
+    def sets_for(bytes_per_set):
+        return max(2, int(2.5 * L2 // max(bytes_per_set, 1)) + 1)
+
+    def time_it(fn, n_sets):
+        for i in range(a.warmup):
+            fn(i % n_sets)
+        ctx.synchronize()
+        E0, E1 = (1 << 20) + 2, (1 << 20) + 3
+        ctx.event_record(E0)
+        for i in range(a.steps):
+            fn(i % n_sets)
+        ctx.event_record(E1)
+        return ctx.event_elapsed_ms(E0, E1) / a.steps
+
+    def emit(cfg, kernel, ms, tokens, alg_bytes=None, useful_flops=None, dtype="f32", extra=None):
+        line = {"workload": "kernels", "config": cfg, "kernel": kernel, "dtype": dtype, "ms": round(ms, 5),
+                "tokens_per_s": tokens / (ms / 1e3), "steps": a.steps, "warmup": a.warmup}
+        if alg_bytes is not None:
+            gbs = alg_bytes / (ms / 1e3) / 1e9
+            line["roofline"] = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": round(gbs / peaks["hbm_gbs"], 4), "algorithmic_bytes": int(alg_bytes),
+                                "frac_of_nominal_8TBs": round(gbs / 8000.0, 4), "peak_source": peaks["source"]}
+        if useful_flops is not None:
+            tf = useful_flops / (ms / 1e3) / 1e12
+            line["roofline"] = {"bound": "tensor", "achieved": round(tf, 2), "peak": peaks["bf16_tflops"],
+                                "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops"], 4),
+                                "useful_flops": useful_flops, "peak_source": peaks["source"] + " bf16 burst"}
+        if extra:
+            line.update(extra)
+        print(json.dumps(line), flush=True)
+
+    f4 = 4
+    # ---- config 1: fused add + LayerNorm, 16384 x 384 (and the config-5 width 32768 x 1280)
+    for (N, C) in ((16384, 384), (32768, 1280)):
+        nb = N * C * f4
+        n_sets = sets_for(4 * nb)
+        x = [dev(N * C) for _ in range(n_sets)]; r = [dev(N * C) for _ in range(n_sets)]
+        h = [dev(N * C) for _ in range(n_sets)]; y = [dev(N * C) for _ in range(n_sets)]
+        gam, bet, dg, db = dev(C), dev(C), dev(C), dev(C)
+        pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
+        ms = time_it(lambda i: ctx.add_layernorm_forward(x[i], r[i], gam, bet, h[i], y[i], 0, 0, N, C, 1e-5), n_sets)
+        emit("cfg1" if C == 384 else "cfg5-width", f"add_layernorm_forward {N}x{C}", ms, N, alg_bytes=4 * nb)
+        # backward: dy = y[i], saved input = h[i], residual gradient accumulated in place in x[i]
+        ms = time_it(lambda i: ctx.layernorm_backward(y[i], h[i], gam, x[i], x[i], dg, db, part.ptr.address, pb, N, C,
+                                                      1e-5), n_sets)
+        emit("cfg1" if C == 384 else "cfg5-width", f"layernorm_backward(+residual grad) {N}x{C}", ms, N, alg_bytes=4 * nb)
+        free_all()
+    # ---- GELU 16384 x 1536
+    n = 16384 * 1536
+    n_sets = sets_for(3 * n * f4)
+    x = [dev(n) for _ in range(n_sets)]; y = [dev(n) for _ in range(n_sets)]; g = [dev(n) for _ in range(n_sets)]
+    ms = time_it(lambda i: ctx.gelu_forward(x[i], y[i], n), n_sets)
+    emit("gelu", "gelu_forward 16384x1536", ms, 16384, alg_bytes=2 * n * f4)
+    ms = time_it(lambda i: ctx.gelu_backward(x[i], y[i], 0, g[i], n), n_sets)
+    emit("gelu", "gelu_backward 16384x1536", ms, 16384, alg_bytes=3 * n * f4)
+    free_all()
+    # ---- config 3: RMSNorm, RoPE, SwiGLU at the Qwen shapes, fp32 and bf16 storage
+    N, C, H, HKV, D, I, B, T = 8192, 1536, 12, 2, 128, 8960, 4, 2048
+    for dt_name, dt, es in (("f32", np.float32, 4), ("bf16", np.uint16, 2)):
+        agdt = ag.AG_F32 if es == 4 else ag.AG_BF16
+        n_sets = sets_for(3 * N * C * es)
+        x = [dev(N * C, dt) for _ in range(n_sets)]; y = [dev(N * C, dt) for _ in range(n_sets)]
+        d = [dev(N * C, dt) for _ in range(n_sets)]
+        gam, dg = dev(C), dev(C)
+        pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
+        ms = time_it(lambda i: ctx.rmsnorm_forward(x[i], gam, y[i], 0, N, C, 1e-6, agdt), n_sets)
+        emit("cfg3", "rmsnorm_forward 8192x1536", ms, N, alg_bytes=2 * N * C * es, dtype=dt_name)
+        ms = time_it(lambda i: ctx.rmsnorm_backward(y[i], x[i], gam, d[i], d[i], dg, part.ptr.address, pb, N, C, 1e-6,
+                                                    agdt), n_sets)
+        emit("cfg3", "rmsnorm_backward(+residual grad) 8192x1536", ms, N, alg_bytes=4 * N * C * es, dtype=dt_name)
+        free_all()
+        nq, nk = N * H * D, N * HKV * D
+        n_sets = sets_for((nq + nk) * es)
+        q = [dev(nq, dt) for _ in range(n_sets)]; k = [dev(nk, dt) for _ in range(n_sets)]
+        from oracle import fused_layers as O   # table formula only (module.py:247-250); not the thing measured
+        cos_, sin_ = O.rope_tables(T, D, 1e6)
+        cos = dev(cos_.size); sin = dev(sin_.size)
+        ctx.copy_from_host(cos, cos_); ctx.copy_from_host(sin, sin_)
+        ms = time_it(lambda i: ctx.rope_qk(q[i], k[i], cos, sin, B, T, H, HKV, D, sin_sign=1, dtype=agdt), n_sets)
+        emit("cfg3", "rope_qk 4x2048 q12 k2 d128", ms, N, alg_bytes=2 * (nq + nk) * es, dtype=dt_name)
+        free_all()
+        n_sets = sets_for(4 * N * I * es)
+        gu = [dev(N * 2 * I, dt) for _ in range(n_sets)]; hid = [dev(N * I, dt) for _ in range(n_sets)]
+        ms = time_it(lambda i: ctx.swiglu_forward(gu[i], hid[i], N, I, agdt), n_sets)
+        emit("cfg3", "swiglu_forward 8192x8960", ms, N, alg_bytes=3 * N * I * es, dtype=dt_name)
+        ms = time_it(lambda i: ctx.swiglu_backward(gu[i], hid[i], N, I, agdt), n_sets)
+        emit("cfg3", "swiglu_backward_inplace 8192x8960", ms, N, alg_bytes=5 * N * I * es, dtype=dt_name)
+        free_all()
+    # ---- config 4: gather / deterministic scatter-add, Zipf(1.1) ids
+    V, C, n = 151936, 1536, 65536
+    rng = np.random.default_rng(1237)
+    p = 1.0 / np.arange(1, V + 1) ** 1.1
+    p /= p.sum()
+    ids_ = rng.choice(V, size=n, p=p).astype(np.int32)
+    uniq = int(np.unique(ids_).size)
+    ids = dev(n, np.int32, ints=ids_)
+    table = dev(V * C, std=0.02); dtable = dev(V * C)
+    n_sets = 2
+    out = [dev(n * C) for _ in range(n_sets)]
+    sb = ctx.scatter_add_scratch_bytes(n, C, V); sc = alloc.alloc((sb,), np.uint8); bufs.append(sc)
+    ms = time_it(lambda i: ctx.gather_forward(ids, table, out[i], n, C, V), n_sets)
+    emit("cfg4", "gather_forward 65536 ids x 1536", ms, n, alg_bytes=2 * n * C * f4,
+         extra={"unique_rows": uniq, "unique_row_lower_bound_bytes": (n + uniq) * C * f4})
+    ctx.fill_f32(dtable, 0.0, V * C)
+    ms = time_it(lambda i: ctx.gather_backward(ids, out[i], dtable, sc.ptr.address, sb, n, C, V), n_sets)
+    emit("cfg4", "scatter_add (sort + segmented sum) 65536 ids x 1536", ms, n, alg_bytes=(n + 2 * uniq) * C * f4,
+         extra={"unique_rows": uniq, "note": "without the dense zero-fill of dTable"})
+    ms0 = time_it(lambda i: ctx.fill_f32(dtable, 0.0, V * C), 1)
+    emit("cfg4", "zero-fill of dTable 151936x1536", ms0, n, alg_bytes=V * C * f4)
+    free_all()
+    # ---- config 2: fused linear + CE, N 16384, V 32768, C 384 and 1280
+    N, V = 16384, 32768
+    tg_ = rng.integers(0, V, size=N).astype(np.int32)
+    tg_[rng.random(N) < 0.05] = -1
+    for C in (384, 1280):
+        for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16", ag.AG_CE_BF16)):
+            X = dev(N * C, std=1.0 / np.sqrt(C)); W = dev(V * C, std=0.02)
+            dX, dW = dev(N * C), dev(V * C)
+            tg = dev(N, np.int32, ints=tg_)
+            loss, dloss, lse = dev(1), dev(1), dev(N)
+            ctx.fill_f32(dloss, 1.0, 1)
+            desc = ctx.flce_desc(N, C, V, vocab_chunk=4096, precision=prec)
+            sbytes = ctx.flce_scratch_bytes(desc); scr = alloc.alloc((sbytes,), np.uint8); bufs.append(scr)
+            ms_f = time_it(lambda i: ctx.flce_forward(desc, X, W, tg, 0, loss, lse, scr.ptr.address, sbytes), 1)
+            ms_b = time_it(lambda i: ctx.flce_backward(desc, X, W, tg, 0, dloss, lse, dX, dW, scr.ptr.address, sbytes), 1)
+            fl = 2.0 * N * C * V
+            emit("cfg2", f"fused_linear_ce forward N16384 C{C} V32768", ms_f, N, useful_flops=fl, dtype=pname)
+            emit("cfg2", f"fused_linear_ce backward N16384 C{C} V32768", ms_b, N, useful_flops=2 * fl, dtype=pname,
+                 extra={"executed_flops": 3 * fl})
+            emit("cfg2", f"fused_linear_ce fwd+bwd N16384 C{C} V32768", ms_f + ms_b, N, useful_flops=3 * fl, dtype=pname,
+                 extra={"scratch_bytes": sbytes})
+            free_all()
+    ctx.check_status()
+
+
 def main():
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "kernels":
+        run_kernels(a)
     else:
         run_b200(a)
 
