@@ -302,10 +302,12 @@ extern "C" int ag_flce_forward(ag_ctx* ctx, const ag_flce_desc* d, const float* 
     const int rows = (int)((d->N - r0) < p.rows_per_tile ? (d->N - r0) : p.rows_per_tile);
     for (int v0 = 0; v0 < V; v0 += d->vocab_chunk) {
       const int vc = (V - v0) < d->vocab_chunk ? (V - v0) : d->vocab_chunk;
-      if (tc)
-        rc = ag_flce_tc_logits(ctx, d, tc_scratch, r0, rows, v0, vc, panel, vc);
-      else
-        rc = sgemm(ctx, X + r0 * C, C, 1, W + (int64_t)v0 * C, 1, C, panel, vc, rows, vc, C, false);
+      if (tc) {
+        rc = ag_flce_tc_forward_panel(ctx, d, tc_scratch, r0, rows, v0, vc, targets, run_max, run_sum, tgt, v0 == 0);
+        if (rc) return rc;
+        continue;
+      }
+      rc = sgemm(ctx, X + r0 * C, C, 1, W + (int64_t)v0 * C, 1, C, panel, vc, rows, vc, C, false);
       if (rc) return rc;
       ce_panel_stats_kernel<<<rows, CE_THREADS, 0, ctx->stream>>>(panel, vc, vc, v0, targets + r0, run_max + r0,
                                                                   run_sum + r0, tgt + r0, v0 == 0);
@@ -347,17 +349,13 @@ extern "C" int ag_flce_backward(ag_ctx* ctx, const ag_flce_desc* d, const float*
     const int rows = (int)((d->N - r0) < p.rows_per_tile ? (d->N - r0) : p.rows_per_tile);
     for (int v0 = 0; v0 < V; v0 += d->vocab_chunk) {
       const int vc = (V - v0) < d->vocab_chunk ? (V - v0) : d->vocab_chunk;
-      if (tc)
-        rc = ag_flce_tc_logits(ctx, d, tc_scratch, r0, rows, v0, vc, panel, vc);
-      else
-        rc = sgemm(ctx, X + r0 * C, C, 1, W + (int64_t)v0 * C, 1, C, panel, vc, rows, vc, C, false);
-      if (rc) return rc;
       if (tc) {
-        rc = ag_flce_tc_grads(ctx, d, tc_scratch, r0, rows, v0, vc, panel, vc, targets, lse, row_scale, dloss, denom,
-                              dX, dW);
+        rc = ag_flce_tc_grads(ctx, d, tc_scratch, r0, rows, v0, vc, targets, lse, row_scale, dloss, denom, dX, dW);
         if (rc) return rc;
         continue;
       }
+      rc = sgemm(ctx, X + r0 * C, C, 1, W + (int64_t)v0 * C, 1, C, panel, vc, rows, vc, C, false);
+      if (rc) return rc;
       ce_panel_dlogits_kernel<<<rows, CE_THREADS, 0, ctx->stream>>>(panel, vc, vc, v0, targets + r0, lse + r0,
                                                                     row_scale ? row_scale + r0 : nullptr, dloss, denom,
                                                                     V, d->ignore_mode);

@@ -15,9 +15,15 @@ int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const
 // panel[rows, vc] (row stride ld) = X[r0:r0+rows] . W[v0:v0+vc]^T from the prepared operands.
 int ag_flce_tc_logits(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
                       float* panel, int64_t ld);
-// From a logits panel: dlogits in operand form, then dX[r0:r0+rows] += dl . W[v0:v0+vc] and
-// dW[v0:v0+vc] += dl^T . X[r0:r0+rows] (either output may be null).  targets / lse / row_scale
-// are the full-length arrays (indexed from r0 inside).
+// Forward of one panel without materialising it: logits tiles stay in TMEM, the GEMM epilogue
+// reduces them to per-tile (max, sum exp) and picks the target logit; the partials are folded
+// into run_max / run_sum (full-length arrays, indexed from r0 inside).
+int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0,
+                             int vc, const int32_t* targets, float* run_max, float* run_sum, float* tgt_logit,
+                             bool first_panel);
+// Backward of one panel: the logits are recomputed, the GEMM epilogue turns them into dlogits in
+// operand form, then dX[r0:r0+rows] += dl . W[v0:v0+vc] and dW[v0:v0+vc] += dl^T . X[r0:r0+rows]
+// (either output may be null).  targets / lse / row_scale are the full-length arrays.
 int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
-                     const float* panel, int64_t ld, const int32_t* targets, const float* lse, const float* row_scale,
-                     const float* dloss, const float* denom, float* dX, float* dW);
+                     const int32_t* targets, const float* lse, const float* row_scale, const float* dloss,
+                     const float* denom, float* dX, float* dW);

@@ -48,7 +48,27 @@ struct TcParams {
   int64_t ldd;
   int accumulate;
   int* status;
+  // fused cross-entropy epilogues (EPI_STATS / EPI_DLOGITS); row-indexed arrays start at A's row 0
+  const int32_t* targets;
+  int v0;                  // vocabulary index of column 0 of this panel
+  int V;
+  float2* part;            // EPI_STATS: per (column tile, row) partial (max, sum exp), [tiles_n][part_ld]
+  int64_t part_ld;
+  float* tgt_logit;        // EPI_STATS: logit of the target column, written by the tile that holds it
+  const float* lse;        // EPI_DLOGITS
+  const float* row_scale;
+  const float* dloss;
+  const float* denom;
+  int ignore_mode;
+  void* dl_hi;             // EPI_DLOGITS outputs: dl [M][ld_dl] and dl^T [N][ld_dlT], (hi, lo) or bf16
+  void* dl_lo;
+  int64_t ld_dl;
+  void* dlT_hi;
+  void* dlT_lo;
+  int64_t ld_dlT;
 };
+
+enum { EPI_STORE = 0, EPI_STATS = 1, EPI_DLOGITS = 2 };
 
 // ---------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ void tc_tma_load_2d(const CUtensorMap* tm, void* smem_dst, uint64_t* bar, int x, int y) {
@@ -130,7 +150,13 @@ __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int tile, int&
 }
 
 // ---------------------------------------------------------------------------- the kernel
-template <bool TF32>
+__device__ __forceinline__ float tc_tf32_rna(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+template <bool TF32, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant__ CUtensorMap tmA_lo,
                const __grid_constant__ CUtensorMap tmB_hi, const __grid_constant__ CUtensorMap tmB_lo,
@@ -273,33 +299,150 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       full_par[buf] ^= 1u;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      float* drow = p.D + (int64_t)row * p.ldd;
-      for (int c0 = 0; c0 < p.BN; c0 += 32) {
-        uint32_t r[32];
-        tc_tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 256u + (uint32_t)c0, r);
-        tc_tmem_ld_wait();
-        const int col = n0 + c0;
-        if (row < p.M && col < p.N) {
-          if (vec_ok && col + 32 <= p.N) {
+      const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 256u;
+      if (EPI == EPI_STORE) {
+        float* drow = p.D + (int64_t)row * p.ldd;
+        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+          uint32_t r[32];
+          tc_tmem_ld32(tacc + (uint32_t)c0, r);
+          tc_tmem_ld_wait();
+          const int col = n0 + c0;
+          if (row < p.M && col < p.N) {
+            if (vec_ok && col + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                     __uint_as_float(r[j + 3]));
-              float4* dst = reinterpret_cast<float4*>(drow + col + j);
-              if (p.accumulate) {
-                const float4 o = *dst;
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                       __uint_as_float(r[j + 3]));
+                float4* dst = reinterpret_cast<float4*>(drow + col + j);
+                if (p.accumulate) {
+                  const float4 o = *dst;
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *dst = v;
               }
-              *dst = v;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col + j < p.N) {
+                  const float v = __uint_as_float(r[j]);
+                  drow[col + j] = p.accumulate ? drow[col + j] + v : v;
+                }
+              }
             }
-          } else {
+          }
+        }
+      } else if (EPI == EPI_STATS) {
+        // (max, sum exp) of this row over the tile's columns, straight from TMEM: two sweeps
+        const int tcol = row < p.M ? p.targets[row] - p.v0 : -1;  // panel-relative target column
+        float mx = -INFINITY;
+        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+          uint32_t r[32];
+          tc_tmem_ld32(tacc + (uint32_t)c0, r);
+          tc_tmem_ld_wait();
+          const int col = n0 + c0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col + j < p.N) mx = fmaxf(mx, __uint_as_float(r[j]));
+        }
+        float sum = 0.0f, tl = 0.0f;
+        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+          uint32_t r[32];
+          tc_tmem_ld32(tacc + (uint32_t)c0, r);
+          tc_tmem_ld_wait();
+          const int col = n0 + c0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col + j < p.N) {
+              const float v = __uint_as_float(r[j]);
+              sum += expf(v - mx);
+              if (col + j == tcol) tl = v;
+            }
+          }
+        }
+        if (row < p.M) {
+          p.part[(int64_t)tn * p.part_ld + row] = make_float2(mx, sum);
+          if (tcol >= n0 && tcol < n0 + p.BN && tcol < p.N) p.tgt_logit[row] = tl;
+        }
+      } else {
+        // dlogits of this row, written in operand form: dl (row-major) and dl^T
+        float sc = 0.0f, e = 0.0f;
+        int tcol = -1;
+        if (row < p.M) {
+          const int t = p.targets[row];
+          const bool valid = t >= 0 && t < p.V;
+          sc = p.row_scale ? p.dloss[0] * p.row_scale[row] : p.dloss[0] / p.denom[0];
+          if (!valid && p.ignore_mode == AG_CE_IGNORE_MASKED) sc = 0.0f;
+          e = p.lse[row];
+          tcol = valid ? t - p.v0 : -1;
+        }
+        const bool row_vec = ((p.ld_dl & 7) == 0);
+        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+          uint32_t r[32];
+          tc_tmem_ld32(tacc + (uint32_t)c0, r);
+          tc_tmem_ld_wait();
+          const int col = n0 + c0;
+          if (row >= p.M || col >= p.N) continue;
+          float hi[32], lo[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float d = 0.0f;
+            if (sc != 0.0f) {
+              float pr = expf(__uint_as_float(r[j]) - e);
+              if (col + j == tcol) pr -= 1.0f;
+              d = pr * sc;
+            }
+            if (TF32) {
+              hi[j] = tc_tf32_rna(d);
+              lo[j] = tc_tf32_rna(d - hi[j]);
+            } else {
+              hi[j] = d;
+            }
+          }
+          if (TF32) {
+            float* dh = static_cast<float*>(p.dl_hi) + (int64_t)row * p.ld_dl + col;
+            float* dlo = static_cast<float*>(p.dl_lo) + (int64_t)row * p.ld_dl + col;
+            if (row_vec && col + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                *reinterpret_cast<float4*>(dh + j) = make_float4(hi[j], hi[j + 1], hi[j + 2], hi[j + 3]);
+                *reinterpret_cast<float4*>(dlo + j) = make_float4(lo[j], lo[j + 1], lo[j + 2], lo[j + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < p.N) { dh[j] = hi[j]; dlo[j] = lo[j]; }
+            }
+            float* th = static_cast<float*>(p.dlT_hi) + (int64_t)col * p.ld_dlT + row;
+            float* tlo = static_cast<float*>(p.dlT_lo) + (int64_t)col * p.ld_dlT + row;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              if (col + j < p.N) {
-                const float v = __uint_as_float(r[j]);
-                drow[col + j] = p.accumulate ? drow[col + j] + v : v;
+              if (col + j < p.N) {  // lanes of a warp hold consecutive rows: each store is one 128-byte line
+                th[(int64_t)j * p.ld_dlT] = hi[j];
+                tlo[(int64_t)j * p.ld_dlT] = lo[j];
               }
             }
+          } else {
+            __nv_bfloat16* dh = static_cast<__nv_bfloat16*>(p.dl_hi) + (int64_t)row * p.ld_dl + col;
+            if (row_vec && col + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q2 = 0; q2 < 4; ++q2) {
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(hi[j + 2 * q2], hi[j + 2 * q2 + 1]);
+                  w[q2] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(dh + j) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < p.N) dh[j] = __float2bfloat16_rn(hi[j]);
+            }
+            __nv_bfloat16* th = static_cast<__nv_bfloat16*>(p.dlT_hi) + (int64_t)col * p.ld_dlT + row;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N) th[(int64_t)j * p.ld_dlT] = __float2bfloat16_rn(hi[j]);
           }
         }
       }
@@ -366,9 +509,25 @@ int tc_encode(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int64_t 
 }
 
 // D[M,N] (+)= A[M,K] . B[N,K]^T on the tensor cores.
+template <bool TF32, int EPI>
+int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const CUtensorMap& a_lo,
+              const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    AG_CUDA(ctx, cudaFuncSetAttribute(tc_gemm_kernel<TF32, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      TC_SMEM_LIMIT));
+    attr_done = true;
+  }
+  tc_gemm_kernel<TF32, EPI><<<grid, TC_THREADS, smem, ctx->stream>>>(a_hi, a_lo, b_hi, b_lo, p);
+  AG_LAUNCHED(ctx, "tc_gemm_kernel");
+  return AG_OK;
+}
+
+// `epi` (may be null = EPI_STORE) carries the fields of the fused cross-entropy epilogues.
 int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, float* D, int64_t ldd, int M, int N, int K,
-            bool accumulate) {
+            bool accumulate, int epi_kind = EPI_STORE, const TcParams* epi = nullptr, int* tiles_n_out = nullptr) {
   TcParams p;
+  if (epi) p = *epi;
   p.M = M; p.N = N; p.K = K;
   p.BK = bf16 ? 64 : 32;
   p.umma_k = bf16 ? 16 : 8;
@@ -392,6 +551,7 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   p.BN = best_bn;
   p.tiles_m = tiles_m;
   p.tiles_n = (N + p.BN - 1) / p.BN;
+  if (tiles_n_out) *tiles_n_out = p.tiles_n;
   p.k_iters = (K + p.BK - 1) / p.BK;
   p.a_bytes = (uint32_t)TC_BM * 128u;
   p.b_bytes = (uint32_t)p.BN * 128u;
@@ -427,23 +587,16 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   const size_t smem = 1024 + (size_t)stages * stage_bytes + 256;
   const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-  if (bf16) {
-    static bool attr_done = false;
-    if (!attr_done) {
-      AG_CUDA(ctx, cudaFuncSetAttribute(tc_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT));
-      attr_done = true;
-    }
-    tc_gemm_kernel<false><<<grid, TC_THREADS, smem, ctx->stream>>>(tA_hi, tA_lo, tB_hi, tB_lo, p);
-  } else {
-    static bool attr_done = false;
-    if (!attr_done) {
-      AG_CUDA(ctx, cudaFuncSetAttribute(tc_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT));
-      attr_done = true;
-    }
-    tc_gemm_kernel<true><<<grid, TC_THREADS, smem, ctx->stream>>>(tA_hi, tA_lo, tB_hi, tB_lo, p);
+  if (epi_kind == EPI_STATS) {
+    AG_REQUIRE(ctx, p.part_ld >= M, "tc_gemm: partial-statistics rows too short");
+    return bf16 ? tc_launch<false, EPI_STATS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
+                : tc_launch<true, EPI_STATS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
   }
-  AG_LAUNCHED(ctx, "tc_gemm_kernel");
-  return AG_OK;
+  if (epi_kind == EPI_DLOGITS)
+    return bf16 ? tc_launch<false, EPI_DLOGITS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
+                : tc_launch<true, EPI_DLOGITS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+  return bf16 ? tc_launch<false, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
+              : tc_launch<true, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
 }
 
 // ---------------------------------------------------------------------------- operand preparation
@@ -575,11 +728,37 @@ dlogits_split_kernel(const float* __restrict__ L, int64_t ldl, int rows, int vc,
   }
 }
 
+// Folds the per-tile (max, sum exp) partials of one panel into the running row statistics, tiles
+// in index order (fixed order, one thread per row).
+__global__ void __launch_bounds__(256)
+ce_merge_partials_kernel(const float2* __restrict__ part, int64_t part_ld, int tiles_n, int rows,
+                         float* __restrict__ run_max, float* __restrict__ run_sum, int first_panel) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float m, s;
+  int t0 = 0;
+  if (first_panel) {
+    const float2 v = part[r];
+    m = v.x; s = v.y; t0 = 1;
+  } else {
+    m = run_max[r]; s = run_sum[r];
+  }
+  for (int t = t0; t < tiles_n; ++t) {
+    const float2 v = part[(int64_t)t * part_ld + r];
+    const float nm = fmaxf(m, v.x);
+    s = s * expf(m - nm) + v.y * expf(v.x - nm);
+    m = nm;
+  }
+  run_max[r] = m;
+  run_sum[r] = s;
+}
+
 // ---------------------------------------------------------------------------- workspace plan
 struct TcPlan {
   int64_t rows_tile, vc, ldn;  // ldn: row stride of the [C][N] transposed activations
   size_t es;                   // operand element size
-  size_t X_hi, X_lo, XT_hi, XT_lo, W_hi, W_lo, WT_hi, WT_lo, dl_hi, dl_lo, dlT_hi, dlT_lo, total;
+  size_t X_hi, X_lo, XT_hi, XT_lo, W_hi, W_lo, WT_hi, WT_lo, dl_hi, dl_lo, dlT_hi, dlT_lo, part, total;
+  int64_t part_ld;
 };
 
 inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -607,6 +786,10 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   p.dl_lo = bf16 ? p.dl_hi : take((size_t)p.rows_tile * ldc);
   p.dlT_hi = take((size_t)p.vc * ldr);
   p.dlT_lo = bf16 ? p.dlT_hi : take((size_t)p.vc * ldr);
+  // per (128-column tile, row) partial softmax statistics of one panel
+  p.part_ld = ldr;
+  p.part = off;
+  off += up256((size_t)((p.vc + 127) / 128) * ldr * sizeof(float2));
   p.total = off;
   return p;
 }
@@ -671,24 +854,57 @@ int ag_flce_tc_logits(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int6
   return tc_gemm(ctx, bf16, A, B, panel, ld, rows, vc, d->C, false);
 }
 
+int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0,
+                             int vc, const int32_t* targets, float* run_max, float* run_sum, float* tgt_logit,
+                             bool first_panel) {
+  const TcPlan p = tc_plan(d);
+  unsigned char* b = static_cast<unsigned char*>(tc_scratch);
+  const bool bf16 = d->precision == AG_CE_BF16;
+  const size_t row_bytes = (size_t)d->C * p.es;
+  TcOperand A{b + p.X_hi + (size_t)r0 * row_bytes, b + p.X_lo + (size_t)r0 * row_bytes, d->C};
+  TcOperand B{b + p.W_hi + (size_t)v0 * row_bytes, b + p.W_lo + (size_t)v0 * row_bytes, d->C};
+  TcParams e = {};
+  e.targets = targets + r0;
+  e.v0 = v0;
+  e.V = d->V;
+  e.part = reinterpret_cast<float2*>(b + p.part);
+  e.part_ld = p.part_ld;
+  e.tgt_logit = tgt_logit + r0;
+  int tiles_n = 0;
+  int rc = tc_gemm(ctx, bf16, A, B, nullptr, 0, rows, vc, d->C, false, EPI_STATS, &e, &tiles_n);
+  if (rc) return rc;
+  ce_merge_partials_kernel<<<(rows + 255) / 256, 256, 0, ctx->stream>>>(e.part, e.part_ld, tiles_n, rows, run_max + r0,
+                                                                      run_sum + r0, first_panel ? 1 : 0);
+  AG_LAUNCHED(ctx, "ce_merge_partials_kernel");
+  return AG_OK;
+}
+
 int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
-                     const float* panel, int64_t ld, const int32_t* targets, const float* lse, const float* row_scale,
-                     const float* dloss, const float* denom, float* dX, float* dW) {
+                     const int32_t* targets, const float* lse, const float* row_scale, const float* dloss,
+                     const float* denom, float* dX, float* dW) {
   const TcPlan p = tc_plan(d);
   unsigned char* b = static_cast<unsigned char*>(tc_scratch);
   const bool bf16 = d->precision == AG_CE_BF16;
   const int64_t ldc = up8(p.vc), ldr = up8(p.rows_tile), ldv = up8(d->V);
-  dim3 grid((vc + 31) / 32, (rows + 31) / 32);
-  if (bf16)
-    dlogits_split_kernel<true><<<grid, dim3(32, 8), 0, ctx->stream>>>(
-        panel, ld, rows, vc, v0, targets + r0, lse + r0, row_scale ? row_scale + r0 : nullptr, dloss, denom, d->V,
-        d->ignore_mode, b + p.dl_hi, b + p.dl_lo, ldc, b + p.dlT_hi, b + p.dlT_lo, ldr);
-  else
-    dlogits_split_kernel<false><<<grid, dim3(32, 8), 0, ctx->stream>>>(
-        panel, ld, rows, vc, v0, targets + r0, lse + r0, row_scale ? row_scale + r0 : nullptr, dloss, denom, d->V,
-        d->ignore_mode, b + p.dl_hi, b + p.dl_lo, ldc, b + p.dlT_hi, b + p.dlT_lo, ldr);
-  AG_LAUNCHED(ctx, "dlogits_split_kernel");
+  const size_t row_bytes = (size_t)d->C * p.es;
   int rc;
+  {
+    // logits panel recomputed on the tensor cores; its epilogue writes dlogits in operand form
+    TcOperand A{b + p.X_hi + (size_t)r0 * row_bytes, b + p.X_lo + (size_t)r0 * row_bytes, d->C};
+    TcOperand B{b + p.W_hi + (size_t)v0 * row_bytes, b + p.W_lo + (size_t)v0 * row_bytes, d->C};
+    TcParams e = {};
+    e.targets = targets + r0;
+    e.v0 = v0;
+    e.V = d->V;
+    e.lse = lse + r0;
+    e.row_scale = row_scale ? row_scale + r0 : nullptr;
+    e.dloss = dloss;
+    e.denom = denom;
+    e.ignore_mode = d->ignore_mode;
+    e.dl_hi = b + p.dl_hi; e.dl_lo = b + p.dl_lo; e.ld_dl = ldc;
+    e.dlT_hi = b + p.dlT_hi; e.dlT_lo = b + p.dlT_lo; e.ld_dlT = ldr;
+    if ((rc = tc_gemm(ctx, bf16, A, B, nullptr, 0, rows, vc, d->C, false, EPI_DLOGITS, &e))) return rc;
+  }
   if (dX) {
     // dX[r0:r0+rows, :] += dl [rows, vc] . (W^T [C, v0:v0+vc])^T
     TcOperand A{b + p.dl_hi, b + p.dl_lo, ldc};
