@@ -195,6 +195,12 @@ __device__ __forceinline__ void ag_bulk_g2s(void* dst_smem, const void* src, uin
       : "memory");
 }
 
+// Ask the copy engine to pull `bytes` (multiple of 16, 16-byte aligned) into L2; no registers or
+// shared memory are tied up and nothing waits on it.
+__device__ __forceinline__ void ag_prefetch_l2_bulk(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // Stage up to two fp32 vectors of n floats each (src1 may be null) into shared memory
 // through the bulk-copy engine when alignment allows, else with plain loads.  Called by all
 // threads of the CTA; returns after a __syncthreads() with the data visible.

@@ -173,9 +173,13 @@ struct GeluBwd {
 __global__ void __launch_bounds__(EW_THREADS) gelu_backward_kernel(GeluBwd f, int64_t n) { ew_drive<4>(n, f); }
 
 // ---------------------------------------------------------------------------- SwiGLU
+// backend.py:1117-1120: 1 / (exp(-g) + 1).  FAST=false: accurate expf and a correctly rounded
+// reciprocal (bit-identical to the IEEE division 1/x, fewer instructions).  FAST=true (bf16
+// storage, tolerance 2e-2): ex2-based __expf; at 8 values per 16-byte packet the accurate
+// version would make the kernel instruction-bound instead of HBM-bound.
+template <bool FAST>
 __device__ __forceinline__ float sigmoid_ref(float g) {
-  // backend.py:1117-1120: 1 / (exp(-g) + 1)
-  return 1.0f / (expf(-g) + 1.0f);
+  return __frcp_rn((FAST ? __expf(-g) : expf(-g)) + 1.0f);
 }
 
 // One thread handles packets of the same column range in the gate and up halves of a row.
@@ -204,7 +208,7 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_forward_kernel(const T* __r
     for (int k = 0; k < 2; ++k) {
       if (live[k]) {
 #pragma unroll
-        for (int e = 0; e < NV; ++e) g[k][e] = (g[k][e] * sigmoid_ref(g[k][e])) * u[k][e];
+        for (int e = 0; e < NV; ++e) g[k][e] = (g[k][e] * sigmoid_ref<(NV > 4)>(g[k][e])) * u[k][e];
         Pack<T>::store(hidden + (i + k * stride) * NV, g[k]);
       }
     }
@@ -221,13 +225,14 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_forward_scalar_kernel(const
     const int col = (int)(i - row * I);
     const float g = Pack<T>::load1(gu + row * 2 * I + col);
     const float u = Pack<T>::load1(gu + row * 2 * I + I + col);
-    Pack<T>::store1(hidden + i, (g * sigmoid_ref(g)) * u);
+    Pack<T>::store1(hidden + i, (g * sigmoid_ref<false>(g)) * u);
   }
 }
 
+template <bool FAST>
 __device__ __forceinline__ void swiglu_bwd1(float g, float u, float dh, float& dg, float& du) {
   // backend.py:1202-1217
-  const float s = sigmoid_ref(g);
+  const float s = sigmoid_ref<FAST>(g);
   float t = 1.0f - s;
   t = t * g;
   t = t + 1.0f;
@@ -267,7 +272,7 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_backward_kernel(T* __restri
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
           float dg, du;
-          swiglu_bwd1(g[k][e], u[k][e], d[k][e], dg, du);
+          swiglu_bwd1<(NV > 4)>(g[k][e], u[k][e], d[k][e], dg, du);
           g[k][e] = dg;
           u[k][e] = du;
         }
@@ -291,7 +296,7 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_backward_scalar_kernel(T* _
     const float g = Pack<T>::load1(pg);
     const float u = Pack<T>::load1(pg + I);
     float dg, du;
-    swiglu_bwd1(g, u, Pack<T>::load1(dh + i), dg, du);
+    swiglu_bwd1<false>(g, u, Pack<T>::load1(dh + i), dg, du);
     Pack<T>::store1(pg, dg);
     Pack<T>::store1(pg + I, du);
   }

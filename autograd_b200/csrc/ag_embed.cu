@@ -259,28 +259,35 @@ scatter_combine_kernel(const uint32_t* __restrict__ keys, float* dtable, const f
   if (start == g0 && g0 > 0 && keys[g0 - 1] == key) return;  // a continuation, an earlier group is the head
   const int head_slot = (start == g0) ? 0 : 1;
 
+  // number of following groups whose first run continues this segment (same for every thread;
+  // found by binary search over the sorted keys: the last entry of the segment)
+  int64_t lo_i = last, hi_i = n - 1;
+  while (lo_i < hi_i) {
+    const int64_t mid = (lo_i + hi_i + 1) >> 1;
+    if (keys[mid] == key) lo_i = mid; else hi_i = mid - 1;
+  }
+  const int64_t g_end = lo_i / SEG_GROUP;  // last group that holds entries of this segment
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
   float* drow = dtable + (int64_t)key * C;
   if (VEC) {
     if (col >= C) return;
     float4 acc = *reinterpret_cast<const float4*>(drow + col);
     acc = f4_add(acc, *reinterpret_cast<const float4*>(partials + (grp * 2 + head_slot) * C + col));
-    for (int64_t g = grp + 1; g < n_groups; ++g) {
-      if (keys[g * SEG_GROUP] != key) break;
-      acc = f4_add(acc, *reinterpret_cast<const float4*>(partials + (g * 2 + 0) * C + col));
-      const int64_t glast = g * SEG_GROUP + SEG_GROUP - 1;
-      if (glast >= n || keys[glast] != key) break;  // the segment ends inside group g
+    int64_t g = grp + 1;
+    // loads of 8 partial rows are independent and in flight together; the adds stay in group order
+    for (; g + 8 <= g_end + 1; g += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(partials + ((g + u) * 2 + 0) * C + col));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc = f4_add(acc, v[u]);
     }
+    for (; g <= g_end; ++g) acc = f4_add(acc, *reinterpret_cast<const float4*>(partials + (g * 2 + 0) * C + col));
     *reinterpret_cast<float4*>(drow + col) = acc;
   } else {
     for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
       float acc = drow[c] + partials[(grp * 2 + head_slot) * C + c];
-      for (int64_t g = grp + 1; g < n_groups; ++g) {
-        if (keys[g * SEG_GROUP] != key) break;
-        acc += partials[(g * 2 + 0) * C + c];
-        const int64_t glast = g * SEG_GROUP + SEG_GROUP - 1;
-        if (glast >= n || keys[glast] != key) break;
-      }
+      for (int64_t g = grp + 1; g <= g_end; ++g) acc += partials[(g * 2 + 0) * C + c];
       drow[c] = acc;
     }
   }

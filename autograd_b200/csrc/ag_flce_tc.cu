@@ -41,6 +41,9 @@ struct TcParams {
   int split;       // 1: operands come as (hi, lo) pairs and 3 MMAs are issued per k-step
   int stages;
   int tiles_m, tiles_n, k_iters;
+  int splits;      // split-K: each output tile is computed by `splits` CTAs over disjoint k ranges
+  int k_per_split; // k iterations per split (the last one may be shorter)
+  int64_t split_stride;  // elements between the partial outputs of consecutive splits
   int n_fastest;   // tile order
   uint32_t idesc;
   uint32_t a_bytes, b_bytes;  // bytes of one A / B tile in a stage
@@ -139,7 +142,13 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile
   return false;
 }
 
-__device__ __forceinline__ void tc_tile_coords(const TcParams& p, int tile, int& tm, int& tn) {
+__device__ __forceinline__ void tc_tile_coords(const TcParams& p, int tile, int& tm, int& tn, int& k_begin,
+                                               int& k_end, int& split) {
+  const int per_split = p.tiles_m * p.tiles_n;
+  split = tile / per_split;
+  tile -= split * per_split;
+  k_begin = split * p.k_per_split;
+  k_end = k_begin + p.k_per_split < p.k_iters ? k_begin + p.k_per_split : p.k_iters;
   if (p.n_fastest) {
     tm = tile / p.tiles_n;
     tn = tile - tm * p.tiles_n;
@@ -200,7 +209,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int total_tiles = p.tiles_m * p.tiles_n * p.splits;
   bool expired = false;
 
   if (warp == 0) {
@@ -208,10 +217,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !expired; tile += gridDim.x) {
-        int tm, tn;
-        tc_tile_coords(p, tile, tm, tn);
+        int tm, tn, k_begin, k_end, split_id;
+        tc_tile_coords(p, tile, tm, tn, k_begin, k_end, split_id);
         const int m0 = tm * TC_BM, n0 = tn * p.BN;
-        for (int k = 0; k < p.k_iters; ++k) {
+        for (int k = k_begin; k < k_end; ++k) {
           if (!tc_wait(&empty[stage], phase ^ 1u, abort_flag)) {
             expired = true;
             break;
@@ -250,7 +259,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
         acc_par[buf] ^= 1u;
         tc_fence_after();
         const uint32_t tacc = tmem_base + (uint32_t)buf * 256u;
-        for (int k = 0; k < p.k_iters; ++k) {
+        int tm, tn, k_begin, k_end, split_id;
+        tc_tile_coords(p, tile, tm, tn, k_begin, k_end, split_id);
+        for (int k = k_begin; k < k_end; ++k) {
           if (!tc_wait(&full[stage], phase, abort_flag)) {
             expired = true;
             break;
@@ -262,7 +273,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           const uint32_t b_lo = b_hi + p.b_bytes;
           for (int kk = 0; kk < k_sub; ++kk) {
             const uint32_t off = (uint32_t)kk * 32u;  // 32 bytes of K per MMA inside the 128-byte row
-            const uint32_t first = (k == 0 && kk == 0) ? 0u : 1u;
+            const uint32_t first = (k == k_begin && kk == 0) ? 0u : 1u;
             if (p.split) {
               tc_mma<TF32>(tacc, tc_smem_desc(a_hi + off), tc_smem_desc(b_lo + off), p.idesc, first);
               tc_mma<TF32>(tacc, tc_smem_desc(a_lo + off), tc_smem_desc(b_hi + off), p.idesc, 1u);
@@ -289,8 +300,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     const bool vec_ok = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
-      int tm, tn;
-      tc_tile_coords(p, tile, tm, tn);
+      int tm, tn, k_begin, k_end, split_id;
+      tc_tile_coords(p, tile, tm, tn, k_begin, k_end, split_id);
       const int m0 = tm * TC_BM, n0 = tn * p.BN;
       if (!tc_wait(&acc_full[buf], full_par[buf], abort_flag)) {
         expired = true;
@@ -301,7 +312,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       const int row = m0 + quarter * 32 + lane;
       const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 256u;
       if (EPI == EPI_STORE) {
-        float* drow = p.D + (int64_t)row * p.ldd;
+        float* drow = p.D + (int64_t)split_id * p.split_stride + (int64_t)row * p.ldd;
         for (int c0 = 0; c0 < p.BN; c0 += 32) {
           uint32_t r[32];
           tc_tmem_ld32(tacc + (uint32_t)c0, r);
@@ -509,6 +520,20 @@ int tc_encode(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int64_t 
 }
 
 // D[M,N] (+)= A[M,K] . B[N,K]^T on the tensor cores.
+// D[m][n] (+)= sum over splits, in split order, of the partial outputs P[s][m][n].
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ P, int splits, int M, int N, float* D, int64_t ldd, int accumulate) {
+  const int64_t total = (int64_t)M * N;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int m = (int)(i / N), n = (int)(i - (int64_t)m * N);
+    float* d = D + (int64_t)m * ldd + n;
+    float acc = accumulate ? *d : 0.0f;
+    for (int sp = 0; sp < splits; ++sp) acc += P[(int64_t)sp * total + i];
+    *d = acc;
+  }
+}
+
 template <bool TF32, int EPI>
 int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const CUtensorMap& a_lo,
               const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
@@ -525,34 +550,55 @@ int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const
 
 // `epi` (may be null = EPI_STORE) carries the fields of the fused cross-entropy epilogues.
 int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, float* D, int64_t ldd, int M, int N, int K,
-            bool accumulate, int epi_kind = EPI_STORE, const TcParams* epi = nullptr, int* tiles_n_out = nullptr) {
+            bool accumulate, int epi_kind = EPI_STORE, const TcParams* epi = nullptr, int* tiles_n_out = nullptr,
+            float* splitk_ws = nullptr, size_t splitk_ws_bytes = 0) {
   TcParams p;
   if (epi) p = *epi;
   p.M = M; p.N = N; p.K = K;
   p.BK = bf16 ? 64 : 32;
   p.umma_k = bf16 ? 16 : 8;
   p.split = bf16 ? 0 : 1;
-  // tile width: the widest tile whose last wave over the SMs is not mostly idle
+  // Tile width and split-K factor.  Measured behaviour of this kernel: a k-step costs time in
+  // proportion to the operand bytes it pulls through shared memory (128 + BN rows), a tile costs
+  // about 8 k-steps of prologue / epilogue on top, and CTAs work in rounds over the SMs.  Split-K
+  // is only considered for plain accumulate outputs with a workspace and few tiles.
   const int cand[] = {256, 192, 160, 128};
-  int best_bn = 128;
+  int best_bn = 128, best_s = 1;
   double best_cost = 1e300;
   const int tiles_m = (M + TC_BM - 1) / TC_BM;
+  const int k_iters_all = (K + p.BK - 1) / p.BK;
   for (int bn : cand) {
     const int tn = (N + bn - 1) / bn;
     const int64_t tiles = (int64_t)tiles_m * tn;
-    const int64_t waves = (tiles + ctx->sm_count - 1) / ctx->sm_count;
-    // time ~ waves * tile work, with a mild penalty for narrow tiles (more operand traffic per flop)
-    const double cost = (double)waves * bn * (1.0 + 16.0 / bn);
-    if (cost < best_cost) {
-      best_cost = cost;
-      best_bn = bn;
+    int s_max = 1;
+    if (epi_kind == EPI_STORE && splitk_ws && tiles < 2 * (int64_t)ctx->sm_count) {
+      s_max = k_iters_all / 16;
+      if (s_max > 16) s_max = 16;
+      const int64_t fit = (int64_t)(splitk_ws_bytes / ((size_t)M * N * sizeof(float)));
+      if (s_max > fit) s_max = (int)fit;
+      if (s_max < 1) s_max = 1;
+    }
+    for (int sp = 1; sp <= s_max; ++sp) {
+      const int k_per = (k_iters_all + sp - 1) / sp;
+      const int s_eff = (k_iters_all + k_per - 1) / k_per;
+      const int64_t rounds = (tiles * s_eff + ctx->sm_count - 1) / ctx->sm_count;
+      double cost = (double)rounds * (k_per + 8) * (128 + bn);
+      if (s_eff > 1) cost += 0.02 * cost;  // the ordered reduction of the partial outputs
+      if (cost < best_cost) {
+        best_cost = cost;
+        best_bn = bn;
+        best_s = s_eff;
+      }
     }
   }
   p.BN = best_bn;
   p.tiles_m = tiles_m;
   p.tiles_n = (N + p.BN - 1) / p.BN;
   if (tiles_n_out) *tiles_n_out = p.tiles_n;
-  p.k_iters = (K + p.BK - 1) / p.BK;
+  p.k_iters = k_iters_all;
+  p.k_per_split = (p.k_iters + best_s - 1) / best_s;
+  p.splits = (p.k_iters + p.k_per_split - 1) / p.k_per_split;
+  p.split_stride = 0;
   p.a_bytes = (uint32_t)TC_BM * 128u;
   p.b_bytes = (uint32_t)p.BN * 128u;
   const uint32_t stage_bytes = (p.a_bytes + p.b_bytes) * (p.split ? 2u : 1u);
@@ -571,6 +617,12 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   const uint32_t fmt = bf16 ? 1u : 2u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
   p.D = D; p.ldd = ldd; p.accumulate = accumulate ? 1 : 0;
+  if (p.splits > 1) {  // partial outputs [splits][M][N] in the workspace, summed in order afterwards
+    p.D = splitk_ws;
+    p.ldd = N;
+    p.accumulate = 0;
+    p.split_stride = (int64_t)M * N;
+  }
   p.status = ctx->d_status;
 
   CUtensorMap tA_hi, tA_lo, tB_hi, tB_lo;
@@ -585,7 +637,7 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
     tB_lo = tB_hi;
   }
   const size_t smem = 1024 + (size_t)stages * stage_bytes + 256;
-  const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
+  const int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.splits;
   const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
   if (epi_kind == EPI_STATS) {
     AG_REQUIRE(ctx, p.part_ld >= M, "tc_gemm: partial-statistics rows too short");
@@ -595,8 +647,15 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   if (epi_kind == EPI_DLOGITS)
     return bf16 ? tc_launch<false, EPI_DLOGITS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
                 : tc_launch<true, EPI_DLOGITS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
-  return bf16 ? tc_launch<false, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
-              : tc_launch<true, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+  rc = bf16 ? tc_launch<false, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
+            : tc_launch<true, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+  if (rc || p.splits == 1) return rc;
+  const int64_t n4 = ((int64_t)M * N + 3) / 4;
+  int64_t want = (n4 + 255) / 256;
+  if (want > (int64_t)ctx->sm_count * 8) want = (int64_t)ctx->sm_count * 8;
+  splitk_reduce_kernel<<<(int)want, 256, 0, ctx->stream>>>(splitk_ws, p.splits, M, N, D, ldd, accumulate ? 1 : 0);
+  AG_LAUNCHED(ctx, "splitk_reduce_kernel");
+  return AG_OK;
 }
 
 // ---------------------------------------------------------------------------- operand preparation
@@ -757,7 +816,8 @@ ce_merge_partials_kernel(const float2* __restrict__ part, int64_t part_ld, int t
 struct TcPlan {
   int64_t rows_tile, vc, ldn;  // ldn: row stride of the [C][N] transposed activations
   size_t es;                   // operand element size
-  size_t X_hi, X_lo, XT_hi, XT_lo, W_hi, W_lo, WT_hi, WT_lo, dl_hi, dl_lo, dlT_hi, dlT_lo, part, total;
+  size_t X_hi, X_lo, XT_hi, XT_lo, W_hi, W_lo, WT_hi, WT_lo, dl_hi, dl_lo, dlT_hi, dlT_lo, part, splitk, splitk_bytes,
+      total;
   int64_t part_ld;
 };
 
@@ -790,6 +850,10 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   p.part_ld = ldr;
   p.part = off;
   off += up256((size_t)((p.vc + 127) / 128) * ldr * sizeof(float2));
+  // split-K partial outputs of the dW panel GEMM (vc x C), up to 16 splits
+  p.splitk = off;
+  p.splitk_bytes = up256((size_t)16 * p.vc * d->C * sizeof(float));
+  off += p.splitk_bytes;
   p.total = off;
   return p;
 }
@@ -915,7 +979,9 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
     // dW[v0:v0+vc, :] += dl^T [vc, rows] . (X^T [C, r0:r0+rows])^T
     TcOperand A{b + p.dlT_hi, b + p.dlT_lo, ldr};
     TcOperand B{b + p.XT_hi + (size_t)r0 * p.es, b + p.XT_lo + (size_t)r0 * p.es, p.ldn};
-    if ((rc = tc_gemm(ctx, bf16, A, B, dW + (int64_t)v0 * d->C, d->C, vc, d->C, rows, true))) return rc;
+    if ((rc = tc_gemm(ctx, bf16, A, B, dW + (int64_t)v0 * d->C, d->C, vc, d->C, rows, true, EPI_STORE, nullptr, nullptr,
+                      reinterpret_cast<float*>(b + p.splitk), p.splitk_bytes)))
+      return rc;
   }
   return AG_OK;
 }

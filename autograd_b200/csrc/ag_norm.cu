@@ -249,6 +249,17 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     const T* xr = x + row * C;
     const T* gr = dy + row * C;
     const T* drr = (dres && dx) ? dres + row * C : nullptr;
+    {
+      // the rows this warp will visit next are requested into L2 now, so that their loads meet a
+      // short latency: with one resident CTA per SM at wide rows there are few warps to hide HBM
+      const int64_t nxt = row + (int64_t)gridDim.x * NORM_WARPS;
+      if (lane == 0 && nxt < N) {
+        const uint32_t rb = (uint32_t)C * (uint32_t)sizeof(T);
+        ag_prefetch_l2_bulk(x + nxt * C, rb);
+        ag_prefetch_l2_bulk(dy + nxt * C, rb);
+        if (drr) ag_prefetch_l2_bulk(dres + nxt * C, rb);
+      }
+    }
 #pragma unroll
     for (int p = 0; p < KP; ++p) {
       const int col = (p * 32 + lane) * NV;

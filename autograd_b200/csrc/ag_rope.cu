@@ -1,77 +1,74 @@
 // Rotate-half RoPE applied in place to q (B,T,H,D) and k (B,T,HKV,D).
 //
-// One CTA handles one token (b,t).  A thread owns one 16-byte packet of the low half of a head
-// together with the matching packet of the high half, so both halves are read once and written
-// once; its cos/sin entries come straight from the (L2-resident) tables.  All loads of a thread
-// are issued in one burst before the first store: there is no shared-memory stage and no
-// barrier in the kernel.  Shapes where D/2 is not a multiple of the packet width use a scalar
+// The (token, head, packet) space is flattened and dealt out to CTAs in contiguous slabs.  A
+// thread owns one 16-byte packet of the low half of a head together with the matching packet of
+// the high half, so both halves are read once and written once; its cos/sin entries come
+// straight from the (L2-resident) tables.  All loads of a thread (four packet pairs) are issued
+// in one burst before the first store: there is no shared-memory stage and no barrier.  Shapes where D/2 is not a multiple of the packet width use a scalar
 // kernel.
 #include "ag_common.cuh"
 
 namespace {
 
 constexpr int ROPE_THREADS = 256;
-constexpr int ROPE_MAX_ITEMS = 4;  // packets pairs per thread kept in flight
+constexpr int ROPE_MAX_BYTES = 64;  // bytes of each half a thread keeps in flight (4 fp32 / 2 bf16 packets)
 
 template <typename T>
 __global__ void __launch_bounds__(ROPE_THREADS)
-rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int T_len, int H, int HKV,
-            int D, int64_t q_stride, int64_t k_stride, float sgn) {
+rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int64_t tokens, int T_len,
+            int H, int HKV, int D, int64_t q_stride, int64_t k_stride, float sgn) {
   constexpr int NV = Pack<T>::N;
+  constexpr int ROPE_MAX_ITEMS = ROPE_MAX_BYTES / 16 * 4 / NV;  // 4 packet pairs for fp32, 2 for bf16
   const int d2 = D >> 1;
-  const int64_t tok = blockIdx.x;  // b*T + t
-  const int t = (int)(tok % T_len);
-  const int ppd = d2 / NV;              // packets per half head
-  const int items = (H + HKV) * ppd;    // packet pairs of this token
-  T* qt = q + tok * q_stride;
-  T* kt = k ? k + tok * k_stride : nullptr;
-  const float* crow = cos_tab + (int64_t)t * d2;
-  const float* srow = sin_tab + (int64_t)t * d2;
-
-  const int nthreads = blockDim.x;
-  for (int base = threadIdx.x; base < items; base += nthreads * ROPE_MAX_ITEMS) {
-    float lo[ROPE_MAX_ITEMS][NV], hi[ROPE_MAX_ITEMS][NV], c[ROPE_MAX_ITEMS][NV], s[ROPE_MAX_ITEMS][NV];
-    T* ptr[ROPE_MAX_ITEMS];
-    // every load of this thread - activations and the table entries (L2-resident, the table is
-    // T*D/2 floats) - is issued before the first dependent use
+  const int ppd = d2 / NV;                     // packets per half head
+  const int items = (H + HKV) * ppd;           // packet pairs per token
+  const int64_t total = tokens * items;        // packet pairs of the whole call, token-major
+  // A CTA covers ROPE_THREADS * ROPE_MAX_ITEMS consecutive packet pairs; a thread takes every
+  // ROPE_THREADS-th of them, so a warp touches 32 consecutive packets (512 contiguous bytes per
+  // half) and every thread has ROPE_MAX_ITEMS independent load groups in flight.
+  const int64_t base = (int64_t)blockIdx.x * (ROPE_THREADS * ROPE_MAX_ITEMS) + threadIdx.x;
+  float lo[ROPE_MAX_ITEMS][NV], hi[ROPE_MAX_ITEMS][NV], c[ROPE_MAX_ITEMS][NV], s[ROPE_MAX_ITEMS][NV];
+  T* ptr[ROPE_MAX_ITEMS];
 #pragma unroll
-    for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
-      const int it = base + u * nthreads;
-      ptr[u] = nullptr;
-      if (it < items) {
-        const int head = it / ppd;
-        const int col = (it - head * ppd) * NV;
-        T* hp = head < H ? qt + (int64_t)head * D : (kt ? kt + (int64_t)(head - H) * D : nullptr);
-        if (hp) {
-          ptr[u] = hp + col;
-          Pack<T>::load(ptr[u], lo[u]);
-          Pack<T>::load(ptr[u] + d2, hi[u]);
+  for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
+    const int64_t g = base + (int64_t)u * ROPE_THREADS;
+    ptr[u] = nullptr;
+    if (g < total) {
+      const int64_t tok = g / items;
+      const int it = (int)(g - tok * items);
+      const int head = it / ppd;
+      const int col = (it - head * ppd) * NV;
+      const int t = (int)(tok % T_len);
+      T* hp = head < H ? q + tok * q_stride + (int64_t)head * D : k + tok * k_stride + (int64_t)(head - H) * D;
+      ptr[u] = hp + col;
+      Pack<T>::load(ptr[u], lo[u]);
+      Pack<T>::load(ptr[u] + d2, hi[u]);
+      const float* crow = cos_tab + (int64_t)t * d2 + col;   // L2-resident tables (T * D/2 floats)
+      const float* srow = sin_tab + (int64_t)t * d2 + col;
 #pragma unroll
-          for (int e = 0; e < NV; e += 4) {
-            const float4 cv = __ldg(reinterpret_cast<const float4*>(crow + col + e));
-            const float4 sv = __ldg(reinterpret_cast<const float4*>(srow + col + e));
-            c[u][e] = cv.x; c[u][e + 1] = cv.y; c[u][e + 2] = cv.z; c[u][e + 3] = cv.w;
-            s[u][e] = sv.x; s[u][e + 1] = sv.y; s[u][e + 2] = sv.z; s[u][e + 3] = sv.w;
-          }
-        }
+      for (int e = 0; e < NV; e += 4) {
+        const float4 cv = __ldg(reinterpret_cast<const float4*>(crow + e));
+        const float4 sv = __ldg(reinterpret_cast<const float4*>(srow + e));
+        c[u][e] = cv.x; c[u][e + 1] = cv.y; c[u][e + 2] = cv.z; c[u][e + 3] = cv.w;
+        s[u][e] = sv.x; s[u][e + 1] = sv.y; s[u][e + 2] = sv.z; s[u][e + 3] = sv.w;
       }
     }
+  }
 #pragma unroll
-    for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
-      if (ptr[u]) {
-        float olo[NV], ohi[NV];
+  for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
+    if (ptr[u]) {
+      float olo[NV], ohi[NV];
 #pragma unroll
-        for (int e = 0; e < NV; ++e) {
-          const float cc = c[u][e];
-          const float ss = sgn * s[u][e];
-          // sgn=+1: lo*c - hi*s , lo*s + hi*c   (backend.py:1413-1414)
-          // sgn=-1: lo*c + hi*s , -lo*s + hi*c  (backend.py:1396-1397)
-          olo[e] = lo[u][e] * cc - hi[u][e] * ss;
-          ohi[e] = lo[u][e] * ss + hi[u][e] * cc;
-        }
-        Pack<T>::store(ptr[u], olo);
-        Pack<T>::store(ptr[u] + d2, ohi);
+      for (int e = 0; e < NV; ++e) {
+        const float cc = c[u][e];
+        const float ss = sgn * s[u][e];
+        // sgn=+1: lo*c - hi*s , lo*s + hi*c   (backend.py:1413-1414)
+        // sgn=-1: lo*c + hi*s , -lo*s + hi*c  (backend.py:1396-1397)
+        olo[e] = lo[u][e] * cc - hi[u][e] * ss;
+        ohi[e] = lo[u][e] * ss + hi[u][e] * cc;
       }
+      Pack<T>::store(ptr[u], olo);
+      Pack<T>::store(ptr[u] + d2, ohi);
     }
   }
 }
@@ -109,14 +106,11 @@ int rope_t(ag_ctx* ctx, void* qv, void* kv, const float* cos_tab, const float* s
   const bool vec_ok = (d2 % NV == 0) && ag_aligned16(q) && ag_aligned16(k) && (qs % NV == 0) && (ks % NV == 0) &&
                       ag_aligned16(cos_tab) && ag_aligned16(sin_tab);
   if (vec_ok) {
-    // block size such that every thread owns the same number of packet pairs (e.g. 20 heads x 16
-    // packets = 320 pairs -> 160 threads x 2, not 256 threads of which 64 do double work)
-    const int items = (H + (k ? HKV : 0)) * (d2 / NV);
-    const int per_thread = (items + ROPE_THREADS - 1) / ROPE_THREADS;
-    int threads = ((items + per_thread - 1) / per_thread + 31) / 32 * 32;
-    if (threads > ROPE_THREADS) threads = ROPE_THREADS;
-    rope_kernel<T><<<(unsigned)tokens, threads, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H, k ? HKV : 0, D,
-                                                                       qs, ks, sgn);
+    const int hkv = k ? HKV : 0;
+    const int64_t total = tokens * (int64_t)((H + hkv) * (d2 / NV));
+    const int64_t per_cta = (int64_t)ROPE_THREADS * (ROPE_MAX_BYTES / 16 * 4 / NV);
+    rope_kernel<T><<<(unsigned)((total + per_cta - 1) / per_cta), ROPE_THREADS, 0, ctx->stream>>>(
+        q, k, cos_tab, sin_tab, tokens, T_len, H, hkv, D, qs, ks, sgn);
     AG_LAUNCHED(ctx, "rope_kernel");
   } else {
     rope_scalar_kernel<T><<<(unsigned)tokens, ROPE_THREADS, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H,

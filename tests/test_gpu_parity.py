@@ -465,6 +465,35 @@ def test_flce_mid_size_vs_oracle(N, C, V, precision):
     G.check_clean_status()
 
 
+@pytest.mark.parametrize("C", [384, 1280])
+def test_flce_config2_full_size(C):
+    """Config 2 at full size: 16384 tokens, vocab 32768, chunk 4096, 5 % ignored, 3xTF32 tensor-core
+    panels against the numpy oracle on the same seeded inputs; plus size-independent properties:
+    rows of dX for ignored tokens are exactly zero, every dlogits row sums to zero so that
+    sum_v dW[v,:] equals -sum over nothing (checked as column sums of dW against X^T . rowsum = 0)."""
+    ctx, alloc, be = G.env()
+    N, V = 16384, 32768
+    rng = np.random.default_rng(1235 + C)
+    X_ = (rng.standard_normal((1, N, C)) / np.sqrt(C)).astype(np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C))).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(1, N)).astype(np.int32)
+    Y_[rng.random((1, N)) < 0.05] = -1
+    ref = O.flce_masked(X_[0], W_, Y_[0])
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, 1, ignore_mode=0, chunk=4096)
+    assert abs(loss - float(ref["loss"])) <= TOL_FWD * abs(loss)
+    assert_close(dX[0], ref["dX"], TOL_BWD, "dX")
+    assert_close(dW, ref["dW"], TOL_BWD, "dW")
+    ignored = Y_[0] < 0
+    assert ignored.sum() > 500 and not dX[0][ignored].any()
+    # softmax - onehot sums to zero over the vocabulary for every valid row: the column sums of dW vanish
+    col = dW.astype(np.float64).sum(axis=0)
+    assert np.max(np.abs(col)) <= 1e-4 * np.sqrt(np.mean(dW.astype(np.float64) ** 2)) * np.sqrt(V)
+    # mean over valid rows = mean over all rows * N / N_valid (integer bookkeeping of the ignore mask)
+    loss_v, _, _ = _run_flce(be, X_, W_, Y_, 1, ignore_mode=0, reduction=1, chunk=4096)
+    assert abs(loss_v - loss * N / int((~ignored).sum())) <= 1e-5 * abs(loss_v)
+    G.check_clean_status()
+
+
 @pytest.mark.parametrize("N,C,V", [(2048, 384, 8192), (1000, 1280, 4104)])
 def test_flce_bf16_mode_vs_oracle(N, C, V):
     """The stated bf16 tensor-core mode of the CE GEMMs: 2e-2 against the fp32 oracle run on the
