@@ -6,7 +6,7 @@
 //   warp 1      : allocates TMEM, then one elected lane issues tcgen05.mma (cta_group::1,
 //                 M = 128, N = BN) from shared-memory descriptors into one of two TMEM
 //                 accumulators; tcgen05.commit releases stages and publishes accumulators;
-//   warps 2..5  : epilogue - tcgen05.ld of the finished accumulator (one TMEM lane = one output
+//   warps 2..9  : epilogue - tcgen05.ld of the finished accumulator (one TMEM lane = one output
 //                 row per thread), store / accumulate to global memory, while the MMA warp
 //                 already works on the next tile in the other accumulator.
 // Precision modes:
@@ -28,7 +28,7 @@
 namespace {
 
 constexpr int TC_BM = 128;
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 constexpr int TC_MAX_STAGES = 6;
 constexpr int TC_SMEM_LIMIT = 227 * 1024;
@@ -192,7 +192,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       ag_mbar_init(&acc_full[b], 1);
-      ag_mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      ag_mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     ag_fence_mbar_init();
@@ -293,8 +293,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps share each TMEM lane quarter and take alternate 32-column chunks of the tile: the
+    // epilogues run one warp per scheduler, so their latency is exposed and more warps hide it.
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are this warp's
+    const int half = (warp - 2) >> 2;
+    const int c_first = half * 32;
     uint32_t full_par[2] = {0, 0};
     int local = 0;
     const bool vec_ok = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
@@ -313,7 +317,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 256u;
       if (EPI == EPI_STORE) {
         float* drow = p.D + (int64_t)split_id * p.split_stride + (int64_t)row * p.ldd;
-        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        for (int c0 = c_first; c0 < p.BN; c0 += 64) {
           uint32_t r[32];
           tc_tmem_ld32(tacc + (uint32_t)c0, r);
           tc_tmem_ld_wait();
@@ -346,7 +350,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
         // (max, sum exp) of this row over the tile's columns, straight from TMEM: two sweeps
         const int tcol = row < p.M ? p.targets[row] - p.v0 : -1;  // panel-relative target column
         float mx = -INFINITY;
-        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        for (int c0 = c_first; c0 < p.BN; c0 += 64) {
           uint32_t r[32];
           tc_tmem_ld32(tacc + (uint32_t)c0, r);
           tc_tmem_ld_wait();
@@ -356,7 +360,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             if (col + j < p.N) mx = fmaxf(mx, __uint_as_float(r[j]));
         }
         float sum = 0.0f, tl = 0.0f;
-        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        bool have_t = false;
+        for (int c0 = c_first; c0 < p.BN; c0 += 64) {
           uint32_t r[32];
           tc_tmem_ld32(tacc + (uint32_t)c0, r);
           tc_tmem_ld_wait();
@@ -365,14 +370,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           for (int j = 0; j < 32; ++j) {
             if (col + j < p.N) {
               const float v = __uint_as_float(r[j]);
-              sum += expf(v - mx);
-              if (col + j == tcol) tl = v;
+              sum += __expf(v - mx);
+              if (col + j == tcol) { tl = v; have_t = true; }
             }
           }
         }
         if (row < p.M) {
-          p.part[(int64_t)tn * p.part_ld + row] = make_float2(mx, sum);
-          if (tcol >= n0 && tcol < n0 + p.BN && tcol < p.N) p.tgt_logit[row] = tl;
+          // a half that saw no valid column (narrow last tile) contributes (max -inf, sum 0)
+          p.part[(int64_t)(tn * 2 + half) * p.part_ld + row] = make_float2(mx, sum);
+          if (have_t) p.tgt_logit[row] = tl;
         }
       } else {
         // dlogits of this row, written in operand form: dl (row-major) and dl^T
@@ -387,7 +393,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           tcol = valid ? t - p.v0 : -1;
         }
         const bool row_vec = ((p.ld_dl & 7) == 0);
-        for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        for (int c0 = c_first; c0 < p.BN; c0 += 64) {
           uint32_t r[32];
           tc_tmem_ld32(tacc + (uint32_t)c0, r);
           tc_tmem_ld_wait();
@@ -398,7 +404,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           for (int j = 0; j < 32; ++j) {
             float d = 0.0f;
             if (sc != 0.0f) {
-              float pr = expf(__uint_as_float(r[j]) - e);
+              float pr = __expf(__uint_as_float(r[j]) - e);
               if (col + j == tcol) pr -= 1.0f;
               d = pr * sc;
             }
@@ -804,6 +810,7 @@ ce_merge_partials_kernel(const float2* __restrict__ part, int64_t part_ld, int t
   }
   for (int t = t0; t < tiles_n; ++t) {
     const float2 v = part[(int64_t)t * part_ld + r];
+    if (v.y == 0.0f) continue;  // an empty partial (max = -inf)
     const float nm = fmaxf(m, v.x);
     s = s * expf(m - nm) + v.y * expf(v.x - nm);
     m = nm;
@@ -846,10 +853,10 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   p.dl_lo = bf16 ? p.dl_hi : take((size_t)p.rows_tile * ldc);
   p.dlT_hi = take((size_t)p.vc * ldr);
   p.dlT_lo = bf16 ? p.dlT_hi : take((size_t)p.vc * ldr);
-  // per (128-column tile, row) partial softmax statistics of one panel
+  // per (column tile, epilogue half, row) partial softmax statistics of one panel
   p.part_ld = ldr;
   p.part = off;
-  off += up256((size_t)((p.vc + 127) / 128) * ldr * sizeof(float2));
+  off += up256((size_t)((p.vc + 127) / 128) * 2 * ldr * sizeof(float2));
   // split-K partial outputs of the dW panel GEMM (vc x C), up to 16 splits
   p.splitk = off;
   p.splitk_bytes = up256((size_t)16 * p.vc * d->C * sizeof(float));
@@ -937,7 +944,7 @@ int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratc
   int tiles_n = 0;
   int rc = tc_gemm(ctx, bf16, A, B, nullptr, 0, rows, vc, d->C, false, EPI_STATS, &e, &tiles_n);
   if (rc) return rc;
-  ce_merge_partials_kernel<<<(rows + 255) / 256, 256, 0, ctx->stream>>>(e.part, e.part_ld, tiles_n, rows, run_max + r0,
+  ce_merge_partials_kernel<<<(rows + 255) / 256, 256, 0, ctx->stream>>>(e.part, e.part_ld, tiles_n * 2, rows, run_max + r0,
                                                                       run_sum + r0, first_panel ? 1 : 0);
   AG_LAUNCHED(ctx, "ce_merge_partials_kernel");
   return AG_OK;
