@@ -36,11 +36,26 @@ norm_forward_kernel(const T* x, const T* r, const float* __restrict__ gamma,
   float* s_gamma = reinterpret_cast<float*>(smem_raw);
   float* s_beta = s_gamma + C;
   __shared__ __align__(8) uint64_t s_bar;
-  if (gamma) ag_stage_vectors(s_gamma, gamma, s_beta, (KIND == kLayerNorm) ? beta : nullptr, C, &s_bar, status);
-
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const float inv_c = 1.0f / (float)C;
+  // Narrow rows keep gamma/beta in registers (plain loads that overlap the first row's loads);
+  // wide rows stage them once per CTA in shared memory through the bulk-copy engine.
+  constexpr bool IN_REGS = KP <= 4;
+  float rg[IN_REGS ? KP : 1][NV], rb[IN_REGS ? KP : 1][NV];
+  if (IN_REGS) {
+#pragma unroll
+    for (int p = 0; p < (IN_REGS ? KP : 1); ++p) {
+      const int col = (p * 32 + lane) * NV;
+#pragma unroll
+      for (int e = 0; e < NV; ++e) {
+        rg[p][e] = (gamma && col < C) ? __ldg(gamma + col + e) : 1.0f;
+        rb[p][e] = (KIND == kLayerNorm && col < C) ? __ldg(beta + col + e) : 0.0f;
+      }
+    }
+  } else if (gamma) {
+    ag_stage_vectors(s_gamma, gamma, s_beta, (KIND == kLayerNorm) ? beta : nullptr, C, &s_bar, status);
+  }
 
   for (int64_t row = (int64_t)blockIdx.x * NORM_WARPS + warp; row < N; row += (int64_t)gridDim.x * NORM_WARPS) {
     float v[KP][NV];
@@ -122,8 +137,13 @@ norm_forward_kernel(const T* x, const T* r, const float* __restrict__ gamma,
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
           float t = v[p][e] * scale;
-          if (gamma) t = t * s_gamma[col + e];
-          if (KIND == kLayerNorm) t = t + s_beta[col + e];
+          if (IN_REGS) {
+            if (gamma) t = t * rg[p][e];
+            if (KIND == kLayerNorm) t = t + rb[p][e];
+          } else {
+            if (gamma) t = t * s_gamma[col + e];
+            if (KIND == kLayerNorm) t = t + s_beta[col + e];
+          }
           o[e] = t;
         }
         Pack<T>::store_stream(yr + col, o);
@@ -224,11 +244,21 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   float* s_gamma = reinterpret_cast<float*>(smem_raw);  // C floats
   float* s_acc = s_gamma + C;                           // NORM_WARPS * SLOTS * C floats
   __shared__ __align__(8) uint64_t s_bar;
-  if (gamma) ag_stage_vectors(s_gamma, gamma, nullptr, nullptr, C, &s_bar, status);
-
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const float inv_c = 1.0f / (float)C;
+  constexpr bool IN_REGS = KP <= 4;  // as in forward
+  float rg[IN_REGS ? KP : 1][NV];
+  if (IN_REGS) {
+#pragma unroll
+    for (int p = 0; p < (IN_REGS ? KP : 1); ++p) {
+      const int col = (p * 32 + lane) * NV;
+#pragma unroll
+      for (int e = 0; e < NV; ++e) rg[p][e] = (gamma && col < C) ? __ldg(gamma + col + e) : 1.0f;
+    }
+  } else if (gamma) {
+    ag_stage_vectors(s_gamma, gamma, nullptr, nullptr, C, &s_bar, status);
+  }
   float* my_g = s_acc + (size_t)warp * SLOTS * C;
   float* my_b = my_g + C;  // LayerNorm only
   // each lane zeroes exactly the columns it will accumulate into: no cross-lane hazard
@@ -331,7 +361,7 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
             v[p][e] = xh;
             agp[j] += g[p][e] * xh;
             if (KIND == kLayerNorm) abp[j] += g[p][e];
-            const float dg = gamma ? g[p][e] * s_gamma[col + e] : g[p][e];
+            const float dg = gamma ? g[p][e] * (IN_REGS ? rg[p][e] : s_gamma[col + e]) : g[p][e];
             g[p][e] = dg;
             s1 += dg;
             s2 += dg * xh;
@@ -491,12 +521,18 @@ inline int pick_kp(int packets_per_row) {
 
 // Persistent grid: exactly the number of CTAs that are resident at once (occupancy x SMs),
 // so that no partial second wave forms; fewer when there are not enough rows.
-inline int persistent_grid(const ag_ctx* ctx, int64_t N, int ctas_per_sm) {
+// When every warp would visit only a few rows, a resident-sized grid quantises badly (2.3 rows
+// per warp costs 3 iterations); then one CTA per 8 rows is launched instead and the hardware
+// scheduler fills SMs as CTAs retire.  `max_grid` bounds the grid where each CTA owns a partial row.
+inline int persistent_grid(const ag_ctx* ctx, int64_t N, int ctas_per_sm, int64_t max_grid = (1ll << 30)) {
   int64_t want = (N + NORM_WARPS - 1) / NORM_WARPS;
   if (ctas_per_sm < 1) ctas_per_sm = 1;
   if (ctas_per_sm > 8) ctas_per_sm = 8;
   int64_t cap = (int64_t)ctx->sm_count * ctas_per_sm;
-  return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+  if (want < 1) want = 1;
+  int64_t grid = want <= cap ? want : (want <= 6 * cap ? want : cap);
+  if (grid > max_grid) grid = max_grid > cap ? max_grid / cap * cap : max_grid;
+  return (int)grid;
 }
 
 // Resident CTAs per SM of one kernel instantiation at a given dynamic shared-memory size;
@@ -570,7 +606,7 @@ int launch_bwd_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, cons
   static size_t occ_smem = 0;
   const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
   if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
-  const int grid = persistent_grid(ctx, N, occ);
+  const int grid = persistent_grid(ctx, N, occ, max_partial_rows(ctx));
   kern<<<grid, NORM_THREADS, smem, ctx->stream>>>(dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, ctx->d_status);
   AG_LAUNCHED(ctx, "norm_backward_kernel");
   *grid_out = grid;
