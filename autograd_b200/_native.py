@@ -51,6 +51,8 @@ SIGNATURES = {
     "ag_pass_end_profiled": (_int, [_ctx, C.POINTER(_f32)]),
     "ag_event_record": (_int, [_ctx, _int]),
     "ag_event_elapsed": (_int, [_ctx, _int, _int, C.POINTER(_f32)]),
+    "ag_tc_timing": (_int, [_ctx, _int, _int]),
+    "ag_tc_timing_count": (_int, [_ctx]),
     "ag_alloc_host": (_int, [_ctx, _sz, C.POINTER(_ptr)]),
     "ag_free_host": (_int, [_ctx, _ptr]),
     "ag_fill_f32": (_int, [_ctx, _ptr, _f32, _i64]),

@@ -106,6 +106,13 @@ class CudaContext:
         self._check(lib.ag_event_elapsed(self._h, int(start_index), int(end_index), C.byref(ms)))
         return ms.value
 
+    def tc_timing(self, enable: bool, first_event_index: int = 0):
+        """Bracket every tensor-core GEMM launch of the CE head with pool events (see the header)."""
+        self._check(lib.ag_tc_timing(self._h, 1 if enable else 0, int(first_event_index)))
+
+    def tc_timing_count(self) -> int:
+        return int(lib.ag_tc_timing_count(self._h))
+
     def alloc_host(self, nbytes: int) -> int:
         out = C.c_void_p()
         self._check(lib.ag_alloc_host(self._h, int(nbytes), C.byref(out)))

@@ -23,6 +23,9 @@ struct ag_ctx {
   cudaEvent_t* ev_pool;  // ag_event_record / ag_event_elapsed
   int ev_pool_size;
   int64_t launches;
+  int tc_timing;        // ag_tc_timing: bracket tensor-core GEMM launches with pool events
+  int tc_timing_base;
+  int tc_timing_count;
   char err[512];
 };
 

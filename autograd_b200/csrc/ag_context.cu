@@ -205,6 +205,19 @@ extern "C" int ag_event_elapsed(ag_ctx* ctx, int start_index, int end_index, flo
   return AG_OK;
 }
 
+extern "C" int ag_tc_timing(ag_ctx* ctx, int enable, int first_event_index) {
+  if (!ctx) return AG_ERR_INVALID;
+  AG_REQUIRE(ctx, first_event_index >= 0, "ag_tc_timing: negative event index");
+  ctx->tc_timing = enable ? 1 : 0;
+  if (enable) {
+    ctx->tc_timing_base = first_event_index;
+    ctx->tc_timing_count = 0;
+  }
+  return AG_OK;
+}
+
+extern "C" int ag_tc_timing_count(const ag_ctx* ctx) { return ctx ? ctx->tc_timing_count : 0; }
+
 extern "C" int ag_alloc_host(ag_ctx* ctx, size_t bytes, void** out) {
   if (!ctx || !out) return AG_ERR_INVALID;
   *out = nullptr;

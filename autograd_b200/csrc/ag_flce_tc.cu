@@ -549,8 +549,14 @@ int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const
                                       TC_SMEM_LIMIT));
     attr_done = true;
   }
+  int rc_ev;
+  if (ctx->tc_timing && (rc_ev = ag_event_record(ctx, ctx->tc_timing_base + 2 * ctx->tc_timing_count))) return rc_ev;
   tc_gemm_kernel<TF32, EPI><<<grid, TC_THREADS, smem, ctx->stream>>>(a_hi, a_lo, b_hi, b_lo, p);
   AG_LAUNCHED(ctx, "tc_gemm_kernel");
+  if (ctx->tc_timing) {
+    if ((rc_ev = ag_event_record(ctx, ctx->tc_timing_base + 2 * ctx->tc_timing_count + 1))) return rc_ev;
+    ctx->tc_timing_count++;
+  }
   return AG_OK;
 }
 

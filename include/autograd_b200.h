@@ -79,6 +79,11 @@ int ag_pass_end_profiled(ag_ctx* ctx, float* ms);
  * returns the milliseconds between them. */
 int ag_event_record(ag_ctx* ctx, int index);
 int ag_event_elapsed(ag_ctx* ctx, int start_index, int end_index, float* ms);
+/* Per-launch timing of the tensor-core GEMM inside the fused linear+CE calls: while enabled,
+ * every launch of that kernel is bracketed by events first_event_index + 2*i (before) and
+ * + 2*i + 1 (after), i counting from 0 at the enabling call; ag_tc_timing_count returns i. */
+int ag_tc_timing(ag_ctx* ctx, int enable, int first_event_index);
+int ag_tc_timing_count(const ag_ctx* ctx);
 /* Pinned host memory for staging inputs (cudaHostAlloc / cudaFreeHost). */
 int ag_alloc_host(ag_ctx* ctx, size_t bytes, void** out);
 int ag_free_host(ag_ctx* ctx, void* ptr);
