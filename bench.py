@@ -380,7 +380,7 @@ def run_b200(a):
                         "peak_source": peaks["source"]}
         else:
             roofline = None
-        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+        traffic_path = os.path.join(ROOT, "bench_traffic.json")   # per-launch DRAM bytes read off the ncu summaries in profiles/
         if roofline is not None and os.path.exists(traffic_path):
             with open(traffic_path) as f:
                 tr = json.load(f).get(roofline["kernel"])
