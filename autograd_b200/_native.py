@@ -76,6 +76,9 @@ SIGNATURES = {
     "ag_flce_scratch_bytes": (_sz, [C.POINTER(FlceDesc)]),
     "ag_flce_forward": (_int, [_ctx, C.POINTER(FlceDesc), _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz]),
     "ag_flce_backward": (_int, [_ctx, C.POINTER(FlceDesc), _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz]),
+    "ag_linear_add_scratch_bytes": (_sz, [_i64, _int, _int, _int]),
+    "ag_linear_add_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _int, _int, _int, _ptr, _sz]),
+    "ag_linear_add_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _int, _int, _int, _ptr, _sz]),
     "ag_adamw_step": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _i64, _f64, _f64, _f64, _f64, _f64, _f64, _f64]),
 }
 

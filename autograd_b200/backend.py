@@ -76,6 +76,7 @@ class CudaBackend:
             "GatherOp": self._gather_forward,
             "FusedLinearCrossEntropyOp": self._flce_forward,
             "FusedRMSNormLinearCrossEntropyOp": self._rms_flce_forward,
+            "FusedLinearAddOp": self._linear_add_forward,
         }
         self._backward = {
             "LayerNormOp": self._layernorm_backward,
@@ -83,6 +84,7 @@ class CudaBackend:
             "GatherOp": self._gather_backward,
             "FusedLinearCrossEntropyOp": self._flce_backward,
             "FusedRMSNormLinearCrossEntropyOp": self._rms_flce_backward,
+            "FusedLinearAddOp": self._linear_add_backward,
         }
 
     # ------------------------------------------------------------------ Backend interface
@@ -347,6 +349,42 @@ class CudaBackend:
         dw = _addr(w.grad) if w.requires_grad else 0
         self._context.flce_backward(desc, _addr(x), _addr(w), _addr(targets), _addr(row_scale), _addr(out.grad),
                                     address_of(lse), dx, dw, sc, sc_bytes)
+
+    # ------------------------------------------------------------------ linear + bias + residual
+    def _linear_precision(self):
+        # the projection GEMMs are tensor-core only; the exact-fp32 CE mode maps to 3xTF32 here
+        return N.AG_CE_BF16 if self.ce_precision == N.AG_CE_BF16 else N.AG_CE_3XTF32
+
+    def _linear_add_forward(self, inputs, outputs, scratch=None):
+        """backend.py:2040-2058: out = act @ w + b + x (out may alias x)."""
+        x, act, w, b = inputs
+        out = outputs[0]
+        n, k = self._rows_cols(act)
+        c = w.shape[1]
+        prec = self._linear_precision()
+        sc, sc_bytes = self._slot(scratch, "linear_add", self._context.linear_add_scratch_bytes(n, k, c, prec))
+        self._context.linear_add_forward(_addr(x), _addr(act), _addr(w), _addr(b), _addr(out), n, k, c, prec, sc,
+                                         sc_bytes)
+
+    def _linear_add_backward(self, inputs, outputs, scratch=None):
+        """backend.py:2249-2259 (the branch whose `act` is still materialised)."""
+        x, act, w, b = inputs
+        out = outputs[0]
+        if out.grad is None:
+            return
+        if w.requires_grad and act.op is not None and getattr(act.op.op, "op_name", "") == "FusedRMSNormGQA":
+            raise NotImplementedError(
+                "FusedLinearAdd backward after FusedRMSNormGQA recomputes the attention output on the reference "
+                "CPU path (backend.py:2156-2245); attention is outside this backend")
+        n, k = self._rows_cols(act)
+        c = w.shape[1]
+        prec = self._linear_precision()
+        sc, sc_bytes = self._slot(scratch, "linear_add", self._context.linear_add_scratch_bytes(n, k, c, prec))
+        self._context.linear_add_backward(_addr(out.grad), _addr(act), _addr(w),
+                                          _addr(x.grad) if x.requires_grad else 0,
+                                          _addr(act.grad) if act.requires_grad else 0,
+                                          _addr(w.grad) if w.requires_grad else 0,
+                                          _addr(b.grad) if b.requires_grad else 0, n, k, c, prec, sc, sc_bytes)
 
     # ------------------------------------------------------------------ RMSNorm + linear + CE
     def _rms_flce_layout(self, n, c, v):

@@ -209,6 +209,19 @@ class CudaContext:
         self._check(lib.ag_flce_backward(self._h, C.byref(desc), _p(X), _p(W), _p(targets), _p(row_scale), _p(dloss),
                                          _p(lse), _p(dX), _p(dW), _p(scratch), int(scratch_bytes)))
 
+    @staticmethod
+    def linear_add_scratch_bytes(N_, K_, C_, precision=N.AG_CE_3XTF32):
+        return int(lib.ag_linear_add_scratch_bytes(int(N_), int(K_), int(C_), int(precision)))
+
+    def linear_add_forward(self, x, act, w, b, out, N_, K_, C_, precision, scratch, scratch_bytes):
+        self._check(lib.ag_linear_add_forward(self._h, _p(x), _p(act), _p(w), _p(b), _p(out), int(N_), int(K_), int(C_),
+                                              int(precision), _p(scratch), int(scratch_bytes)))
+
+    def linear_add_backward(self, dout, act, w, dx, dact, dw, db, N_, K_, C_, precision, scratch, scratch_bytes):
+        self._check(lib.ag_linear_add_backward(self._h, _p(dout), _p(act), _p(w), _p(dx), _p(dact), _p(dw), _p(db),
+                                               int(N_), int(K_), int(C_), int(precision), _p(scratch),
+                                               int(scratch_bytes)))
+
     def adamw_step(self, p, g, m, v, n, lr, lr_t, b1, b2, eps, weight_decay, grad_scale=1.0):
         self._check(lib.ag_adamw_step(self._h, _p(p), _p(g), _p(m), _p(v), int(n), float(lr), float(lr_t), float(b1),
                                       float(b2), float(eps), float(weight_decay), float(grad_scale)))

@@ -27,3 +27,18 @@ int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratc
 int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
                      const int32_t* targets, const float* lse, const float* row_scale, const float* dloss,
                      const float* denom, float* dX, float* dW);
+
+// ---- the tensor-core GEMM as a building block (used by the linear + bias + residual op) --------
+struct AgTcOperand {
+  const void* hi;   // tf32 "hi" parts, or the bf16 values
+  const void* lo;   // tf32 "lo" parts (null / unused in bf16 mode)
+  int64_t ld;       // elements between consecutive rows (K-major operand)
+};
+// D[M,N] (+)= A[M,K] . B[N,K]^T (+ bias[n]) (+ resid[m,n]); split-K with an ordered reduction when a
+// workspace is given and the problem has few tiles.
+int ag_tc_gemm(ag_ctx* ctx, bool bf16, const AgTcOperand& A, const AgTcOperand& B, float* D, int64_t ldd, int M, int N,
+               int K, bool accumulate, const float* bias, const float* resid, int64_t ld_resid, float* splitk_ws,
+               size_t splitk_ws_bytes);
+// src[R][Cc] -> operand form: (hi, lo) [R][ldo] when hi is given, transposed (hiT, loT) [Cc][ldt] when hiT is given.
+int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, void* hiT,
+                void* loT, int64_t ldt, int R, int Cc);

@@ -51,6 +51,10 @@ struct TcParams {
   int64_t ldd;
   int accumulate;
   int* status;
+  // EPI_STORE extras of the linear+bias+residual op: out = acc + bias[col] + resid[row][col]
+  const float* bias;
+  const float* resid;
+  int64_t ld_resid;
   // fused cross-entropy epilogues (EPI_STATS / EPI_DLOGITS); row-indexed arrays start at A's row 0
   const int32_t* targets;
   int v0;                  // vocabulary index of column 0 of this panel
@@ -301,7 +305,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     const int c_first = half * 32;
     uint32_t full_par[2] = {0, 0};
     int local = 0;
-    const bool vec_ok = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+    const bool vec_ok = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) &&
+                        (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) &&
+                        (!p.resid || (((p.ld_resid & 3) == 0) && (reinterpret_cast<uintptr_t>(p.resid) & 15u) == 0));
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
       int tm, tn, k_begin, k_end, split_id;
@@ -333,14 +339,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
                   const float4 o = *dst;
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                 }
+                if (p.bias) {
+                  const float4 bv = *reinterpret_cast<const float4*>(p.bias + col + j);
+                  v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+                }
+                if (p.resid) {
+                  const float4 rv = *reinterpret_cast<const float4*>(p.resid + (int64_t)row * p.ld_resid + col + j);
+                  v.x += rv.x; v.y += rv.y; v.z += rv.z; v.w += rv.w;
+                }
                 *dst = v;
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 if (col + j < p.N) {
-                  const float v = __uint_as_float(r[j]);
-                  drow[col + j] = p.accumulate ? drow[col + j] + v : v;
+                  float v = __uint_as_float(r[j]);
+                  if (p.accumulate) v += drow[col + j];
+                  if (p.bias) v += p.bias[col + j];
+                  if (p.resid) v += p.resid[(int64_t)row * p.ld_resid + col + j];
+                  drow[col + j] = v;
                 }
               }
             }
@@ -564,7 +581,7 @@ int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const
 int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, float* D, int64_t ldd, int M, int N, int K,
             bool accumulate, int epi_kind = EPI_STORE, const TcParams* epi = nullptr, int* tiles_n_out = nullptr,
             float* splitk_ws = nullptr, size_t splitk_ws_bytes = 0) {
-  TcParams p;
+  TcParams p = {};
   if (epi) p = *epi;
   p.M = M; p.N = N; p.K = K;
   p.BK = bf16 ? 64 : 32;
@@ -872,6 +889,29 @@ TcPlan tc_plan(const ag_flce_desc* d) {
 }
 
 }  // namespace
+
+// ---- entry points for other translation units (ag_flce.cuh) ---------------------------------
+int ag_tc_gemm(ag_ctx* ctx, bool bf16, const AgTcOperand& A, const AgTcOperand& B, float* D, int64_t ldd, int M, int N,
+               int K, bool accumulate, const float* bias, const float* resid, int64_t ld_resid, float* splitk_ws,
+               size_t splitk_ws_bytes) {
+  TcParams e = {};
+  e.bias = bias;
+  e.resid = resid;
+  e.ld_resid = ld_resid;
+  TcOperand a{A.hi, A.lo, A.ld}, b{B.hi, B.lo, B.ld};
+  return tc_gemm(ctx, bf16, a, b, D, ldd, M, N, K, accumulate, EPI_STORE, &e, nullptr, splitk_ws, splitk_ws_bytes);
+}
+
+int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, void* hiT,
+                void* loT, int64_t ldt, int R, int Cc) {
+  dim3 grid((Cc + 31) / 32, (R + 31) / 32);
+  if (bf16)
+    split_transpose_kernel<true><<<grid, dim3(32, 8), 0, ctx->stream>>>(src, lds, hi, lo, ldo, hiT, loT, ldt, R, Cc);
+  else
+    split_transpose_kernel<false><<<grid, dim3(32, 8), 0, ctx->stream>>>(src, lds, hi, lo, ldo, hiT, loT, ldt, R, Cc);
+  AG_LAUNCHED(ctx, "split_transpose_kernel");
+  return AG_OK;
+}
 
 // =========================================================================================
 bool ag_flce_tc_supported(const ag_flce_desc* d) {

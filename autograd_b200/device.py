@@ -20,7 +20,8 @@ from .backend import CudaBackend
 from .context import CudaContext
 from .storage import CudaAllocator, DEVICE_NAME
 
-_CUDA_SCRATCH_OPS = ("LayerNormOp", "GatherOp", "FusedLinearCrossEntropyOp", "FusedRMSNormLinearCrossEntropyOp")
+_CUDA_SCRATCH_OPS = ("LayerNormOp", "GatherOp", "FusedLinearCrossEntropyOp", "FusedRMSNormLinearCrossEntropyOp",
+                     "FusedLinearAddOp")
 
 
 def create(device: int = 0, stream: int | None = None):
@@ -61,6 +62,12 @@ def cuda_scratch_layouts(node, backend, pack_slots):
         nbytes = 2 * z_bytes + part_bytes + flce_bytes
         return (pack_slots([("rms_flce", (nbytes,), u8)], align=256),
                 pack_slots([("rms_flce", (nbytes,), u8)], align=256))
+    if name == "FusedLinearAddOp":
+        act, w = node.inputs[1], node.inputs[2]
+        n, k, c = int(prod(act.shape[:-1])), int(act.shape[-1]), int(w.shape[1])
+        nbytes = ctx.linear_add_scratch_bytes(n, k, c, backend._linear_precision())
+        return (pack_slots([("linear_add", (nbytes,), u8)], align=256),
+                pack_slots([("linear_add", (nbytes,), u8)], align=256))
     return None, None
 
 

@@ -215,6 +215,22 @@ int ag_flce_backward(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const f
                      const int32_t* targets, const float* row_scale, const float* dloss,
                      const float* lse, float* dX, float* dW, void* scratch, size_t scratch_bytes);
 
+/* ---- f2 linear projection with bias + residual epilogue --------------------------------------
+ * Replaces: backend.py:2040-2058 cpu_fused_linear_add_forward and :2147-2259
+ * cpu_fused_linear_add_backward (the branch whose `act` is materialised); Metal path
+ * backend.py bind of FusedLinearAddOp.  out[N,C] = act[N,K] . w[K,C] + b[C] + x[N,C]; b and x may be
+ * NULL; out may alias x (runtime.py:397-417 aliases them).  The GEMMs run on tcgen05 tensor cores,
+ * precision AG_CE_3XTF32 (fp32-grade) or AG_CE_BF16; K and C must be multiples of 4 (8 for bf16).
+ * backward accumulates: dx += dout, dact += dout . w^T, dw += act^T . dout, db += colsum(dout);
+ * any of the four may be NULL. */
+size_t ag_linear_add_scratch_bytes(int64_t N, int K, int C, int precision);
+int ag_linear_add_forward(ag_ctx* ctx, const float* x, const float* act, const float* w, const float* b,
+                          float* out, int64_t N, int K, int C, int precision, void* scratch,
+                          size_t scratch_bytes);
+int ag_linear_add_backward(ag_ctx* ctx, const float* dout, const float* act, const float* w, float* dx,
+                           float* dact, float* dw, float* db, int64_t N, int K, int C, int precision,
+                           void* scratch, size_t scratch_bytes);
+
 /* ---- f3 AdamW fp32 step ----------------------------------------------------------------
  * Replaces: backend.py:2013-2038 cpu_adamw_step; metal_ops.metal:10139-10227.
  * g is read as g*grad_scale. */

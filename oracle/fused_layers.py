@@ -351,6 +351,21 @@ def rmsnorm_flce(X, W, G, Y, eps, dloss=1.0, row_scale=None, chunk=1024):
 
 
 # --------------------------------------------------------------------------------------
+# f2  linear projection + bias + residual   backend.py:2040-2058, :2249-2259
+# --------------------------------------------------------------------------------------
+def linear_add_forward(x, act, w, b):
+    out = np.matmul(act, w)
+    out = np.add(out, b)
+    return np.add(out, x).astype(F32)
+
+
+def linear_add_backward(dout, act, w, x_grad, act_grad, w_grad, b_grad):
+    """Returns updated (x_grad, act_grad, w_grad, b_grad); all accumulate."""
+    return (np.add(x_grad, dout), np.add(act_grad, (dout @ w.T).astype(F32)),
+            np.add(w_grad, (act.T @ dout).astype(F32)), np.add(b_grad, np.sum(dout, axis=0).astype(F32)))
+
+
+# --------------------------------------------------------------------------------------
 # f3  AdamW fp32 step            backend.py:2013-2038
 # --------------------------------------------------------------------------------------
 def adamw_step(p, g, m, v, lr, lr_t, b1, b2, eps, wd):

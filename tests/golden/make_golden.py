@@ -359,6 +359,37 @@ def gen_rmsnorm_flce(ref, out):
     np.savez_compressed(os.path.join(out, "rmsnorm_flce.npz"), **blob)
 
 
+def gen_linear_add(ref, out):
+    """cpu_fused_linear_add_forward / _backward (backend.py:2040-2058, :2147-2259) on namespace tensors,
+    the branch whose `act` is a materialised tensor."""
+    blob = {}
+    for name, (N, K, C, seed) in {"square": (48, 64, 64, 1234 + 90), "wide": (130, 32, 96, 1234 + 91),
+                                  "mlp_down": (70, 256, 64, 1234 + 92)}.items():
+        rng = np.random.default_rng(seed)
+        f = np.float32
+        x = rng.standard_normal((1, N, C), dtype=f)
+        act = rng.standard_normal((1, N, K), dtype=f)
+        w = (rng.standard_normal((K, C)) / np.sqrt(K)).astype(f)
+        b = (0.1 * rng.standard_normal(C)).astype(f)
+        dout = rng.standard_normal((1, N, C), dtype=f)
+        pre = {k: rng.standard_normal(v.shape).astype(f) for k, v in dict(x=x, act=act, w=w, b=b).items()}
+        xt = ns_tensor(x, grad=pre["x"].copy())
+        at = ns_tensor(act, grad=pre["act"].copy())
+        at.op = None
+        wt = ns_tensor(w, grad=pre["w"].copy())
+        bt = ns_tensor(b, grad=pre["b"].copy())
+        outt = ns_tensor(np.zeros((1, N, C), f), grad=dout)
+        ref.backend.cpu_fused_linear_add_forward((xt, at, wt, bt), (outt,))
+        y = outt.storage.data.copy()
+        ref.backend.cpu_fused_linear_add_backward((xt, at, wt, bt), (outt,))
+        blob.update({f"{name}.x": x, f"{name}.act": act, f"{name}.w": w, f"{name}.b": b, f"{name}.dout": dout,
+                     f"{name}.out": y, f"{name}.pre_x": pre["x"], f"{name}.pre_act": pre["act"],
+                     f"{name}.pre_w": pre["w"], f"{name}.pre_b": pre["b"],
+                     f"{name}.dx": xt.grad.storage.data.copy(), f"{name}.dact": at.grad.storage.data.copy(),
+                     f"{name}.dw": wt.grad.storage.data.copy(), f"{name}.db": bt.grad.storage.data.copy()})
+    np.savez_compressed(os.path.join(out, "linear_add.npz"), **blob)
+
+
 def gen_adamw_bf16(ref, out):
     import utils as ref_utils
     rng = np.random.default_rng(SEED + 80)
@@ -387,7 +418,7 @@ def main():
     args = ap.parse_args()
     ref = load_reference(args.reference)
     for fn in (gen_add_layernorm, gen_gelu, gen_gather, gen_flce, gen_rmsnorm_swiglu, gen_rope,
-               gen_rmsnorm_flce, gen_adamw_bf16):
+               gen_rmsnorm_flce, gen_linear_add, gen_adamw_bf16):
         fn(ref, args.out)
         print("wrote", fn.__name__)
 

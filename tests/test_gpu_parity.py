@@ -564,6 +564,65 @@ def test_rmsnorm_flce_golden(golden, case):
     G.free(*inputs, loss)
 
 
+# ------------------------------------------------------------------------------ linear + bias + residual
+@pytest.mark.parametrize("case", ["square", "wide", "mlp_down"])
+def test_linear_add_golden(golden, case):
+    """FusedLinearAddOp on the tcgen05 GEMM (3xTF32): forward with the output aliasing the residual
+    input, backward accumulating on pre-loaded gradients, against the reference's CPU kernels."""
+    ctx, alloc, be = G.env()
+    g = golden("linear_add")
+    x = G.up(g[f"{case}.x"], grad=g[f"{case}.pre_x"])
+    act = G.up(g[f"{case}.act"], grad=g[f"{case}.pre_act"])
+    w = G.up(g[f"{case}.w"], grad=g[f"{case}.pre_w"])
+    b = G.up(g[f"{case}.b"], grad=g[f"{case}.pre_b"])
+    out = G.empty(g[f"{case}.out"].shape, grad=g[f"{case}.dout"])
+    n = G.node("FusedLinearAddOp", (x, act, w, b), (out,))
+    G.run_forward(n)
+    assert_close(G.down(out), g[f"{case}.out"], TOL_FWD, "out")
+    G.run_backward(n)
+    assert_close(G.down(x.grad), g[f"{case}.dx"], TOL_BWD, "dx")
+    assert_close(G.down(act.grad), g[f"{case}.dact"], TOL_BWD, "dact")
+    assert_close(G.down(w.grad), g[f"{case}.dw"], TOL_BWD, "dw")
+    assert_close(G.down(b.grad), g[f"{case}.db"], TOL_BWD, "db")
+    # in place: out aliases x (the reference aliases them when x dies at this node)
+    x2 = G.up(g[f"{case}.x"])
+    n2 = G.node("FusedLinearAddOp", (x2, act, w, b), (x2,))
+    G.run_forward(n2)
+    assert_close(G.down(x2), g[f"{case}.out"], TOL_FWD, "out in place")
+    G.check_clean_status()
+    G.free(x, act, w, b, out, x2)
+
+
+def test_linear_add_projection_size_vs_oracle():
+    """An attention-output projection of the depth-20 model (C 1280 -> 1280) on 4096 token rows."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(1242)
+    N, K, C = 4096, 1280, 1280
+    x_ = rng.standard_normal((N, C), dtype=np.float32)
+    act_ = rng.standard_normal((N, K), dtype=np.float32)
+    w_ = (rng.standard_normal((K, C)) / np.sqrt(K)).astype(np.float32)
+    b_ = (0.1 * rng.standard_normal(C)).astype(np.float32)
+    dout_ = rng.standard_normal((N, C), dtype=np.float32)
+    x, act, w, b = G.up(x_, grad=0), G.up(act_, grad=0), G.up(w_, grad=0), G.up(b_, grad=0)
+    out = G.empty((N, C), grad=dout_)
+    n = G.node("FusedLinearAddOp", (x, act, w, b), (out,))
+    G.run_forward(n)
+    # K = 1280 means 160 MMA steps x 3 terms accumulated inside the tensor core, whose fp32 adder
+    # does not round to nearest: the error grows with the number of steps (measured 2.5e-5 here,
+    # below 1e-5 for K <= 256), so this long-K forward is held to 5e-5 instead of 1e-5.
+    assert_close(G.down(out), O.linear_add_forward(x_, act_, w_, b_), 5e-5, "out")
+    G.run_backward(n)
+    z = np.zeros
+    dx, dact, dw, db = O.linear_add_backward(dout_, act_, w_, z((N, C), np.float32), z((N, K), np.float32),
+                                             z((K, C), np.float32), z(C, np.float32))
+    assert_close(G.down(x.grad), dx, TOL_BWD, "dx")
+    assert_close(G.down(act.grad), dact, TOL_BWD, "dact")
+    assert_close(G.down(w.grad), dw, TOL_BWD, "dw")
+    assert_close(G.down(b.grad), db, TOL_BWD, "db")
+    G.check_clean_status()
+    G.free(x, act, w, b, out)
+
+
 # ------------------------------------------------------------------------------ AdamW
 def test_adamw_golden(golden):
     ctx, alloc, be = G.env()

@@ -124,6 +124,21 @@ def test_rmsnorm_flce(golden):
         assert_close(r["dG"], g[f"{c}.dG"], 1e-5, f"{c}.dG")
 
 
+def test_linear_add(golden):
+    g = golden("linear_add")
+    for c in g.cases():
+        x, act, w, b, dout = (g[f"{c}.{k}"] for k in ("x", "act", "w", "b", "dout"))
+        n, k = act.shape[1], act.shape[2]
+        out = O.linear_add_forward(x[0], act[0], w, b)
+        assert_close(out, g[f"{c}.out"][0], 1e-5, f"{c}.out")
+        dx, dact, dw, db = O.linear_add_backward(dout[0], act[0], w, g[f"{c}.pre_x"][0], g[f"{c}.pre_act"][0],
+                                                 g[f"{c}.pre_w"], g[f"{c}.pre_b"])
+        assert_close(dx, g[f"{c}.dx"][0], TIGHT, f"{c}.dx")
+        assert_close(dact, g[f"{c}.dact"][0], 1e-5, f"{c}.dact")
+        assert_close(dw, g[f"{c}.dw"], 1e-5, f"{c}.dw")
+        assert_close(db, g[f"{c}.db"], 1e-5, f"{c}.db")
+
+
 def test_adamw_and_bf16(golden):
     g = golden("adamw_bf16")
     lr, lr_t, b1, b2, eps, wd = (float(v) for v in g["hp"])
