@@ -293,7 +293,7 @@ extern "C" int ag_flce_forward(ag_ctx* ctx, const ag_flce_desc* d, const float* 
   const bool tc = d->precision != AG_CE_FP32 && ag_flce_tc_supported(d);
   void* tc_scratch = base + p.total;
   if (tc) {
-    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch, false);
+    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch);
     if (rc) return rc;
   }
   AG_CUDA(ctx, cudaMemsetAsync(tgt, 0, (size_t)d->N * 4, ctx->stream));
@@ -339,7 +339,7 @@ extern "C" int ag_flce_backward(ag_ctx* ctx, const ag_flce_desc* d, const float*
   const bool tc = d->precision != AG_CE_FP32 && ag_flce_tc_supported(d);
   void* tc_scratch = base + p.total;
   if (tc) {
-    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch, true);
+    rc = ag_flce_tc_prepare(ctx, d, X, W, tc_scratch);
     if (rc) return rc;
   }
   ce_denominator_kernel<<<1, 1024, 0, ctx->stream>>>(targets, d->N, d->V, d->reduction, denom);

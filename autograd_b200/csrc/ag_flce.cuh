@@ -6,15 +6,10 @@
 
 // True when the tensor-core path takes this problem (precision mode, shape, alignment).
 bool ag_flce_tc_supported(const ag_flce_desc* d);
-// Extra workspace (split / converted / transposed operands) the tensor-core path needs.
+// Extra workspace (split / converted operands, dlogits panel, split-K partials) the tensor-core path needs.
 size_t ag_flce_tc_scratch_bytes(const ag_flce_desc* d);
-// Converts X and W into the operand format of d->precision inside tc_scratch; `backward` also
-// produces the transposed copies the gradient GEMMs read.
-int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch,
-                       bool backward);
-// panel[rows, vc] (row stride ld) = X[r0:r0+rows] . W[v0:v0+vc]^T from the prepared operands.
-int ag_flce_tc_logits(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
-                      float* panel, int64_t ld);
+// Converts X and W into the operand format of d->precision inside tc_scratch.
+int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch);
 // Forward of one panel without materialising it: logits tiles stay in TMEM, the GEMM epilogue
 // reduces them to per-tile (max, sum exp) and picks the target logit; the partials are folded
 // into run_max / run_sum (full-length arrays, indexed from r0 inside).
@@ -32,13 +27,15 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
 struct AgTcOperand {
   const void* hi;   // tf32 "hi" parts, or the bf16 values
   const void* lo;   // tf32 "lo" parts (null / unused in bf16 mode)
-  int64_t ld;       // elements between consecutive rows (K-major operand)
+  int64_t ld;       // elements between consecutive rows of the array as stored
+  int mn_major;     // 0: stored [MN][K] (K contiguous); 1: stored [K][MN] (MN contiguous)
 };
-// D[M,N] (+)= A[M,K] . B[N,K]^T (+ bias[n]) (+ resid[m,n]); split-K with an ordered reduction when a
+// D[M,N] (+)= A . B^T with A logically [M][K] and B logically [N][K], each stored K-major or MN-major
+// (+ bias[n]) (+ resid[m,n]); split-K with an ordered reduction when a
 // workspace is given and the problem has few tiles.
 int ag_tc_gemm(ag_ctx* ctx, bool bf16, const AgTcOperand& A, const AgTcOperand& B, float* D, int64_t ldd, int M, int N,
                int K, bool accumulate, const float* bias, const float* resid, int64_t ld_resid, float* splitk_ws,
                size_t splitk_ws_bytes);
-// src[R][Cc] -> operand form: (hi, lo) [R][ldo] when hi is given, transposed (hiT, loT) [Cc][ldt] when hiT is given.
-int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, void* hiT,
-                void* loT, int64_t ldt, int R, int Cc);
+// src[R][Cc] (row stride lds) -> operand form [R][Cc] (row stride ldo): (hi, lo) tf32 pairs or bf16 in `hi`.
+int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R,
+                int Cc);

@@ -1,6 +1,7 @@
 // tcgen05 tensor-core panels of the fused linear + cross-entropy head.
 //
-// One persistent GEMM kernel, D[M,N] (+)= A[M,K] . B[N,K]^T with both operands K-major:
+// One persistent GEMM kernel, D[M,N] (+)= A[M,K] . B[N,K]^T, each operand read from memory either
+// K-major ([MN][K], K contiguous) or MN-major ([K][MN], MN contiguous):
 //   warp 0      : TMA producer  - cp.async.bulk.tensor tiles (128-byte swizzle) into a ring of
 //                 shared-memory stages, completion on mbarriers;
 //   warp 1      : allocates TMEM, then one elected lane issues tcgen05.mma (cta_group::1,
@@ -14,10 +15,13 @@
 //            issues hi*lo + lo*hi + hi*hi into the same fp32 accumulator (error ~2^-22 of the
 //            product, i.e. fp32-grade logits from tf32 tensor cores);
 //   BF16   : operands rounded to bf16 once, a single MMA per k-step.
-// All three GEMMs of the head are expressed K-major by keeping transposed operand copies:
-//   logits  = X   . W^T       A = X  [rows,C]    B = W  [vc,C]
-//   dX     += dl  . W         A = dl [rows,vc]   B = W^T[C,vc]
-//   dW     += dl^T. X         A = dl^T[vc,rows]  B = X^T[C,rows]
+// The three GEMMs of the head read X, W and dl as stored; no transposed copy exists:
+//   logits  = X   . W^T       A = X  [rows,C] K-major     B = W [vc,C]   K-major
+//   dX     += dl  . W         A = dl [rows,vc] K-major    B = W [vc,C]   MN-major (contraction over vc)
+//   dW     += dl^T. X         A = dl [rows,vc] MN-major   B = X [rows,C] MN-major (contraction over rows)
+// An MN-major tile is fetched as one 3-d TMA box {128 bytes of MN, BK k-rows, MN groups} (one 2-d box per
+// group when the MN extent is ragged) and described to the MMA with the transposing descriptor forms
+// (see tc_smem_desc_mn).
 // Every output tile has exactly one writer, so accumulation order is fixed.
 // Every mbarrier wait is bounded; on expiry the CTA raises AG_STATUS_WAIT_EXPIRED, all roles
 // leave their loops, TMEM is released and the kernel returns.  Every CTA loads its own tiles; no thread-block clusters.
@@ -44,6 +48,9 @@ struct TcParams {
   int splits;      // split-K: each output tile is computed by `splits` CTAs over disjoint k ranges
   int k_per_split; // k iterations per split (the last one may be shorter)
   int64_t split_stride;  // elements between the partial outputs of consecutive splits
+  int a_mn, b_mn;  // operand is MN-major in memory ([K][MN], MN contiguous) instead of K-major ([MN][K])
+  int mn_group;    // MN elements per 128-byte row of an MN-major tile (32 fp32 / 64 bf16)
+  int a_3d, b_3d;  // MN-major operand fetched as one 3-d box {MN group, BK, groups} instead of one box per group
   int n_fastest;   // tile order
   uint32_t idesc;
   uint32_t a_bytes, b_bytes;  // bytes of one A / B tile in a stage
@@ -67,12 +74,9 @@ struct TcParams {
   const float* dloss;
   const float* denom;
   int ignore_mode;
-  void* dl_hi;             // EPI_DLOGITS outputs: dl [M][ld_dl] and dl^T [N][ld_dlT], (hi, lo) or bf16
+  void* dl_hi;             // EPI_DLOGITS output: dl [M][ld_dl], (hi, lo) or bf16
   void* dl_lo;
   int64_t ld_dl;
-  void* dlT_hi;
-  void* dlT_lo;
-  int64_t ld_dlT;
 };
 
 enum { EPI_STORE = 0, EPI_STATS = 1, EPI_DLOGITS = 2 };
@@ -83,6 +87,14 @@ __device__ __forceinline__ void tc_tma_load_2d(const CUtensorMap* tm, void* smem
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
           ag_smem_u32(smem_dst)),
       "l"(tm), "r"(ag_smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_tma_load_3d(const CUtensorMap* tm, void* smem_dst, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          ag_smem_u32(smem_dst)),
+      "l"(tm), "r"(ag_smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 
@@ -116,6 +128,18 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t
 // 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// MN-major operand: the tile is stored as [MN group][k row][128 bytes of MN]; consecutive MN groups are
+// `group_bytes` apart (leading byte offset).  16-bit operands use the plain 128-byte swizzle, whose
+// atom is 8 k rows (1024 bytes, the stride byte offset).  32-bit operands can only be transposed by
+// the tensor core from the 128-byte swizzle with 32-byte atomicity (layout type 1): its atom is 4 k
+// rows (512 bytes), and the matching TMA mode swizzles 32-byte chunks by the row index modulo 4.
+template <bool TF32>
+__device__ __forceinline__ uint64_t tc_smem_desc_mn(uint32_t smem_addr, uint32_t group_bytes) {
+  constexpr uint64_t sbo = TF32 ? 32ull : 64ull, layout = TF32 ? 1ull : 2ull;
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((group_bytes >> 4) & 0x3FFFu) << 16) | (sbo << 32) |
+         (1ull << 46) | (layout << 61);
 }
 
 __device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -232,13 +256,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           unsigned char* s = tiles + (size_t)stage * stage_bytes;
           ag_mbar_expect_tx(&full[stage], stage_bytes);
           const int kx = k * p.BK;
-          tc_tma_load_2d(&tmA_hi, s, &full[stage], kx, m0);
+          // K-major operand: one box {BK, rows}.  MN-major operand: one box {128 bytes of MN, BK rows} per
+          // MN group, stored group after group.
+          const uint32_t gbytes = (uint32_t)p.BK * 128u;
+          auto load_operand = [&](const CUtensorMap* tm, unsigned char* dst, int mn0, int mn_rows, int mn_major, int is3d) {
+            if (!mn_major) {
+              tc_tma_load_2d(tm, dst, &full[stage], kx, mn0);
+            } else if (is3d) {
+              tc_tma_load_3d(tm, dst, &full[stage], 0, kx, mn0 / p.mn_group);
+            } else {
+              for (int g = 0; g * p.mn_group < mn_rows; ++g)
+                tc_tma_load_2d(tm, dst + (size_t)g * gbytes, &full[stage], mn0 + g * p.mn_group, kx);
+            }
+          };
+          load_operand(&tmA_hi, s, m0, TC_BM, p.a_mn, p.a_3d);
           if (p.split) {
-            tc_tma_load_2d(&tmA_lo, s + p.a_bytes, &full[stage], kx, m0);
-            tc_tma_load_2d(&tmB_hi, s + 2 * p.a_bytes, &full[stage], kx, n0);
-            tc_tma_load_2d(&tmB_lo, s + 2 * p.a_bytes + p.b_bytes, &full[stage], kx, n0);
+            load_operand(&tmA_lo, s + p.a_bytes, m0, TC_BM, p.a_mn, p.a_3d);
+            load_operand(&tmB_hi, s + 2 * p.a_bytes, n0, p.BN, p.b_mn, p.b_3d);
+            load_operand(&tmB_lo, s + 2 * p.a_bytes + p.b_bytes, n0, p.BN, p.b_mn, p.b_3d);
           } else {
-            tc_tma_load_2d(&tmB_hi, s + p.a_bytes, &full[stage], kx, n0);
+            load_operand(&tmB_hi, s + p.a_bytes, n0, p.BN, p.b_mn, p.b_3d);
           }
           if (++stage == (uint32_t)p.stages) {
             stage = 0;
@@ -275,15 +312,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           const uint32_t a_hi = s, a_lo = s + p.a_bytes;
           const uint32_t b_hi = p.split ? s + 2 * p.a_bytes : s + p.a_bytes;
           const uint32_t b_lo = b_hi + p.b_bytes;
+          const uint32_t gbytes = (uint32_t)p.BK * 128u;
           for (int kk = 0; kk < k_sub; ++kk) {
-            const uint32_t off = (uint32_t)kk * 32u;  // 32 bytes of K per MMA inside the 128-byte row
+            // K-major: 32 bytes of K per MMA inside the 128-byte row.  MN-major: umma_k k-rows of
+            // 128 bytes per MMA.
             const uint32_t first = (k == k_begin && kk == 0) ? 0u : 1u;
+            const uint32_t offk = (uint32_t)kk * 32u, offm = (uint32_t)kk * (uint32_t)p.umma_k * 128u;
+            auto da = [&](uint32_t base) { return p.a_mn ? tc_smem_desc_mn<TF32>(base + offm, gbytes) : tc_smem_desc(base + offk); };
+            auto db = [&](uint32_t base) { return p.b_mn ? tc_smem_desc_mn<TF32>(base + offm, gbytes) : tc_smem_desc(base + offk); };
             if (p.split) {
-              tc_mma<TF32>(tacc, tc_smem_desc(a_hi + off), tc_smem_desc(b_lo + off), p.idesc, first);
-              tc_mma<TF32>(tacc, tc_smem_desc(a_lo + off), tc_smem_desc(b_hi + off), p.idesc, 1u);
-              tc_mma<TF32>(tacc, tc_smem_desc(a_hi + off), tc_smem_desc(b_hi + off), p.idesc, 1u);
+              tc_mma<TF32>(tacc, da(a_hi), db(b_lo), p.idesc, first);
+              tc_mma<TF32>(tacc, da(a_lo), db(b_hi), p.idesc, 1u);
+              tc_mma<TF32>(tacc, da(a_hi), db(b_hi), p.idesc, 1u);
             } else {
-              tc_mma<TF32>(tacc, tc_smem_desc(a_hi + off), tc_smem_desc(b_hi + off), p.idesc, first);
+              tc_mma<TF32>(tacc, da(a_hi), db(b_hi), p.idesc, first);
             }
           }
           tc_commit(&empty[stage]);  // stage reusable once these MMAs have read it
@@ -330,25 +372,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           const int col = n0 + c0;
           if (row < p.M && col < p.N) {
             if (vec_ok && col + 32 <= p.N) {
+              // all loads of a source are issued before anything is stored: with a load and a store per
+              // packet in one loop the eight round trips to memory would be taken one after the other
+              float4* dst = reinterpret_cast<float4*>(drow + col);
+              float4 v[8];
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                       __uint_as_float(r[j + 3]));
-                float4* dst = reinterpret_cast<float4*>(drow + col + j);
-                if (p.accumulate) {
-                  const float4 o = *dst;
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                if (p.bias) {
-                  const float4 bv = *reinterpret_cast<const float4*>(p.bias + col + j);
-                  v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-                }
-                if (p.resid) {
-                  const float4 rv = *reinterpret_cast<const float4*>(p.resid + (int64_t)row * p.ld_resid + col + j);
-                  v.x += rv.x; v.y += rv.y; v.z += rv.z; v.w += rv.w;
-                }
-                *dst = v;
+              for (int j = 0; j < 8; ++j)
+                v[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                   __uint_as_float(r[4 * j + 3]));
+              if (p.accumulate) {
+                float4 o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = dst[j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v[j].x += o[j].x; v[j].y += o[j].y; v[j].z += o[j].z; v[j].w += o[j].w; }
               }
+              if (p.bias) {
+                const float4* bsrc = reinterpret_cast<const float4*>(p.bias + col);
+                float4 o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = __ldg(bsrc + j);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v[j].x += o[j].x; v[j].y += o[j].y; v[j].z += o[j].z; v[j].w += o[j].w; }
+              }
+              if (p.resid) {
+                const float4* rsrc = reinterpret_cast<const float4*>(p.resid + (int64_t)row * p.ld_resid + col);
+                float4 o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = rsrc[j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v[j].x += o[j].x; v[j].y += o[j].y; v[j].z += o[j].z; v[j].w += o[j].w; }
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) dst[j] = v[j];
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -398,7 +454,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           if (have_t) p.tgt_logit[row] = tl;
         }
       } else {
-        // dlogits of this row, written in operand form: dl (row-major) and dl^T
+        // dlogits of this row, written in operand form (hi, lo) or bf16
         float sc = 0.0f, e = 0.0f;
         int tcol = -1;
         if (row < p.M) {
@@ -446,15 +502,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
               for (int j = 0; j < 32; ++j)
                 if (col + j < p.N) { dh[j] = hi[j]; dlo[j] = lo[j]; }
             }
-            float* th = static_cast<float*>(p.dlT_hi) + (int64_t)col * p.ld_dlT + row;
-            float* tlo = static_cast<float*>(p.dlT_lo) + (int64_t)col * p.ld_dlT + row;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col + j < p.N) {  // lanes of a warp hold consecutive rows: each store is one 128-byte line
-                th[(int64_t)j * p.ld_dlT] = hi[j];
-                tlo[(int64_t)j * p.ld_dlT] = lo[j];
-              }
-            }
           } else {
             __nv_bfloat16* dh = static_cast<__nv_bfloat16*>(p.dl_hi) + (int64_t)row * p.ld_dl + col;
             if (row_vec && col + 32 <= p.N) {
@@ -473,10 +520,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
               for (int j = 0; j < 32; ++j)
                 if (col + j < p.N) dh[j] = __float2bfloat16_rn(hi[j]);
             }
-            __nv_bfloat16* th = static_cast<__nv_bfloat16*>(p.dlT_hi) + (int64_t)col * p.ld_dlT + row;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col + j < p.N) th[(int64_t)j * p.ld_dlT] = __float2bfloat16_rn(hi[j]);
           }
         }
       }
@@ -498,7 +541,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
 struct TcOperand {
   const void* hi;
   const void* lo;   // null in bf16 mode
-  int64_t ld;       // elements between consecutive rows
+  int64_t ld;       // elements between consecutive rows of the array as stored
+  int mn_major;     // 0: stored [MN][K] (K contiguous); 1: stored [K][MN] (MN contiguous)
 };
 
 // The driver API is reached through the runtime (cudaGetDriverEntryPoint) so that the library has
@@ -524,7 +568,7 @@ EncodeTiledFn tc_encode_fn(ag_ctx* ctx) {
 }
 
 int tc_encode(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int64_t k_extent, int64_t rows, int64_t ld,
-              int box_k, int box_rows) {
+              int box_k, int box_rows, bool atom32 = false) {
   EncodeTiledFn encode = tc_encode_fn(ctx);
   if (!encode) return AG_ERR_CUDA;
   const size_t es = bf16 ? 2 : 4;
@@ -534,7 +578,8 @@ int tc_encode(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int64_t 
   cuuint32_t estr[2] = {1, 1};
   CUresult r = encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                                       const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     AG_FAIL(ctx, AG_ERR_CUDA, "cuTensorMapEncodeTiled failed: CUresult %d (ptr %p, k %lld, rows %lld, ld %lld, box %dx%d)",
@@ -542,7 +587,27 @@ int tc_encode(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int64_t 
   return AG_OK;
 }
 
-// D[M,N] (+)= A[M,K] . B[N,K]^T on the tensor cores.
+// MN-major operand stored [K][mn_extent] (row stride ld) seen as {group elements, K, groups}: one box
+// {group, box_k, box_groups} lands in shared memory as [group][k row][128 bytes].
+int tc_encode_mn3(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int64_t mn_extent, int64_t k_extent,
+                  int64_t ld, int group, int box_k, int box_groups) {
+  EncodeTiledFn encode = tc_encode_fn(ctx);
+  if (!encode) return AG_ERR_CUDA;
+  const size_t es = bf16 ? 2 : 4;
+  cuuint64_t dims[3] = {(cuuint64_t)group, (cuuint64_t)k_extent, (cuuint64_t)(mn_extent / group)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * es, (cuuint64_t)group * es};
+  cuuint32_t box[3] = {(cuuint32_t)group, (cuuint32_t)box_k, (cuuint32_t)box_groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                      const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    AG_FAIL(ctx, AG_ERR_CUDA, "cuTensorMapEncodeTiled (3-d) failed: CUresult %d (ptr %p, mn %lld, k %lld, ld %lld)", (int)r,
+            ptr, (long long)mn_extent, (long long)k_extent, (long long)ld);
+  return AG_OK;
+}
+
 // D[m][n] (+)= sum over splits, in split order, of the partial outputs P[s][m][n].
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ P, int splits, int M, int N, float* D, int64_t ldd, int accumulate) {
@@ -596,7 +661,11 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   double best_cost = 1e300;
   const int tiles_m = (M + TC_BM - 1) / TC_BM;
   const int k_iters_all = (K + p.BK - 1) / p.BK;
+  p.a_mn = A.mn_major ? 1 : 0;
+  p.b_mn = B.mn_major ? 1 : 0;
+  p.mn_group = bf16 ? 64 : 32;
   for (int bn : cand) {
+    if (p.b_mn && bn % p.mn_group != 0) continue;
     const int tn = (N + bn - 1) / bn;
     const int64_t tiles = (int64_t)tiles_m * tn;
     int s_max = 1;
@@ -644,7 +713,8 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   }
   // instruction descriptor: D fp32, A/B tf32 or bf16, both K-major, N>>3 at bit 17, M>>4 at bit 24
   const uint32_t fmt = bf16 ? 1u : 2u;
-  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+            ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
   p.D = D; p.ldd = ldd; p.accumulate = accumulate ? 1 : 0;
   if (p.splits > 1) {  // partial outputs [splits][M][N] in the workspace, summed in order afterwards
     p.D = splitk_ws;
@@ -656,11 +726,22 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
 
   CUtensorMap tA_hi, tA_lo, tB_hi, tB_lo;
   int rc;
-  if ((rc = tc_encode(ctx, &tA_hi, A.hi, bf16, K, M, A.ld, p.BK, TC_BM))) return rc;
-  if ((rc = tc_encode(ctx, &tB_hi, B.hi, bf16, K, N, B.ld, p.BK, p.BN))) return rc;
+  // tensor maps: K-major {K inner, MN rows} with box {BK, tile rows}; MN-major {MN inner, K rows} with
+  // box {one 128-byte MN group, BK}
+  // whole MN groups: one 3-d box per operand tile; a ragged MN extent falls back to one 2-d box per group
+  p.a_3d = (p.a_mn && M % p.mn_group == 0) ? 1 : 0;
+  p.b_3d = (p.b_mn && N % p.mn_group == 0) ? 1 : 0;
+  auto encode_operand = [&](CUtensorMap* tm, const void* ptr, const TcOperand& op, int mn_extent, int tile_rows) -> int {
+    if (!op.mn_major) return tc_encode(ctx, tm, ptr, bf16, K, mn_extent, op.ld, p.BK, tile_rows);
+    if (mn_extent % p.mn_group == 0)
+      return tc_encode_mn3(ctx, tm, ptr, bf16, mn_extent, K, op.ld, p.mn_group, p.BK, tile_rows / p.mn_group);
+    return tc_encode(ctx, tm, ptr, bf16, mn_extent, K, op.ld, p.mn_group, p.BK, /*atom32=*/!bf16);
+  };
+  if ((rc = encode_operand(&tA_hi, A.hi, A, M, TC_BM))) return rc;
+  if ((rc = encode_operand(&tB_hi, B.hi, B, N, p.BN))) return rc;
   if (p.split) {
-    if ((rc = tc_encode(ctx, &tA_lo, A.lo, bf16, K, M, A.ld, p.BK, TC_BM))) return rc;
-    if ((rc = tc_encode(ctx, &tB_lo, B.lo, bf16, K, N, B.ld, p.BK, p.BN))) return rc;
+    if ((rc = encode_operand(&tA_lo, A.lo, A, M, TC_BM))) return rc;
+    if ((rc = encode_operand(&tB_lo, B.lo, B, N, p.BN))) return rc;
   } else {
     tA_lo = tA_hi;
     tB_lo = tB_hi;
@@ -699,119 +780,31 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   lo = tf32_rna(x - hi);
 }
 
-// src[R][Cc] (row stride lds) -> hi/lo [R][Cc] (row stride ldo) and, when the T pointers are given,
-// hiT/loT [Cc][R] (row stride ldt).  32x32 tiles through shared memory; block (32, 8).
-// BF16: the outputs are bf16 (hi only).
+// src[R][Cc] (row stride lds) -> operand form [R][Cc] (row stride ldo): (hi, lo) tf32 pairs, or bf16
+// values in `hi`.  Cc, lds and ldo are multiples of 4; one thread converts 4 consecutive elements.
 template <bool BF16>
 __global__ void __launch_bounds__(256)
-split_transpose_kernel(const float* __restrict__ src, int64_t lds, void* __restrict__ hi, void* __restrict__ lo,
-                       int64_t ldo, void* __restrict__ hiT, void* __restrict__ loT, int64_t ldt, int R, int Cc) {
-  __shared__ float s_hi[32][33];
-  __shared__ float s_lo[32][33];
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  for (int i = threadIdx.y; i < 32; i += 8) {
-    const int r = r0 + i, c = c0 + threadIdx.x;
-    float h = 0.0f, l = 0.0f;
-    if (r < R && c < Cc) {
-      const float x = src[(int64_t)r * lds + c];
-      if (BF16) {
-        h = x;
-      } else {
-        split_tf32(x, h, l);
-      }
-      if (hi) {
-        if (BF16) {
-          static_cast<__nv_bfloat16*>(hi)[(int64_t)r * ldo + c] = __float2bfloat16_rn(h);
-        } else {
-          static_cast<float*>(hi)[(int64_t)r * ldo + c] = h;
-          static_cast<float*>(lo)[(int64_t)r * ldo + c] = l;
-        }
-      }
-    }
-    s_hi[i][threadIdx.x] = h;
-    s_lo[i][threadIdx.x] = l;
-  }
-  if (!hiT) return;
-  __syncthreads();
-  for (int i = threadIdx.y; i < 32; i += 8) {
-    const int c = c0 + i, r = r0 + threadIdx.x;  // output row = source column
-    if (c < Cc && r < R) {
-      if (BF16) {
-        static_cast<__nv_bfloat16*>(hiT)[(int64_t)c * ldt + r] = __float2bfloat16_rn(s_hi[threadIdx.x][i]);
-      } else {
-        static_cast<float*>(hiT)[(int64_t)c * ldt + r] = s_hi[threadIdx.x][i];
-        static_cast<float*>(loT)[(int64_t)c * ldt + r] = s_lo[threadIdx.x][i];
-      }
-    }
-  }
-}
-
-// dlogits of one panel, written straight in tensor-core operand form:
-//   dl[r][c] = scale_r * (exp(L[r][c] - lse[r]) - [c == target_r - v0])   (0 for ignored rows when masked)
-// -> dl (hi, lo) [rows][ld_dl] and dl^T (hi, lo) [vc][ld_dlT].
-template <bool BF16>
-__global__ void __launch_bounds__(256)
-dlogits_split_kernel(const float* __restrict__ L, int64_t ldl, int rows, int vc, int v0,
-                     const int32_t* __restrict__ targets, const float* __restrict__ lse,
-                     const float* __restrict__ row_scale, const float* __restrict__ dloss,
-                     const float* __restrict__ denom, int V, int ignore_mode, void* __restrict__ dl_hi,
-                     void* __restrict__ dl_lo, int64_t ld_dl, void* __restrict__ dlT_hi, void* __restrict__ dlT_lo,
-                     int64_t ld_dlT) {
-  __shared__ float s_hi[32][33];
-  __shared__ float s_lo[32][33];
-  __shared__ float s_lse[32], s_scale[32];
-  __shared__ int s_tc[32];
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  if (threadIdx.y == 0) {
-    const int r = r0 + threadIdx.x;
-    float sc = 0.0f, e = 0.0f;
-    int tc = -1;
-    if (r < rows) {
-      const int t = targets[r];
-      const bool valid = t >= 0 && t < V;
-      sc = row_scale ? dloss[0] * row_scale[r] : dloss[0] / denom[0];
-      if (!valid && ignore_mode == AG_CE_IGNORE_MASKED) sc = 0.0f;
-      e = lse[r];
-      tc = valid ? t - v0 : -1;
-    }
-    s_lse[threadIdx.x] = e;
-    s_scale[threadIdx.x] = sc;
-    s_tc[threadIdx.x] = tc;
-  }
-  __syncthreads();
-  for (int i = threadIdx.y; i < 32; i += 8) {
-    const int r = r0 + i, c = c0 + threadIdx.x;
-    float h = 0.0f, l = 0.0f;
-    if (r < rows && c < vc) {
-      const float sc = s_scale[i];
-      float d = 0.0f;
-      if (sc != 0.0f) {
-        float pr = expf(L[(int64_t)r * ldl + c] - s_lse[i]);
-        if (c == s_tc[i]) pr -= 1.0f;
-        d = pr * sc;
-      }
-      if (BF16) {
-        h = d;
-        static_cast<__nv_bfloat16*>(dl_hi)[(int64_t)r * ld_dl + c] = __float2bfloat16_rn(d);
-      } else {
-        split_tf32(d, h, l);
-        static_cast<float*>(dl_hi)[(int64_t)r * ld_dl + c] = h;
-        static_cast<float*>(dl_lo)[(int64_t)r * ld_dl + c] = l;
-      }
-    }
-    s_hi[i][threadIdx.x] = h;
-    s_lo[i][threadIdx.x] = l;
-  }
-  __syncthreads();
-  for (int i = threadIdx.y; i < 32; i += 8) {
-    const int c = c0 + i, r = r0 + threadIdx.x;
-    if (c < vc && r < rows) {
-      if (BF16) {
-        static_cast<__nv_bfloat16*>(dlT_hi)[(int64_t)c * ld_dlT + r] = __float2bfloat16_rn(s_hi[threadIdx.x][i]);
-      } else {
-        static_cast<float*>(dlT_hi)[(int64_t)c * ld_dlT + r] = s_hi[threadIdx.x][i];
-        static_cast<float*>(dlT_lo)[(int64_t)c * ld_dlT + r] = s_lo[threadIdx.x][i];
-      }
+split_kernel(const float* __restrict__ src, int64_t lds, void* __restrict__ hi, void* __restrict__ lo, int64_t ldo,
+             int R, int Cc) {
+  const int c4 = Cc >> 2;
+  const int64_t total = (int64_t)R * c4;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / c4;
+    const int c = (int)(i - r * c4) << 2;
+    const float4 x = *reinterpret_cast<const float4*>(src + r * lds + c);
+    if (BF16) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(hi) + r * ldo + c) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    } else {
+      float4 h, l;
+      split_tf32(x.x, h.x, l.x);
+      split_tf32(x.y, h.y, l.y);
+      split_tf32(x.z, h.z, l.z);
+      split_tf32(x.w, h.w, l.w);
+      *reinterpret_cast<float4*>(static_cast<float*>(hi) + r * ldo + c) = h;
+      *reinterpret_cast<float4*>(static_cast<float*>(lo) + r * ldo + c) = l;
     }
   }
 }
@@ -844,10 +837,9 @@ ce_merge_partials_kernel(const float2* __restrict__ part, int64_t part_ld, int t
 
 // ---------------------------------------------------------------------------- workspace plan
 struct TcPlan {
-  int64_t rows_tile, vc, ldn;  // ldn: row stride of the [C][N] transposed activations
-  size_t es;                   // operand element size
-  size_t X_hi, X_lo, XT_hi, XT_lo, W_hi, W_lo, WT_hi, WT_lo, dl_hi, dl_lo, dlT_hi, dlT_lo, part, splitk, splitk_bytes,
-      total;
+  int64_t rows_tile, vc;
+  size_t es;  // operand element size
+  size_t X_hi, X_lo, W_hi, W_lo, dl_hi, dl_lo, part, splitk, splitk_bytes, total;
   int64_t part_ld;
 };
 
@@ -860,22 +852,15 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   p.es = bf16 ? 2 : 4;
   p.rows_tile = d->N < 16384 ? d->N : 16384;
   p.vc = d->vocab_chunk < d->V ? d->vocab_chunk : d->V;
-  p.ldn = up8(d->N);
-  const int64_t ldv = up8(d->V), ldr = up8(p.rows_tile), ldc = up8(p.vc);
+  const int64_t ldr = up8(p.rows_tile), ldc = up8(p.vc);
   size_t off = 0;
   auto take = [&](size_t elems) { size_t o = off; off += up256(elems * p.es); return o; };
   p.X_hi = take((size_t)d->N * d->C);
   p.X_lo = bf16 ? p.X_hi : take((size_t)d->N * d->C);
   p.W_hi = take((size_t)d->V * d->C);
   p.W_lo = bf16 ? p.W_hi : take((size_t)d->V * d->C);
-  p.XT_hi = take((size_t)d->C * p.ldn);
-  p.XT_lo = bf16 ? p.XT_hi : take((size_t)d->C * p.ldn);
-  p.WT_hi = take((size_t)d->C * ldv);
-  p.WT_lo = bf16 ? p.WT_hi : take((size_t)d->C * ldv);
   p.dl_hi = take((size_t)p.rows_tile * ldc);
   p.dl_lo = bf16 ? p.dl_hi : take((size_t)p.rows_tile * ldc);
-  p.dlT_hi = take((size_t)p.vc * ldr);
-  p.dlT_lo = bf16 ? p.dlT_hi : take((size_t)p.vc * ldr);
   // per (column tile, epilogue half, row) partial softmax statistics of one panel
   p.part_ld = ldr;
   p.part = off;
@@ -888,6 +873,19 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   return p;
 }
 
+int tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R, int Cc) {
+  AG_REQUIRE(ctx, Cc % 4 == 0 && lds % 4 == 0 && ldo % 4 == 0 && R < (1ll << 31), "tc_split: rows must be whole 16-byte packets");
+  int64_t want = (R * (Cc / 4) + 255) / 256;
+  if (want > (int64_t)ctx->sm_count * 16) want = (int64_t)ctx->sm_count * 16;
+  if (want < 1) want = 1;
+  if (bf16)
+    split_kernel<true><<<(int)want, 256, 0, ctx->stream>>>(src, lds, hi, lo, ldo, (int)R, Cc);
+  else
+    split_kernel<false><<<(int)want, 256, 0, ctx->stream>>>(src, lds, hi, lo, ldo, (int)R, Cc);
+  AG_LAUNCHED(ctx, "split_kernel");
+  return AG_OK;
+}
+
 }  // namespace
 
 // ---- entry points for other translation units (ag_flce.cuh) ---------------------------------
@@ -898,19 +896,13 @@ int ag_tc_gemm(ag_ctx* ctx, bool bf16, const AgTcOperand& A, const AgTcOperand& 
   e.bias = bias;
   e.resid = resid;
   e.ld_resid = ld_resid;
-  TcOperand a{A.hi, A.lo, A.ld}, b{B.hi, B.lo, B.ld};
+  TcOperand a{A.hi, A.lo, A.ld, A.mn_major}, b{B.hi, B.lo, B.ld, B.mn_major};
   return tc_gemm(ctx, bf16, a, b, D, ldd, M, N, K, accumulate, EPI_STORE, &e, nullptr, splitk_ws, splitk_ws_bytes);
 }
 
-int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, void* hiT,
-                void* loT, int64_t ldt, int R, int Cc) {
-  dim3 grid((Cc + 31) / 32, (R + 31) / 32);
-  if (bf16)
-    split_transpose_kernel<true><<<grid, dim3(32, 8), 0, ctx->stream>>>(src, lds, hi, lo, ldo, hiT, loT, ldt, R, Cc);
-  else
-    split_transpose_kernel<false><<<grid, dim3(32, 8), 0, ctx->stream>>>(src, lds, hi, lo, ldo, hiT, loT, ldt, R, Cc);
-  AG_LAUNCHED(ctx, "split_transpose_kernel");
-  return AG_OK;
+int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R,
+                int Cc) {
+  return tc_split(ctx, bf16, src, lds, hi, lo, ldo, R, Cc);
 }
 
 // =========================================================================================
@@ -926,49 +918,13 @@ bool ag_flce_tc_supported(const ag_flce_desc* d) {
 
 size_t ag_flce_tc_scratch_bytes(const ag_flce_desc* d) { return tc_plan(d).total; }
 
-int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch,
-                       bool backward) {
+int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch) {
   const TcPlan p = tc_plan(d);
   unsigned char* b = static_cast<unsigned char*>(tc_scratch);
   const bool bf16 = d->precision == AG_CE_BF16;
-  const dim3 blk(32, 8);
-  const int64_t ldv = up8(d->V);
-  {
-    dim3 grid((d->C + 31) / 32, (unsigned)((d->N + 31) / 32));
-    void* hT = backward ? b + p.XT_hi : nullptr;
-    void* lT = backward ? b + p.XT_lo : nullptr;
-    if (bf16)
-      split_transpose_kernel<true><<<grid, blk, 0, ctx->stream>>>(X, d->C, b + p.X_hi, b + p.X_lo, d->C, hT, lT, p.ldn,
-                                                                   (int)d->N, d->C);
-    else
-      split_transpose_kernel<false><<<grid, blk, 0, ctx->stream>>>(X, d->C, b + p.X_hi, b + p.X_lo, d->C, hT, lT,
-                                                                    p.ldn, (int)d->N, d->C);
-    AG_LAUNCHED(ctx, "split_transpose_kernel(X)");
-  }
-  {
-    dim3 grid((d->C + 31) / 32, (unsigned)((d->V + 31) / 32));
-    void* hT = backward ? b + p.WT_hi : nullptr;
-    void* lT = backward ? b + p.WT_lo : nullptr;
-    if (bf16)
-      split_transpose_kernel<true><<<grid, blk, 0, ctx->stream>>>(W, d->C, b + p.W_hi, b + p.W_lo, d->C, hT, lT, ldv,
-                                                                   d->V, d->C);
-    else
-      split_transpose_kernel<false><<<grid, blk, 0, ctx->stream>>>(W, d->C, b + p.W_hi, b + p.W_lo, d->C, hT, lT, ldv,
-                                                                    d->V, d->C);
-    AG_LAUNCHED(ctx, "split_transpose_kernel(W)");
-  }
-  return AG_OK;
-}
-
-int ag_flce_tc_logits(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0, int vc,
-                      float* panel, int64_t ld) {
-  const TcPlan p = tc_plan(d);
-  unsigned char* b = static_cast<unsigned char*>(tc_scratch);
-  const bool bf16 = d->precision == AG_CE_BF16;
-  const size_t row_bytes = (size_t)d->C * p.es;
-  TcOperand A{b + p.X_hi + (size_t)r0 * row_bytes, b + p.X_lo + (size_t)r0 * row_bytes, d->C};
-  TcOperand B{b + p.W_hi + (size_t)v0 * row_bytes, b + p.W_lo + (size_t)v0 * row_bytes, d->C};
-  return tc_gemm(ctx, bf16, A, B, panel, ld, rows, vc, d->C, false);
+  int rc;
+  if ((rc = tc_split(ctx, bf16, X, d->C, b + p.X_hi, b + p.X_lo, d->C, d->N, d->C))) return rc;
+  return tc_split(ctx, bf16, W, d->C, b + p.W_hi, b + p.W_lo, d->C, d->V, d->C);
 }
 
 int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0,
@@ -1002,7 +958,7 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
   const TcPlan p = tc_plan(d);
   unsigned char* b = static_cast<unsigned char*>(tc_scratch);
   const bool bf16 = d->precision == AG_CE_BF16;
-  const int64_t ldc = up8(p.vc), ldr = up8(p.rows_tile), ldv = up8(d->V);
+  const int64_t ldc = up8(p.vc);
   const size_t row_bytes = (size_t)d->C * p.es;
   int rc;
   {
@@ -1019,19 +975,20 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
     e.denom = denom;
     e.ignore_mode = d->ignore_mode;
     e.dl_hi = b + p.dl_hi; e.dl_lo = b + p.dl_lo; e.ld_dl = ldc;
-    e.dlT_hi = b + p.dlT_hi; e.dlT_lo = b + p.dlT_lo; e.ld_dlT = ldr;
     if ((rc = tc_gemm(ctx, bf16, A, B, nullptr, 0, rows, vc, d->C, false, EPI_DLOGITS, &e))) return rc;
   }
   if (dX) {
-    // dX[r0:r0+rows, :] += dl [rows, vc] . (W^T [C, v0:v0+vc])^T
-    TcOperand A{b + p.dl_hi, b + p.dl_lo, ldc};
-    TcOperand B{b + p.WT_hi + (size_t)v0 * p.es, b + p.WT_lo + (size_t)v0 * p.es, ldv};
+    // dX[r0:r0+rows, :] += dl [rows, vc] . W[v0:v0+vc, :]; W as stored has the contraction index
+    // (vocabulary) as its row index, i.e. it is the MN-major form of the B operand
+    TcOperand A{b + p.dl_hi, b + p.dl_lo, ldc, 0};
+    TcOperand B{b + p.W_hi + (size_t)v0 * row_bytes, b + p.W_lo + (size_t)v0 * row_bytes, d->C, 1};
     if ((rc = tc_gemm(ctx, bf16, A, B, dX + r0 * d->C, d->C, rows, d->C, vc, true))) return rc;
   }
   if (dW) {
-    // dW[v0:v0+vc, :] += dl^T [vc, rows] . (X^T [C, r0:r0+rows])^T
-    TcOperand A{b + p.dlT_hi, b + p.dlT_lo, ldr};
-    TcOperand B{b + p.XT_hi + (size_t)r0 * p.es, b + p.XT_lo + (size_t)r0 * p.es, p.ldn};
+    // dW[v0:v0+vc, :] += dl^T . X[r0:r0+rows, :]; the contraction index (row) is the row index of
+    // both dl and X as stored: both operands MN-major
+    TcOperand A{b + p.dl_hi, b + p.dl_lo, ldc, 1};
+    TcOperand B{b + p.X_hi + (size_t)r0 * row_bytes, b + p.X_lo + (size_t)r0 * row_bytes, d->C, 1};
     if ((rc = tc_gemm(ctx, bf16, A, B, dW + (int64_t)v0 * d->C, d->C, vc, d->C, rows, true, EPI_STORE, nullptr, nullptr,
                       reinterpret_cast<float*>(b + p.splitk), p.splitk_bytes)))
       return rc;

@@ -5,23 +5,23 @@
 // kernel of ag_flce_tc.cu in 3xTF32 (fp32-grade) or bf16; bias and residual are added in its
 // epilogue while the accumulator is read out of TMEM, so the projection output is written once and
 // `out` may alias `x` (the reference aliases them when x dies here, runtime.py:397-417).
-//   forward : out[N,C]  = act[N,K] . W[K,C] + b[C] + x[N,C]
+//   forward : out[N,C]  = act[N,K] . W[K,C] + b[C] + x[N,C]     (W read MN-major)
 //   backward: dx   += dout
-//             dact += dout . W^T
-//             dW   += act^T . dout          (split-K with ordered reduction)
+//             dact += dout . W^T                                 (both K-major as stored)
+//             dW   += act^T . dout          (both MN-major; split-K with ordered reduction)
 //             db   += column sums of dout   (two passes, fixed order, no atomics)
+// act, W and dout are only converted to the operand format (tf32 hi/lo pairs or bf16); the GEMM
+// reads them in whichever orientation each product needs, so no transposed copy is made.
 #include "ag_flce.cuh"
 
 namespace {
 
 inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
-inline int64_t up8(int64_t x) { return (x + 7) & ~(int64_t)7; }
 
 struct LinPlan {
   size_t es;
-  int64_t ldn;  // row stride of the [*, N] transposed activations
-  size_t act, act_lo, wT, wT_lo;                          // forward operands
-  size_t dout, dout_lo, w, w_lo, actT, actT_lo, doutT, doutT_lo, splitk, splitk_bytes, colsum;  // backward
+  size_t act, act_lo, w, w_lo;                              // operands of forward and backward
+  size_t dout, dout_lo, splitk, splitk_bytes, colsum;       // backward only
   size_t total_fwd, total_bwd;
 };
 
@@ -31,23 +31,15 @@ LinPlan lin_plan(int64_t N, int K, int C, int precision) {
   LinPlan p;
   const bool bf16 = precision == AG_CE_BF16;
   p.es = bf16 ? 2 : 4;
-  p.ldn = up8(N);
   size_t off = 0;
   auto take = [&](size_t elems) { size_t o = off; off += up256(elems * p.es); return o; };
   p.act = take((size_t)N * K);
   p.act_lo = bf16 ? p.act : take((size_t)N * K);
-  p.wT = take((size_t)C * up8(K));
-  p.wT_lo = bf16 ? p.wT : take((size_t)C * up8(K));
-  p.total_fwd = off;
-  off = 0;
-  p.dout = take((size_t)N * C);
-  p.dout_lo = bf16 ? p.dout : take((size_t)N * C);
   p.w = take((size_t)K * C);
   p.w_lo = bf16 ? p.w : take((size_t)K * C);
-  p.actT = take((size_t)K * p.ldn);
-  p.actT_lo = bf16 ? p.actT : take((size_t)K * p.ldn);
-  p.doutT = take((size_t)C * p.ldn);
-  p.doutT_lo = bf16 ? p.doutT : take((size_t)C * p.ldn);
+  p.total_fwd = off;
+  p.dout = take((size_t)N * C);
+  p.dout_lo = bf16 ? p.dout : take((size_t)N * C);
   p.splitk = off;
   p.splitk_bytes = up256((size_t)16 * K * C * sizeof(float));
   off += p.splitk_bytes;
@@ -114,11 +106,11 @@ extern "C" int ag_linear_add_forward(ag_ctx* ctx, const float* x, const float* a
   AG_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "ag_linear_add_forward: scratch not 256-byte aligned");
   unsigned char* s = static_cast<unsigned char*>(scratch);
   const bool bf16 = precision == AG_CE_BF16;
-  // act -> (hi, lo) [N][K];  W [K][C] -> W^T (hi, lo) [C][ldk]
-  if ((rc = ag_tc_split(ctx, bf16, act, K, s + p.act, s + p.act_lo, K, nullptr, nullptr, 0, (int)N, K))) return rc;
-  if ((rc = ag_tc_split(ctx, bf16, w, C, nullptr, nullptr, 0, s + p.wT, s + p.wT_lo, up8(K), K, C))) return rc;
-  AgTcOperand A{s + p.act, s + p.act_lo, K};
-  AgTcOperand B{s + p.wT, s + p.wT_lo, up8(K)};
+  if ((rc = ag_tc_split(ctx, bf16, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
+  if ((rc = ag_tc_split(ctx, bf16, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
+  // B[n = C][k = K] is W[K][C] as stored with the contraction index as row index: MN-major
+  AgTcOperand A{s + p.act, s + p.act_lo, K, 0};
+  AgTcOperand B{s + p.w, s + p.w_lo, C, 1};
   return ag_tc_gemm(ctx, bf16, A, B, out, C, (int)N, C, K, false, b, x, C, nullptr, 0);
 }
 
@@ -149,22 +141,19 @@ extern "C" int ag_linear_add_backward(ag_ctx* ctx, const float* dout, const floa
     AG_LAUNCHED(ctx, "colsum_final_kernel");
   }
   if (!dact && !dw) return AG_OK;
-  // dout -> (hi, lo) [N][C] for dact and, transposed [C][ldn], for dW
-  if ((rc = ag_tc_split(ctx, bf16, dout, C, dact ? s + p.dout : nullptr, s + p.dout_lo, C, dw ? s + p.doutT : nullptr,
-                        s + p.doutT_lo, p.ldn, (int)N, C)))
-    return rc;
+  if ((rc = ag_tc_split(ctx, bf16, dout, C, s + p.dout, s + p.dout_lo, C, N, C))) return rc;
   if (dact) {
-    // dact[N,K] += dout[N,C] . (W[K,C])^T : W is K-major as stored
-    if ((rc = ag_tc_split(ctx, bf16, w, C, s + p.w, s + p.w_lo, C, nullptr, nullptr, 0, K, C))) return rc;
-    AgTcOperand A{s + p.dout, s + p.dout_lo, C};
-    AgTcOperand B{s + p.w, s + p.w_lo, C};
+    // dact[N,K] += dout[N,C] . (W[K,C])^T : both K-major as stored
+    if ((rc = ag_tc_split(ctx, bf16, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
+    AgTcOperand A{s + p.dout, s + p.dout_lo, C, 0};
+    AgTcOperand B{s + p.w, s + p.w_lo, C, 0};
     if ((rc = ag_tc_gemm(ctx, bf16, A, B, dact, K, (int)N, K, C, true, nullptr, nullptr, 0, nullptr, 0))) return rc;
   }
   if (dw) {
-    // dW[K,C] += act^T[K,N] . (dout^T[C,N])^T
-    if ((rc = ag_tc_split(ctx, bf16, act, K, nullptr, nullptr, 0, s + p.actT, s + p.actT_lo, p.ldn, (int)N, K))) return rc;
-    AgTcOperand A{s + p.actT, s + p.actT_lo, p.ldn};
-    AgTcOperand B{s + p.doutT, s + p.doutT_lo, p.ldn};
+    // dW[K,C] += act^T . dout : the contraction index (token row) is the row index of both as stored
+    if ((rc = ag_tc_split(ctx, bf16, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
+    AgTcOperand A{s + p.act, s + p.act_lo, K, 1};
+    AgTcOperand B{s + p.dout, s + p.dout_lo, C, 1};
     if ((rc = ag_tc_gemm(ctx, bf16, A, B, dw, C, K, C, (int)N, true, nullptr, nullptr, 0,
                          reinterpret_cast<float*>(s + p.splitk), p.splitk_bytes)))
       return rc;
