@@ -23,6 +23,7 @@ struct ag_ctx {
   cudaEvent_t* ev_pool;  // ag_event_record / ag_event_elapsed
   int ev_pool_size;
   int64_t launches;
+  int pdl;              // 1: bandwidth kernels are launched with programmatic stream serialization
   int tc_timing;        // ag_tc_timing: bracket tensor-core GEMM launches with pool events
   int tc_timing_base;
   int tc_timing_count;
@@ -56,6 +57,34 @@ struct ag_ctx {
       AG_FAIL(ctx, AG_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e_));  \
     (ctx)->launches++;                                                                      \
   } while (0)
+
+// Launch with programmatic stream serialization: the grid may be scheduled while the tail of the
+// previous kernel of the stream is still running, which hides the launch latency of short kernels.
+// A kernel launched this way must execute ag_pdl_wait() before its first access to global memory
+// (it returns once every earlier grid has completed and its writes are visible) and should execute
+// ag_pdl_trigger() early so that its own successor can be scheduled in the same way.
+#define AG_LAUNCH_PDL(ctx, name, kern, grid, block, smem, ...)                                  \
+  do {                                                                                          \
+    cudaLaunchConfig_t cfg_ = {};                                                               \
+    cfg_.gridDim = (grid);                                                                      \
+    cfg_.blockDim = (block);                                                                    \
+    cfg_.dynamicSmemBytes = (smem);                                                             \
+    cfg_.stream = (ctx)->stream;                                                                \
+    cudaLaunchAttribute at_[1];                                                                 \
+    at_[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                             \
+    at_[0].val.programmaticStreamSerializationAllowed = 1;                                      \
+    cfg_.attrs = at_;                                                                           \
+    cfg_.numAttrs = (ctx)->pdl ? 1 : 0;                                                         \
+    cudaError_t e_ = cudaLaunchKernelEx(&cfg_, kern, __VA_ARGS__);                              \
+    if (e_ != cudaSuccess)                                                                      \
+      AG_FAIL(ctx, AG_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e_));      \
+    (ctx)->launches++;                                                                          \
+  } while (0)
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void ag_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ag_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 static inline bool ag_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -57,6 +57,11 @@ extern "C" int ag_ctx_create(int device, void* stream, ag_ctx** out) {
     CREATE_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     c->own_stream = true;
   }
+  {
+    // AG_B200_PDL=0 launches every kernel fully serialized (diagnostics)
+    const char* e = getenv("AG_B200_PDL");
+    c->pdl = (e && e[0] == '0') ? 0 : 1;
+  }
   CREATE_CUDA(cudaMalloc(&c->d_status, sizeof(int)));
   CREATE_CUDA(cudaMemset(c->d_status, 0, sizeof(int)));
   CREATE_CUDA(cudaMallocHost(&c->h_status, sizeof(int)));

@@ -21,6 +21,8 @@ inline int ew_grid(const ag_ctx* ctx, int64_t packets) {
 //   void scalar(int64_t elem_index)                    - process one element (ragged tail)
 template <int NV, typename F>
 __device__ __forceinline__ void ew_drive(int64_t n, F& f) {
+  ag_pdl_wait();
+  ag_pdl_trigger();
   const int64_t packets = n / NV;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -182,15 +184,43 @@ __device__ __forceinline__ float sigmoid_ref(float g) {
   return __frcp_rn((FAST ? __expf(-g) : expf(-g)) + 1.0f);
 }
 
+// Position (row, packet in row) of a packet index that advances by a fixed step.
+struct RowWalk {
+  int64_t row, drow;
+  int col, dcol;
+  __device__ __forceinline__ void init(int64_t p, int ppr, int64_t step_packets) {
+    row = p / ppr;
+    col = (int)(p - row * ppr);
+    drow = step_packets / ppr;
+    dcol = (int)(step_packets - drow * ppr);
+  }
+  __device__ __forceinline__ void step(int ppr) {
+    row += drow;
+    col += dcol;
+    if (col >= ppr) {
+      col -= ppr;
+      ++row;
+    }
+  }
+};
+
 // One thread handles packets of the same column range in the gate and up halves of a row.
 template <typename T>
 __global__ void __launch_bounds__(EW_THREADS) swiglu_forward_kernel(const T* __restrict__ gu, T* __restrict__ hidden,
                                                                     int64_t N, int I) {
+  ag_pdl_wait();
+  ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
   const int ppr = I / NV;  // packets per row (I % NV == 0 on this path)
   const int64_t packets = N * (int64_t)ppr;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < packets; i += 2 * stride) {
+  // (row, packet-in-row) of the two packets of an iteration advance by a fixed step: one 64-bit
+  // division per thread instead of two per iteration (they would cost as much as the activation)
+  const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  RowWalk w[2];
+  w[0].init(i0, ppr, 2 * stride);
+  w[1].init(i0 + stride, ppr, 2 * stride);
+  for (int64_t i = i0; i < packets; i += 2 * stride) {
     float g[2][NV], u[2][NV];
     bool live[2];
 #pragma unroll
@@ -198,11 +228,12 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_forward_kernel(const T* __r
       const int64_t p = i + k * stride;
       live[k] = p < packets;
       if (live[k]) {
-        const int64_t row = p / ppr;
-        const int col = (int)(p - row * ppr) * NV;
+        const int64_t row = w[k].row;
+        const int col = w[k].col * NV;
         Pack<T>::load_stream(gu + row * 2 * I + col, g[k]);
         Pack<T>::load_stream(gu + row * 2 * I + I + col, u[k]);
       }
+      w[k].step(ppr);
     }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
@@ -245,11 +276,17 @@ __device__ __forceinline__ void swiglu_bwd1(float g, float u, float dh, float& d
 template <typename T>
 __global__ void __launch_bounds__(EW_THREADS) swiglu_backward_kernel(T* __restrict__ gu, const T* __restrict__ dh,
                                                                      int64_t N, int I) {
+  ag_pdl_wait();
+  ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
   const int ppr = I / NV;
   const int64_t packets = N * (int64_t)ppr;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < packets; i += 2 * stride) {
+  const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  RowWalk w[2];
+  w[0].init(i0, ppr, 2 * stride);
+  w[1].init(i0 + stride, ppr, 2 * stride);
+  for (int64_t i = i0; i < packets; i += 2 * stride) {
     float g[2][NV], u[2][NV], d[2][NV];
     bool live[2];
     int64_t goff[2];
@@ -258,13 +295,12 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_backward_kernel(T* __restri
       const int64_t p = i + k * stride;
       live[k] = p < packets;
       if (live[k]) {
-        const int64_t row = p / ppr;
-        const int col = (int)(p - row * ppr) * NV;
-        goff[k] = row * 2 * I + col;
+        goff[k] = w[k].row * 2 * I + w[k].col * NV;
         Pack<T>::load(gu + goff[k], g[k]);
         Pack<T>::load(gu + goff[k] + I, u[k]);
         Pack<T>::load_stream(dh + p * NV, d[k]);
       }
+      w[k].step(ppr);
     }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
@@ -357,8 +393,7 @@ extern "C" int ag_add_forward(ag_ctx* ctx, const float* x, const float* y, float
   if (n == 0) return AG_OK;
   AG_REQUIRE(ctx, x && y && out && n > 0, "ag_add_forward: null pointer or negative n");
   AG_REQUIRE(ctx, all_aligned16(x, y, out), "ag_add_forward: pointers must be 16-byte aligned");
-  add_forward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(AddFwd{x, y, out}, n);
-  AG_LAUNCHED(ctx, "add_forward_kernel");
+  AG_LAUNCH_PDL(ctx, "add_forward_kernel", add_forward_kernel, ew_grid(ctx, n / 4), EW_THREADS, 0, AddFwd{x, y, out}, n);
   return AG_OK;
 }
 
@@ -367,8 +402,7 @@ extern "C" int ag_add_backward(ag_ctx* ctx, const float* g, float* xgrad, float*
   if (n == 0 || (!xgrad && !ygrad)) return AG_OK;
   AG_REQUIRE(ctx, g && n > 0, "ag_add_backward: null g or negative n");
   AG_REQUIRE(ctx, all_aligned16(g, xgrad, ygrad), "ag_add_backward: pointers must be 16-byte aligned");
-  add_backward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(AddBwd{g, xgrad, ygrad}, n);
-  AG_LAUNCHED(ctx, "add_backward_kernel");
+  AG_LAUNCH_PDL(ctx, "add_backward_kernel", add_backward_kernel, ew_grid(ctx, n / 4), EW_THREADS, 0, AddBwd{g, xgrad, ygrad}, n);
   return AG_OK;
 }
 
@@ -377,8 +411,7 @@ extern "C" int ag_gelu_forward(ag_ctx* ctx, const float* x, float* y, int64_t n)
   if (n == 0) return AG_OK;
   AG_REQUIRE(ctx, x && y && n > 0, "ag_gelu_forward: null pointer or negative n");
   AG_REQUIRE(ctx, all_aligned16(x, y), "ag_gelu_forward: pointers must be 16-byte aligned");
-  gelu_forward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(GeluFwd{x, y}, n);
-  AG_LAUNCHED(ctx, "gelu_forward_kernel");
+  AG_LAUNCH_PDL(ctx, "gelu_forward_kernel", gelu_forward_kernel, ew_grid(ctx, n / 4), EW_THREADS, 0, GeluFwd{x, y}, n);
   return AG_OK;
 }
 
@@ -388,8 +421,7 @@ extern "C" int ag_gelu_backward(ag_ctx* ctx, const float* x, const float* dy, co
   if (n == 0) return AG_OK;
   AG_REQUIRE(ctx, x && dy && dx && n > 0, "ag_gelu_backward: null pointer or negative n");
   AG_REQUIRE(ctx, all_aligned16(x, dy, dres, dx), "ag_gelu_backward: pointers must be 16-byte aligned");
-  gelu_backward_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(GeluBwd{x, dy, dres, dx}, n);
-  AG_LAUNCHED(ctx, "gelu_backward_kernel");
+  AG_LAUNCH_PDL(ctx, "gelu_backward_kernel", gelu_backward_kernel, ew_grid(ctx, n / 4), EW_THREADS, 0, GeluBwd{x, dy, dres, dx}, n);
   return AG_OK;
 }
 
@@ -398,9 +430,8 @@ static int swiglu_forward_t(ag_ctx* ctx, const void* gu, void* hidden, int64_t N
   constexpr int NV = Pack<T>::N;
   if (I % NV == 0 && all_aligned16(gu, hidden)) {
     const int64_t packets = N * (int64_t)(I / NV);
-    swiglu_forward_kernel<T><<<ew_grid(ctx, packets * 2), EW_THREADS, 0, ctx->stream>>>(
-        static_cast<const T*>(gu), static_cast<T*>(hidden), N, I);
-    AG_LAUNCHED(ctx, "swiglu_forward_kernel");
+    AG_LAUNCH_PDL(ctx, "swiglu_forward_kernel", swiglu_forward_kernel<T>, ew_grid(ctx, packets * 2), EW_THREADS, 0,
+                  static_cast<const T*>(gu), static_cast<T*>(hidden), N, I);
   } else {
     swiglu_forward_scalar_kernel<T><<<ew_grid(ctx, N * (int64_t)I), EW_THREADS, 0, ctx->stream>>>(
         static_cast<const T*>(gu), static_cast<T*>(hidden), N, I);
@@ -414,9 +445,8 @@ static int swiglu_backward_t(ag_ctx* ctx, void* gu, const void* dh, int64_t N, i
   constexpr int NV = Pack<T>::N;
   if (I % NV == 0 && all_aligned16(gu, dh)) {
     const int64_t packets = N * (int64_t)(I / NV);
-    swiglu_backward_kernel<T><<<ew_grid(ctx, packets * 2), EW_THREADS, 0, ctx->stream>>>(
-        static_cast<T*>(gu), static_cast<const T*>(dh), N, I);
-    AG_LAUNCHED(ctx, "swiglu_backward_kernel");
+    AG_LAUNCH_PDL(ctx, "swiglu_backward_kernel", swiglu_backward_kernel<T>, ew_grid(ctx, packets * 2), EW_THREADS, 0,
+                  static_cast<T*>(gu), static_cast<const T*>(dh), N, I);
   } else {
     swiglu_backward_scalar_kernel<T><<<ew_grid(ctx, N * (int64_t)I), EW_THREADS, 0, ctx->stream>>>(
         static_cast<T*>(gu), static_cast<const T*>(dh), N, I);
@@ -460,7 +490,6 @@ extern "C" int ag_adamw_step(ag_ctx* ctx, float* p, const float* g, float* m, fl
   f.one_minus_b2 = (float)(1.0 - b2);
   f.eps = (float)eps; f.grad_scale = (float)grad_scale;
   f.decay = weight_decay > 0.0;
-  adamw_kernel<<<ew_grid(ctx, n / 4), EW_THREADS, 0, ctx->stream>>>(f, n);
-  AG_LAUNCHED(ctx, "adamw_kernel");
+  AG_LAUNCH_PDL(ctx, "adamw_kernel", adamw_kernel, ew_grid(ctx, n / 4), EW_THREADS, 0, f, n);
   return AG_OK;
 }

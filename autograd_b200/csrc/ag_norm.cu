@@ -30,7 +30,11 @@ template <typename T, int KP, int KIND>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_forward_kernel(const T* x, const T* r, const float* __restrict__ gamma,
                     const float* __restrict__ beta, T* h, T* __restrict__ y, float* __restrict__ stat0,
-                    float* __restrict__ stat1, int64_t N, int C, float eps, int* status) {
+                    float* __restrict__ stat1, int64_t N, int C, float eps, int* status, int pdl_early) {
+  ag_pdl_wait();
+  // Early trigger only when the whole grid is resident at once: otherwise the next kernel's CTAs,
+  // which only wait, would take SM slots from this grid's later waves.
+  if (pdl_early) ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* s_gamma = reinterpret_cast<float*>(smem_raw);
@@ -237,7 +241,9 @@ template <typename T, int KP, int KIND>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
                      const T* dres, T* dx, float* __restrict__ partials, int want_dgamma, int want_dbeta, int64_t N,
-                     int C, float eps, int* status) {
+                     int C, float eps, int* status, int pdl_early) {
+  ag_pdl_wait();
+  if (pdl_early) ag_pdl_trigger();  // see norm_forward_kernel
   constexpr int NV = Pack<T>::N;
   constexpr int SLOTS = norm_bwd_slots<KIND>();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -490,14 +496,26 @@ norm_backward_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, 
 // 32 group sums are then added in group order.  Fixed order, no atomics.
 __global__ void __launch_bounds__(1024)
 norm_partials_reduce_kernel(const float* __restrict__ partials, int P, int C, float* dgamma, float* dbeta) {
+  ag_pdl_wait();
+  ag_pdl_trigger();
   __shared__ float s[32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   const int slot = blockIdx.y;
   float* out = slot == 0 ? dgamma : dbeta;
   if (!out) return;  // uniform per block
   float t = 0.0f;
-  if (c < C)
-    for (int p = threadIdx.y; p < P; p += 32) t += partials[((int64_t)p * 2 + slot) * C + c];
+  if (c < C) {
+    // eight loads in flight per thread, added in row order
+    int p = threadIdx.y;
+    for (; p + 7 * 32 < P; p += 8 * 32) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = partials[((int64_t)(p + j * 32) * 2 + slot) * C + c];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t += v[j];
+    }
+    for (; p < P; p += 32) t += partials[((int64_t)p * 2 + slot) * C + c];
+  }
   s[threadIdx.y][threadIdx.x] = t;
   __syncthreads();
   if (threadIdx.y == 0 && c < C) {
@@ -560,9 +578,9 @@ int launch_fwd_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const
   static size_t occ_smem = 0;
   const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
   if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_forward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
-  kern<<<persistent_grid(ctx, N, occ), NORM_THREADS, smem, ctx->stream>>>(x, r, gamma, beta, h, y, s0, s1, N, C, eps,
-                                                                          ctx->d_status);
-  AG_LAUNCHED(ctx, "norm_forward_kernel");
+  const int grid = persistent_grid(ctx, N, occ);
+  AG_LAUNCH_PDL(ctx, "norm_forward_kernel", kern, grid, NORM_THREADS, smem, x, r, gamma, beta, h, y, s0, s1, N, C, eps,
+                ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
   return AG_OK;
 }
 
@@ -607,8 +625,8 @@ int launch_bwd_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, cons
   const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
   if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
   const int grid = persistent_grid(ctx, N, occ, max_partial_rows(ctx));
-  kern<<<grid, NORM_THREADS, smem, ctx->stream>>>(dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, ctx->d_status);
-  AG_LAUNCHED(ctx, "norm_backward_kernel");
+  AG_LAUNCH_PDL(ctx, "norm_backward_kernel", kern, grid, NORM_THREADS, smem, dy, x, gamma, dres, dx, partials, wg, wb, N, C,
+                eps, ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
   *grid_out = grid;
   return AG_OK;
 }
@@ -654,9 +672,8 @@ int launch_bwd(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T
   }
   if (wg || wb) {
     dim3 rgrid((C + 31) / 32, KIND == kLayerNorm ? 2 : 1);
-    norm_partials_reduce_kernel<<<rgrid, dim3(32, 32), 0, ctx->stream>>>(partials, grid, C, wg ? dgamma : nullptr,
-                                                                         wb ? dbeta : nullptr);
-    AG_LAUNCHED(ctx, "norm_partials_reduce_kernel");
+    AG_LAUNCH_PDL(ctx, "norm_partials_reduce_kernel", norm_partials_reduce_kernel, rgrid, dim3(32, 32), 0,
+                  (const float*)partials, grid, C, wg ? dgamma : (float*)nullptr, wb ? dbeta : (float*)nullptr);
   }
   return AG_OK;
 }
@@ -785,8 +802,8 @@ int ln_noalloc_launch_kp(ag_ctx* ctx, const float* dy, const float* x, const flo
     AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
   int grid = persistent_grid(ctx, N, occ);
   if (grid > max_grid) grid = max_grid;
-  kern<<<grid, NORM_THREADS, smem, ctx->stream>>>(dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, ctx->d_status);
-  AG_LAUNCHED(ctx, "norm_backward_kernel");
+  AG_LAUNCH_PDL(ctx, "norm_backward_kernel", kern, grid, NORM_THREADS, smem, dy, x, gamma, dres, dx, partials, wg, wb, N, C,
+                eps, ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
   *grid_out = grid;
   return AG_OK;
 }
@@ -840,9 +857,8 @@ extern "C" int ag_layernorm_backward_noalloc(ag_ctx* ctx, const float* dy, const
   }
   if (wg || wb) {
     dim3 rgrid((C + 31) / 32, 2);
-    norm_partials_reduce_kernel<<<rgrid, dim3(32, 32), 0, ctx->stream>>>(partials, grid, C, wg ? dgamma : nullptr,
-                                                                         wb ? dbeta : nullptr);
-    AG_LAUNCHED(ctx, "norm_partials_reduce_kernel");
+    AG_LAUNCH_PDL(ctx, "norm_partials_reduce_kernel", norm_partials_reduce_kernel, rgrid, dim3(32, 32), 0,
+                  (const float*)partials, grid, C, wg ? dgamma : (float*)nullptr, wb ? dbeta : (float*)nullptr);
   }
   return AG_OK;
 }

@@ -17,6 +17,8 @@ template <typename T>
 __global__ void __launch_bounds__(ROPE_THREADS)
 rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int64_t tokens, int T_len,
             int H, int HKV, int D, int64_t q_stride, int64_t k_stride, float sgn) {
+  ag_pdl_wait();
+  ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
   constexpr int ROPE_MAX_ITEMS = ROPE_MAX_BYTES / 16 * 4 / NV;  // 4 packet pairs for fp32, 2 for bf16
   const int d2 = D >> 1;
@@ -109,9 +111,8 @@ int rope_t(ag_ctx* ctx, void* qv, void* kv, const float* cos_tab, const float* s
     const int hkv = k ? HKV : 0;
     const int64_t total = tokens * (int64_t)((H + hkv) * (d2 / NV));
     const int64_t per_cta = (int64_t)ROPE_THREADS * (ROPE_MAX_BYTES / 16 * 4 / NV);
-    rope_kernel<T><<<(unsigned)((total + per_cta - 1) / per_cta), ROPE_THREADS, 0, ctx->stream>>>(
-        q, k, cos_tab, sin_tab, tokens, T_len, H, hkv, D, qs, ks, sgn);
-    AG_LAUNCHED(ctx, "rope_kernel");
+    AG_LAUNCH_PDL(ctx, "rope_kernel", rope_kernel<T>, (unsigned)((total + per_cta - 1) / per_cta), ROPE_THREADS, 0, q, k,
+                  cos_tab, sin_tab, tokens, T_len, H, hkv, D, qs, ks, sgn);
   } else {
     rope_scalar_kernel<T><<<(unsigned)tokens, ROPE_THREADS, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H,
                                                                               k ? HKV : 0, D, qs, ks, sgn);

@@ -40,6 +40,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--ce-precision", default="3xtf32", choices=["fp32", "3xtf32", "bf16"])
+    ap.add_argument("--no-bf16-mode", action="store_true", help="skip the extra timing of the bf16 CE mode")
     # reduced shapes for profiler captures and tests; the defaults are the benchmark workload
     ap.add_argument("--layers", type=int, default=20)
     ap.add_argument("--batch", type=int, default=16)
@@ -50,6 +51,7 @@ def parse_args():
                     help="step: the fused-layer step (the benchmark); kernels: one JSON line per fused layer "
                          "kernel at the shapes of BASELINE configs 1-4, each against its own roofline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="", help="--workload kernels: comma-separated sections (cfg1,gelu,cfg3,cfg4,cfg2)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=2048)
     ap.add_argument("--cpu-sample-layers", type=int, default=2)
     return ap.parse_args()
@@ -280,20 +282,23 @@ def run_b200(a):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The clock sampler starts before the warm-up steps: nvidia-smi takes the driver's lock while it
+    # initialises, which would otherwise stall this process's launches inside the timed region.  The
+    # warm-up steps run the same kernels, so its samples are under load as well.
+    sampler = ClockSampler(local)
+    sampler.start()
     load(0)
     for i in range(a.warmup):
         one_step(i, e2e=True)
     ctx.check_status()
 
     EV0, EV1 = (1 << 20), (1 << 20) + 1   # event indices outside the family timer's range
-    sampler = ClockSampler(local)
 
     # ---- device-resident timing with per-family events inside the timed region
     step.timer.reset()
     step.timer.enabled = True
     TC_BASE = 1 << 19                     # events of the per-launch timing of the tensor-core GEMM
     barrier()
-    sampler.start()
     launches0 = ctx.launch_count
     ctx.tc_timing(True, TC_BASE)
     ctx.event_record(EV0)
@@ -323,10 +328,28 @@ def run_b200(a):
     clocks = sampler.stop()
     ctx.check_status()
 
+    # ---- the stated bf16 mode of the CE head (operands rounded to bf16, 2e-2 tolerance), same step otherwise;
+    # reported beside the headline, never as it
+    ms_bf16 = None
+    if a.ce_precision == "3xtf32" and not a.no_bf16_mode:
+        step.desc = ctx.flce_desc(Nn, cfg.n_embd, cfg.vocab, vocab_chunk=cfg.ce_vocab_chunk, precision=ag.AG_CE_BF16)
+        assert ctx.flce_scratch_bytes(step.desc) <= step.flce_bytes
+        for i in range(max(a.warmup, 3)):
+            one_step(i, e2e=False)
+        barrier()
+        ctx.event_record(EV0)
+        for i in range(a.steps):
+            one_step(i, e2e=False)
+        ctx.event_record(EV1)
+        barrier()
+        ms_bf16 = ctx.event_elapsed_ms(EV0, EV1)
+        ctx.check_status()
+
     if world > 1:
-        t = torch.tensor([ms_dev, ms_e2e], device=f"cuda:{local}", dtype=torch.float64)
+        t = torch.tensor([ms_dev, ms_e2e, ms_bf16 or 0.0], device=f"cuda:{local}", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e = float(t[0]), float(t[1])
+        ms_bf16 = float(t[2]) if ms_bf16 is not None else None
 
     if rank == 0:
         tokens = Nn * world
@@ -414,6 +437,10 @@ def run_b200(a):
             "cpu_baseline": cpu,
             "loss": last_loss,
         }
+        if ms_bf16 is not None:
+            line["ce_bf16_mode"] = {"ms_per_step": ms_bf16 / a.steps, "value": tokens / (ms_bf16 / a.steps / 1e3),
+                                    "unit": UNIT, "note": "same step with the CE head's GEMM operands rounded to bf16 "
+                                                          "(fp32 accumulation, 2e-2 tolerance); not the headline"}
         print(json.dumps(line), flush=True)
     step.close()
     ctx.free_host(host)
@@ -492,106 +519,123 @@ def run_kernels(a):
         print(json.dumps(line), flush=True)
 
     f4 = 4
-    # ---- config 1: fused add + LayerNorm, 16384 x 384 (and the config-5 width 32768 x 1280)
-    for (N, C) in ((16384, 384), (32768, 1280)):
-        nb = N * C * f4
-        n_sets = sets_for(4 * nb)
-        x = [dev(N * C) for _ in range(n_sets)]; r = [dev(N * C) for _ in range(n_sets)]
-        h = [dev(N * C) for _ in range(n_sets)]; y = [dev(N * C) for _ in range(n_sets)]
-        gam, bet, dg, db = dev(C), dev(C), dev(C), dev(C)
-        pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
-        ms = time_it(lambda i: ctx.add_layernorm_forward(x[i], r[i], gam, bet, h[i], y[i], 0, 0, N, C, 1e-5), n_sets)
-        emit("cfg1" if C == 384 else "cfg5-width", f"add_layernorm_forward {N}x{C}", ms, N, alg_bytes=4 * nb)
-        # backward: dy = y[i], saved input = h[i], residual gradient accumulated in place in x[i]
-        ms = time_it(lambda i: ctx.layernorm_backward(y[i], h[i], gam, x[i], x[i], dg, db, part.ptr.address, pb, N, C,
-                                                      1e-5), n_sets)
-        emit("cfg1" if C == 384 else "cfg5-width", f"layernorm_backward(+residual grad) {N}x{C}", ms, N, alg_bytes=4 * nb)
-        free_all()
-    # ---- GELU 16384 x 1536
-    n = 16384 * 1536
-    n_sets = sets_for(3 * n * f4)
-    x = [dev(n) for _ in range(n_sets)]; y = [dev(n) for _ in range(n_sets)]; g = [dev(n) for _ in range(n_sets)]
-    ms = time_it(lambda i: ctx.gelu_forward(x[i], y[i], n), n_sets)
-    emit("gelu", "gelu_forward 16384x1536", ms, 16384, alg_bytes=2 * n * f4)
-    ms = time_it(lambda i: ctx.gelu_backward(x[i], y[i], 0, g[i], n), n_sets)
-    emit("gelu", "gelu_backward 16384x1536", ms, 16384, alg_bytes=3 * n * f4)
-    free_all()
-    # ---- config 3: RMSNorm, RoPE, SwiGLU at the Qwen shapes, fp32 and bf16 storage
-    N, C, H, HKV, D, I, B, T = 8192, 1536, 12, 2, 128, 8960, 4, 2048
-    for dt_name, dt, es in (("f32", np.float32, 4), ("bf16", np.uint16, 2)):
-        agdt = ag.AG_F32 if es == 4 else ag.AG_BF16
-        n_sets = sets_for(3 * N * C * es)
-        x = [dev(N * C, dt) for _ in range(n_sets)]; y = [dev(N * C, dt) for _ in range(n_sets)]
-        d = [dev(N * C, dt) for _ in range(n_sets)]
-        gam, dg = dev(C), dev(C)
-        pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
-        ms = time_it(lambda i: ctx.rmsnorm_forward(x[i], gam, y[i], 0, N, C, 1e-6, agdt), n_sets)
-        emit("cfg3", "rmsnorm_forward 8192x1536", ms, N, alg_bytes=2 * N * C * es, dtype=dt_name)
-        ms = time_it(lambda i: ctx.rmsnorm_backward(y[i], x[i], gam, d[i], d[i], dg, part.ptr.address, pb, N, C, 1e-6,
-                                                    agdt), n_sets)
-        emit("cfg3", "rmsnorm_backward(+residual grad) 8192x1536", ms, N, alg_bytes=4 * N * C * es, dtype=dt_name)
-        free_all()
-        nq, nk = N * H * D, N * HKV * D
-        n_sets = sets_for((nq + nk) * es)
-        q = [dev(nq, dt) for _ in range(n_sets)]; k = [dev(nk, dt) for _ in range(n_sets)]
-        from oracle import fused_layers as O   # table formula only (module.py:247-250); not the thing measured
-        cos_, sin_ = O.rope_tables(T, D, 1e6)
-        cos = dev(cos_.size); sin = dev(sin_.size)
-        ctx.copy_from_host(cos, cos_); ctx.copy_from_host(sin, sin_)
-        ms = time_it(lambda i: ctx.rope_qk(q[i], k[i], cos, sin, B, T, H, HKV, D, sin_sign=1, dtype=agdt), n_sets)
-        emit("cfg3", "rope_qk 4x2048 q12 k2 d128", ms, N, alg_bytes=2 * (nq + nk) * es, dtype=dt_name)
-        free_all()
-        n_sets = sets_for(4 * N * I * es)
-        gu = [dev(N * 2 * I, dt) for _ in range(n_sets)]; hid = [dev(N * I, dt) for _ in range(n_sets)]
-        ms = time_it(lambda i: ctx.swiglu_forward(gu[i], hid[i], N, I, agdt), n_sets)
-        emit("cfg3", "swiglu_forward 8192x8960", ms, N, alg_bytes=3 * N * I * es, dtype=dt_name)
-        ms = time_it(lambda i: ctx.swiglu_backward(gu[i], hid[i], N, I, agdt), n_sets)
-        emit("cfg3", "swiglu_backward_inplace 8192x8960", ms, N, alg_bytes=5 * N * I * es, dtype=dt_name)
-        free_all()
-    # ---- config 4: gather / deterministic scatter-add, Zipf(1.1) ids
-    V, C, n = 151936, 1536, 65536
-    rng = np.random.default_rng(1237)
-    p = 1.0 / np.arange(1, V + 1) ** 1.1
-    p /= p.sum()
-    ids_ = rng.choice(V, size=n, p=p).astype(np.int32)
-    uniq = int(np.unique(ids_).size)
-    ids = dev(n, np.int32, ints=ids_)
-    table = dev(V * C, std=0.02); dtable = dev(V * C)
-    n_sets = 2
-    out = [dev(n * C) for _ in range(n_sets)]
-    sb = ctx.scatter_add_scratch_bytes(n, C, V); sc = alloc.alloc((sb,), np.uint8); bufs.append(sc)
-    ms = time_it(lambda i: ctx.gather_forward(ids, table, out[i], n, C, V), n_sets)
-    emit("cfg4", "gather_forward 65536 ids x 1536", ms, n, alg_bytes=2 * n * C * f4,
-         extra={"unique_rows": uniq, "unique_row_lower_bound_bytes": (n + uniq) * C * f4})
-    ctx.fill_f32(dtable, 0.0, V * C)
-    ms = time_it(lambda i: ctx.gather_backward(ids, out[i], dtable, sc.ptr.address, sb, n, C, V), n_sets)
-    emit("cfg4", "scatter_add (sort + segmented sum) 65536 ids x 1536", ms, n, alg_bytes=(n + 2 * uniq) * C * f4,
-         extra={"unique_rows": uniq, "note": "without the dense zero-fill of dTable"})
-    ms0 = time_it(lambda i: ctx.fill_f32(dtable, 0.0, V * C), 1)
-    emit("cfg4", "zero-fill of dTable 151936x1536", ms0, n, alg_bytes=V * C * f4)
-    free_all()
-    # ---- config 2: fused linear + CE, N 16384, V 32768, C 384 and 1280
-    N, V = 16384, 32768
-    tg_ = rng.integers(0, V, size=N).astype(np.int32)
-    tg_[rng.random(N) < 0.05] = -1
-    for C in (384, 1280):
-        for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16", ag.AG_CE_BF16)):
-            X = dev(N * C, std=1.0 / np.sqrt(C)); W = dev(V * C, std=0.02)
-            dX, dW = dev(N * C), dev(V * C)
-            tg = dev(N, np.int32, ints=tg_)
-            loss, dloss, lse = dev(1), dev(1), dev(N)
-            ctx.fill_f32(dloss, 1.0, 1)
-            desc = ctx.flce_desc(N, C, V, vocab_chunk=4096, precision=prec)
-            sbytes = ctx.flce_scratch_bytes(desc); scr = alloc.alloc((sbytes,), np.uint8); bufs.append(scr)
-            ms_f = time_it(lambda i: ctx.flce_forward(desc, X, W, tg, 0, loss, lse, scr.ptr.address, sbytes), 1)
-            ms_b = time_it(lambda i: ctx.flce_backward(desc, X, W, tg, 0, dloss, lse, dX, dW, scr.ptr.address, sbytes), 1)
-            fl = 2.0 * N * C * V
-            emit("cfg2", f"fused_linear_ce forward N16384 C{C} V32768", ms_f, N, useful_flops=fl, dtype=pname)
-            emit("cfg2", f"fused_linear_ce backward N16384 C{C} V32768", ms_b, N, useful_flops=2 * fl, dtype=pname,
-                 extra={"executed_flops": 3 * fl})
-            emit("cfg2", f"fused_linear_ce fwd+bwd N16384 C{C} V32768", ms_f + ms_b, N, useful_flops=3 * fl, dtype=pname,
-                 extra={"scratch_bytes": sbytes})
+    def sec_cfg1():
+        # ---- config 1: fused add + LayerNorm, 16384 x 384 (and the config-5 width 32768 x 1280)
+        for (N, C) in ((16384, 384), (32768, 1280)):
+            nb = N * C * f4
+            n_sets = sets_for(4 * nb)
+            x = [dev(N * C) for _ in range(n_sets)]; r = [dev(N * C) for _ in range(n_sets)]
+            h = [dev(N * C) for _ in range(n_sets)]; y = [dev(N * C) for _ in range(n_sets)]
+            gam, bet, dg, db = dev(C), dev(C), dev(C), dev(C)
+            pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
+            ms = time_it(lambda i: ctx.add_layernorm_forward(x[i], r[i], gam, bet, h[i], y[i], 0, 0, N, C, 1e-5), n_sets)
+            emit("cfg1" if C == 384 else "cfg5-width", f"add_layernorm_forward {N}x{C}", ms, N, alg_bytes=4 * nb)
+            # backward: dy = y[i], saved input = h[i], residual gradient accumulated in place in x[i]
+            ms = time_it(lambda i: ctx.layernorm_backward(y[i], h[i], gam, x[i], x[i], dg, db, part.ptr.address, pb, N, C,
+                                                          1e-5), n_sets)
+            emit("cfg1" if C == 384 else "cfg5-width", f"layernorm_backward(+residual grad) {N}x{C}", ms, N, alg_bytes=4 * nb)
             free_all()
+
+    def sec_gelu():
+        # ---- GELU 16384 x 1536
+        n = 16384 * 1536
+        n_sets = sets_for(3 * n * f4)
+        x = [dev(n) for _ in range(n_sets)]; y = [dev(n) for _ in range(n_sets)]; g = [dev(n) for _ in range(n_sets)]
+        ms = time_it(lambda i: ctx.gelu_forward(x[i], y[i], n), n_sets)
+        emit("gelu", "gelu_forward 16384x1536", ms, 16384, alg_bytes=2 * n * f4)
+        ms = time_it(lambda i: ctx.gelu_backward(x[i], y[i], 0, g[i], n), n_sets)
+        emit("gelu", "gelu_backward 16384x1536", ms, 16384, alg_bytes=3 * n * f4)
+        free_all()
+
+    def sec_cfg3():
+        # ---- config 3: RMSNorm, RoPE, SwiGLU at the Qwen shapes, fp32 and bf16 storage
+        N, C, H, HKV, D, I, B, T = 8192, 1536, 12, 2, 128, 8960, 4, 2048
+        for dt_name, dt, es in (("f32", np.float32, 4), ("bf16", np.uint16, 2)):
+            agdt = ag.AG_F32 if es == 4 else ag.AG_BF16
+            n_sets = sets_for(3 * N * C * es)
+            x = [dev(N * C, dt) for _ in range(n_sets)]; y = [dev(N * C, dt) for _ in range(n_sets)]
+            d = [dev(N * C, dt) for _ in range(n_sets)]
+            gam, dg = dev(C), dev(C)
+            pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
+            ms = time_it(lambda i: ctx.rmsnorm_forward(x[i], gam, y[i], 0, N, C, 1e-6, agdt), n_sets)
+            emit("cfg3", "rmsnorm_forward 8192x1536", ms, N, alg_bytes=2 * N * C * es, dtype=dt_name)
+            ms = time_it(lambda i: ctx.rmsnorm_backward(y[i], x[i], gam, d[i], d[i], dg, part.ptr.address, pb, N, C, 1e-6,
+                                                        agdt), n_sets)
+            emit("cfg3", "rmsnorm_backward(+residual grad) 8192x1536", ms, N, alg_bytes=4 * N * C * es, dtype=dt_name)
+            free_all()
+            nq, nk = N * H * D, N * HKV * D
+            n_sets = sets_for((nq + nk) * es)
+            q = [dev(nq, dt) for _ in range(n_sets)]; k = [dev(nk, dt) for _ in range(n_sets)]
+            from oracle import fused_layers as O   # table formula only (module.py:247-250); not the thing measured
+            cos_, sin_ = O.rope_tables(T, D, 1e6)
+            cos = dev(cos_.size); sin = dev(sin_.size)
+            ctx.copy_from_host(cos, cos_); ctx.copy_from_host(sin, sin_)
+            ms = time_it(lambda i: ctx.rope_qk(q[i], k[i], cos, sin, B, T, H, HKV, D, sin_sign=1, dtype=agdt), n_sets)
+            emit("cfg3", "rope_qk 4x2048 q12 k2 d128", ms, N, alg_bytes=2 * (nq + nk) * es, dtype=dt_name)
+            free_all()
+            n_sets = sets_for(4 * N * I * es)
+            gu = [dev(N * 2 * I, dt) for _ in range(n_sets)]; hid = [dev(N * I, dt) for _ in range(n_sets)]
+            ms = time_it(lambda i: ctx.swiglu_forward(gu[i], hid[i], N, I, agdt), n_sets)
+            emit("cfg3", "swiglu_forward 8192x8960", ms, N, alg_bytes=3 * N * I * es, dtype=dt_name)
+            ms = time_it(lambda i: ctx.swiglu_backward(gu[i], hid[i], N, I, agdt), n_sets)
+            emit("cfg3", "swiglu_backward_inplace 8192x8960", ms, N, alg_bytes=5 * N * I * es, dtype=dt_name)
+            free_all()
+
+    def sec_cfg4():
+        # ---- config 4: gather / deterministic scatter-add, Zipf(1.1) ids
+        V, C, n = 151936, 1536, 65536
+        rng = np.random.default_rng(1237)
+        p = 1.0 / np.arange(1, V + 1) ** 1.1
+        p /= p.sum()
+        ids_ = rng.choice(V, size=n, p=p).astype(np.int32)
+        uniq = int(np.unique(ids_).size)
+        ids = dev(n, np.int32, ints=ids_)
+        table = dev(V * C, std=0.02); dtable = dev(V * C)
+        n_sets = 2
+        out = [dev(n * C) for _ in range(n_sets)]
+        sb = ctx.scatter_add_scratch_bytes(n, C, V); sc = alloc.alloc((sb,), np.uint8); bufs.append(sc)
+        ms = time_it(lambda i: ctx.gather_forward(ids, table, out[i], n, C, V), n_sets)
+        emit("cfg4", "gather_forward 65536 ids x 1536", ms, n, alg_bytes=2 * n * C * f4,
+             extra={"unique_rows": uniq, "unique_row_lower_bound_bytes": (n + uniq) * C * f4})
+        ctx.fill_f32(dtable, 0.0, V * C)
+        ms = time_it(lambda i: ctx.gather_backward(ids, out[i], dtable, sc.ptr.address, sb, n, C, V), n_sets)
+        emit("cfg4", "scatter_add (sort + segmented sum) 65536 ids x 1536", ms, n, alg_bytes=(n + 2 * uniq) * C * f4,
+             extra={"unique_rows": uniq, "note": "without the dense zero-fill of dTable"})
+        ms0 = time_it(lambda i: ctx.fill_f32(dtable, 0.0, V * C), 1)
+        emit("cfg4", "zero-fill of dTable 151936x1536", ms0, n, alg_bytes=V * C * f4)
+        free_all()
+
+    def sec_cfg2():
+        # ---- config 2: fused linear + CE, N 16384, V 32768, C 384 and 1280
+        N, V = 16384, 32768
+        rng = np.random.default_rng(1238)
+        tg_ = rng.integers(0, V, size=N).astype(np.int32)
+        tg_[rng.random(N) < 0.05] = -1
+        for C in (384, 1280):
+            for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16", ag.AG_CE_BF16)):
+                X = dev(N * C, std=1.0 / np.sqrt(C)); W = dev(V * C, std=0.02)
+                dX, dW = dev(N * C), dev(V * C)
+                tg = dev(N, np.int32, ints=tg_)
+                loss, dloss, lse = dev(1), dev(1), dev(N)
+                ctx.fill_f32(dloss, 1.0, 1)
+                desc = ctx.flce_desc(N, C, V, vocab_chunk=4096, precision=prec)
+                sbytes = ctx.flce_scratch_bytes(desc); scr = alloc.alloc((sbytes,), np.uint8); bufs.append(scr)
+                ms_f = time_it(lambda i: ctx.flce_forward(desc, X, W, tg, 0, loss, lse, scr.ptr.address, sbytes), 1)
+                ms_b = time_it(lambda i: ctx.flce_backward(desc, X, W, tg, 0, dloss, lse, dX, dW, scr.ptr.address, sbytes), 1)
+                fl = 2.0 * N * C * V
+                emit("cfg2", f"fused_linear_ce forward N16384 C{C} V32768", ms_f, N, useful_flops=fl, dtype=pname)
+                emit("cfg2", f"fused_linear_ce backward N16384 C{C} V32768", ms_b, N, useful_flops=2 * fl, dtype=pname,
+                     extra={"executed_flops": 3 * fl})
+                emit("cfg2", f"fused_linear_ce fwd+bwd N16384 C{C} V32768", ms_f + ms_b, N, useful_flops=3 * fl, dtype=pname,
+                     extra={"scratch_bytes": sbytes})
+                free_all()
+
+    sections = {"cfg1": sec_cfg1, "gelu": sec_gelu, "cfg3": sec_cfg3, "cfg4": sec_cfg4, "cfg2": sec_cfg2}
+    wanted = [s for s in (a.only.split(",") if a.only else sections) if s]
+    for name in wanted:
+        if name not in sections:
+            raise SystemExit(f"--only: unknown section {name!r}; choose from {sorted(sections)}")
+        sections[name]()
     ctx.check_status()
 
 
