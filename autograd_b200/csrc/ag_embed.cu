@@ -26,6 +26,7 @@ constexpr int GATHER_THREADS = 256;
 __global__ void __launch_bounds__(GATHER_THREADS)
 gather_forward_kernel(const int32_t* __restrict__ ids, const float* __restrict__ table, float* __restrict__ out,
                       int64_t n_ids, int C, int V, int* status) {
+  ag_pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = ((int64_t)blockIdx.x * GATHER_THREADS + threadIdx.x) >> 5;
   const int64_t n_warps = ((int64_t)gridDim.x * GATHER_THREADS) >> 5;
@@ -73,6 +74,8 @@ constexpr int SORT_WARPS = SORT_TILE / 32;
 __global__ void __launch_bounds__(SORT_TILE)
 sort_init_kernel(const int32_t* __restrict__ ids, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals, int64_t n,
                  int V, int* status) {
+  ag_pdl_wait();
+  if (gridDim.x * gridDim.y <= 148) ag_pdl_trigger();  // single-wave grids let the next kernel be scheduled early
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int id = ids[i];
@@ -85,6 +88,8 @@ sort_init_kernel(const int32_t* __restrict__ ids, uint32_t* __restrict__ keys, u
 // Per-tile digit histogram: hist[digit * n_tiles + tile].
 __global__ void __launch_bounds__(SORT_TILE)
 sort_hist_kernel(const uint32_t* __restrict__ keys, uint32_t* __restrict__ hist, int64_t n, int shift, int n_tiles) {
+  ag_pdl_wait();
+  if (gridDim.x * gridDim.y <= 148) ag_pdl_trigger();  // single-wave grids let the next kernel be scheduled early
   __shared__ uint32_t s_cnt[SORT_DIGITS];
   for (int d = threadIdx.x; d < SORT_DIGITS; d += SORT_TILE) s_cnt[d] = 0;
   __syncthreads();
@@ -94,39 +99,55 @@ sort_hist_kernel(const uint32_t* __restrict__ keys, uint32_t* __restrict__ hist,
   for (int d = threadIdx.x; d < SORT_DIGITS; d += SORT_TILE) hist[(int64_t)d * n_tiles + blockIdx.x] = s_cnt[d];
 }
 
-// Exclusive scan of hist (digit-major, SORT_DIGITS*n_tiles entries) by a single CTA.
+// Exclusive scan of hist (digit-major, SORT_DIGITS*n_tiles entries) by a single CTA.  Blocks of
+// 32768 entries: warp w owns entries [1024 w, 1024 w + 1024) of the block, loads them all at once
+// (32 coalesced loads per lane in flight), scans them in registers with a running carry, then the 32
+// warp totals are scanned and every warp writes its segment with its offset.
 __global__ void __launch_bounds__(1024) sort_scan_kernel(uint32_t* __restrict__ hist, int64_t total) {
+  ag_pdl_wait();
+  ag_pdl_trigger();
   __shared__ uint32_t s_warp[32];
   __shared__ uint32_t s_carry;
   if (threadIdx.x == 0) s_carry = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int64_t base = 0; base < total; base += 1024) {
-    const int64_t i = base + threadIdx.x;
-    const uint32_t v = i < total ? hist[i] : 0u;
-    uint32_t inc = v;
+  for (int64_t base = 0; base < total; base += 32768) {
+    const int64_t seg = base + (int64_t)warp * 1024 + lane;
+    uint32_t v[32];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += t;
+    for (int k = 0; k < 32; ++k) {
+      const int64_t i = seg + k * 32;
+      v[k] = i < total ? hist[i] : 0u;
     }
-    if (lane == 31) s_warp[warp] = inc;
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t w = s_warp[lane];
-      uint32_t winc = w;
+    uint32_t run = 0;  // sum of the warp's entries before row k
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const uint32_t x = v[k];
+      uint32_t inc = x;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        uint32_t t = __shfl_up_sync(0xffffffffu, winc, o);
-        if (lane >= o) winc += t;
+        const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
       }
-      s_warp[lane] = winc - w;  // exclusive prefix of warp totals
+      v[k] = run + inc - x;  // exclusive prefix inside the warp's segment
+      run += __shfl_sync(0xffffffffu, inc, 31);
     }
+    if (lane == 0) s_warp[warp] = run;
     __syncthreads();
     const uint32_t carry = s_carry;
-    if (i < total) hist[i] = carry + s_warp[warp] + inc - v;
+    uint32_t before = 0, all = 0;
+    for (int w = 0; w < 32; ++w) {  // 32 shared-memory broadcasts; same values for every thread
+      const uint32_t t = s_warp[w];
+      if (w < warp) before += t;
+      all += t;
+    }
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const int64_t i = seg + k * 32;
+      if (i < total) hist[i] = carry + before + v[k];
+    }
     __syncthreads();
-    if (threadIdx.x == 1023) s_carry = carry + s_warp[31] + inc;
+    if (threadIdx.x == 0) s_carry = carry + all;
     __syncthreads();
   }
 }
@@ -137,6 +158,8 @@ __global__ void __launch_bounds__(SORT_TILE)
 sort_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                     const uint32_t* __restrict__ hist, int64_t n, int shift, int n_tiles) {
+  ag_pdl_wait();
+  if (gridDim.x * gridDim.y <= 148) ag_pdl_trigger();  // single-wave grids let the next kernel be scheduled early
   __shared__ uint16_t s_cnt[SORT_WARPS][SORT_DIGITS];  // 32 KB
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int d = lane; d < SORT_DIGITS; d += 32) s_cnt[warp][d] = 0;
@@ -179,13 +202,19 @@ __device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
 // partials: [n_groups][2][C] floats; slot 0 = the group's first run when it continues from
 // the previous group or is the cut part of a longer segment, slot 1 = its last run when
 // that run started inside this group and continues into the next one.
+// Per-entry run information of a group, computed once per CTA.
+constexpr uint32_t RUN_BEGIN = 1u, RUN_END = 2u, RUN_COMPLETE = 4u, RUN_SLOT1 = 8u, RUN_VALID = 16u;
+constexpr int SEG_BATCH = 8;  // sorted entries whose rows are requested together
+
 template <bool VEC>
 __global__ void __launch_bounds__(SEG_THREADS)
 scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ pos,
                       const float* __restrict__ dout, float* dtable, float* __restrict__ partials, int64_t n, int C,
                       int V) {
+  ag_pdl_wait();
   __shared__ uint32_t s_key[SEG_GROUP + 2];  // [0] = key before the group, [1..G] group, [G+1] = key after
   __shared__ uint32_t s_pos[SEG_GROUP];
+  __shared__ uint32_t s_info[SEG_GROUP];
   const int64_t g0 = (int64_t)blockIdx.x * SEG_GROUP;
   const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
   if (threadIdx.x < SEG_GROUP + 2) {
@@ -195,96 +224,174 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
   }
   if (threadIdx.x < SEG_GROUP) s_pos[threadIdx.x] = threadIdx.x < cnt ? pos[g0 + threadIdx.x] : 0u;
   __syncthreads();
+  if ((int)threadIdx.x < cnt) {
+    // the run (equal keys) around entry j: where it begins and ends inside the group, whether it is cut
+    // by the group boundary on either side
+    const int j = threadIdx.x;
+    const uint32_t key = s_key[j + 1];
+    int rb = j, re = j;
+    while (rb > 0 && s_key[rb] == key) --rb;
+    while (re + 1 < cnt && s_key[re + 2] == key) ++re;
+    const bool from_prev = rb == 0 && s_key[0] == key;
+    const bool into_next = re == cnt - 1 && s_key[cnt + 1] == key;
+    uint32_t info = 0;
+    if (j == rb) info |= RUN_BEGIN;
+    if (j == re) info |= RUN_END;
+    if (!from_prev && !into_next) info |= RUN_COMPLETE;
+    if (!(from_prev || rb == 0)) info |= RUN_SLOT1;
+    if (key < (uint32_t)V) info |= RUN_VALID;
+    s_info[j] = info;
+  }
+  __syncthreads();
 
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
-  // scalar mode: a thread covers columns col, col+128, col+256, col+384
-  int e = 0;
-  while (e < cnt) {
-    const uint32_t key = s_key[e + 1];
-    int end = e + 1;
-    while (end < cnt && s_key[end + 1] == key) ++end;
-    const bool from_prev = (e == 0) && (s_key[0] == key);
-    const bool into_next = (end == cnt) && (s_key[cnt + 1] == key);
-    if (key < (uint32_t)V) {
-      const bool complete = !from_prev && !into_next;
-      float* drow = dtable + (int64_t)key * C;
-      float* prow = partials + ((int64_t)blockIdx.x * 2 + (from_prev || e == 0 ? 0 : 1)) * C;
-      if (VEC) {
-        if (col < C) {
-          float4 acc = complete ? *reinterpret_cast<const float4*>(drow + col) : make_float4(0.f, 0.f, 0.f, 0.f);
-          int j = e;
-          for (; j + 4 <= end; j += 4) {
-            float4 v[4];
+  if (VEC) {
+    if (col >= C) return;
+    // Rows of SEG_BATCH entries, and the dtable rows of the complete runs that begin among them, are
+    // requested together; the adds then run in sorted (= position) order, each complete run starting
+    // from its dtable row: the same sequence of additions as an unbuffered add-at.
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j0 = 0; j0 < cnt; j0 += SEG_BATCH) {
+      float4 v[SEG_BATCH], d[SEG_BATCH];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              v[u] = __ldcs(reinterpret_cast<const float4*>(dout + (int64_t)s_pos[j + u] * C + col));
-#pragma unroll
-            for (int u = 0; u < 4; ++u) acc = f4_add(acc, v[u]);
+      for (int u = 0; u < SEG_BATCH; ++u) {
+        const int j = j0 + u;
+        v[u] = d[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < cnt) {
+          const uint32_t info = s_info[j];
+          if (info & RUN_VALID) {
+            v[u] = __ldcs(reinterpret_cast<const float4*>(dout + (int64_t)s_pos[j] * C + col));
+            if ((info & (RUN_BEGIN | RUN_COMPLETE)) == (RUN_BEGIN | RUN_COMPLETE))
+              d[u] = *reinterpret_cast<const float4*>(dtable + (int64_t)s_key[j + 1] * C + col);
           }
-          for (; j < end; ++j)
-            acc = f4_add(acc, __ldcs(reinterpret_cast<const float4*>(dout + (int64_t)s_pos[j] * C + col)));
-          *reinterpret_cast<float4*>((complete ? drow : prow) + col) = acc;
         }
-      } else {
-        for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
-          float acc = complete ? drow[c] : 0.0f;
-          for (int j = e; j < end; ++j) acc += dout[(int64_t)s_pos[j] * C + c];
-          (complete ? drow : prow)[c] = acc;
+      }
+#pragma unroll
+      for (int u = 0; u < SEG_BATCH; ++u) {
+        const int j = j0 + u;
+        if (j < cnt) {
+          const uint32_t info = s_info[j];
+          if (info & RUN_VALID) {
+            if (info & RUN_BEGIN) acc = d[u];  // zero for a cut run
+            acc = f4_add(acc, v[u]);
+            if (info & RUN_END) {
+              float* dst = (info & RUN_COMPLETE)
+                               ? dtable + (int64_t)s_key[j + 1] * C
+                               : partials + ((int64_t)blockIdx.x * 2 + ((info & RUN_SLOT1) ? 1 : 0)) * C;
+              *reinterpret_cast<float4*>(dst + col) = acc;
+            }
+          }
         }
       }
     }
-    e = end;
+  } else {
+    // scalar mode: a thread covers columns col, col+128, col+256, col+384
+    for (int j = 0; j < cnt; ++j) {
+      const uint32_t info = s_info[j];
+      if (!(info & RUN_VALID) || !(info & RUN_BEGIN)) continue;
+      int end = j;
+      while (!(s_info[end] & RUN_END)) ++end;
+      const bool complete = (info & RUN_COMPLETE) != 0;
+      float* drow = dtable + (int64_t)s_key[j + 1] * C;
+      float* prow = partials + ((int64_t)blockIdx.x * 2 + ((info & RUN_SLOT1) ? 1 : 0)) * C;
+      for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
+        float acc = complete ? drow[c] : 0.0f;
+        for (int e = j; e <= end; ++e) acc += dout[(int64_t)s_pos[e] * C + c];
+        (complete ? drow : prow)[c] = acc;
+      }
+    }
   }
 }
 
-// One CTA per (group, column slice): if the group's LAST run opens a multi-group segment
-// (or the group's only run is the head of one), add the partial slots of that segment in
-// group order onto the dtable row.
-template <bool VEC>
-__global__ void __launch_bounds__(SEG_THREADS)
-scatter_combine_kernel(const uint32_t* __restrict__ keys, float* dtable, const float* __restrict__ partials, int64_t n,
-                       int n_groups, int C, int V) {
-  const int64_t grp = blockIdx.x;
+// One warp per group: if the group's LAST run opens a segment that continues into following groups
+// and starts in this group (the head of the segment), heads[group] = 2 * (last group holding entries
+// of the segment) + (partial slot of the head run); otherwise -1.  Coalesced loads and ballots only:
+// no chain of dependent loads.
+constexpr int SEG_SPLIT = 4;  // sub-ranges of a segment's groups summed side by side in the combine kernel
+
+__global__ void __launch_bounds__(128)
+segment_heads_kernel(const uint32_t* __restrict__ keys, long long* __restrict__ heads, int64_t n, int n_groups, int V) {
+  ag_pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long grp = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (grp >= n_groups) return;  // warp-uniform
   const int64_t g0 = grp * SEG_GROUP;
   const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
   const int64_t last = g0 + cnt - 1;
-  if (last + 1 >= n) return;                 // nothing after this group
-  const uint32_t key = keys[last];
-  if (keys[last + 1] != key) return;         // last run does not continue
-  if (key >= (uint32_t)V) return;            // dropped ids
-  // is this group the head of the segment?  The run containing `last` must start here:
-  // either it starts after the group's first entry, or at entry 0 with a different key before.
-  int64_t start = last;
-  while (start > g0 && keys[start - 1] == key) --start;
-  if (start == g0 && g0 > 0 && keys[g0 - 1] == key) return;  // a continuation, an earlier group is the head
-  const int head_slot = (start == g0) ? 0 : 1;
-
-  // number of following groups whose first run continues this segment (same for every thread;
-  // found by binary search over the sorted keys: the last entry of the segment)
-  int64_t lo_i = last, hi_i = n - 1;
-  while (lo_i < hi_i) {
-    const int64_t mid = (lo_i + hi_i + 1) >> 1;
-    if (keys[mid] == key) lo_i = mid; else hi_i = mid - 1;
+  long long rec = -1;
+  if (last + 1 < n) {  // warp-uniform
+    const uint32_t kj = lane < cnt ? keys[g0 + lane] : 0xffffffffu;
+    const uint32_t k_last = __shfl_sync(0xffffffffu, kj, cnt - 1);
+    const uint32_t k_next = keys[last + 1];
+    const uint32_t k_prev = g0 > 0 ? keys[g0 - 1] : 0xffffffffu;
+    bool go = (k_next == k_last) && (k_last < (uint32_t)V);
+    // sorted keys: the entries equal to the last key are the tail of the group
+    const int start = cnt - __popc(__ballot_sync(0xffffffffu, lane < cnt && kj == k_last));
+    if (start == 0 && k_prev == k_last) go = false;  // a continuation: an earlier group is the head
+    if (go) {
+      // first keys of the following groups, 32 groups per probe; equal ones form a prefix
+      long long g_end = grp;
+      for (long long gb = grp + 1;; gb += 32) {
+        const long long gq = gb + lane;
+        const bool same = gq < n_groups && keys[gq * SEG_GROUP] == k_last;
+        const int m = __popc(__ballot_sync(0xffffffffu, same));
+        g_end = gb + m - 1;
+        if (m < 32) break;
+      }
+      rec = g_end * 2 + (start == 0 ? 0 : 1);
+    }
   }
-  const int64_t g_end = lo_i / SEG_GROUP;  // last group that holds entries of this segment
+  if (lane == 0) heads[grp] = rec;
+}
+
+// One CTA per (group, column slice), block (SEG_THREADS, SEG_SPLIT): for a head group, the partial
+// slots of the segment's following groups are split into SEG_SPLIT consecutive sub-ranges; thread row
+// y adds its sub-range in group order (8 loads in flight), then row 0 adds
+// dtable row + head partial + sub-sum 0 + ... + sub-sum 3 and writes the dtable row.  Fixed order.
+template <bool VEC>
+__global__ void __launch_bounds__(SEG_THREADS * SEG_SPLIT)
+scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __restrict__ heads, float* dtable,
+                       const float* __restrict__ partials, int64_t n, int C) {
+  ag_pdl_wait();
+  const int64_t grp = blockIdx.x;
+  const long long rec = heads[grp];
+  if (rec < 0) return;  // uniform
+  const int64_t g_end = rec >> 1;
+  const int head_slot = (int)(rec & 1);
+  const int64_t g0 = grp * SEG_GROUP;
+  const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
+  const uint32_t key = keys[g0 + cnt - 1];
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
   float* drow = dtable + (int64_t)key * C;
   if (VEC) {
-    if (col >= C) return;
-    float4 acc = *reinterpret_cast<const float4*>(drow + col);
-    acc = f4_add(acc, *reinterpret_cast<const float4*>(partials + (grp * 2 + head_slot) * C + col));
-    int64_t g = grp + 1;
-    // loads of 8 partial rows are independent and in flight together; the adds stay in group order
-    for (; g + 8 <= g_end + 1; g += 8) {
-      float4 v[8];
+    __shared__ float4 s_sub[SEG_SPLIT][SEG_THREADS];
+    const int y = threadIdx.y;
+    const int64_t chunk = (g_end - grp + SEG_SPLIT - 1) / SEG_SPLIT;
+    float4 sub = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < C) {
+      int64_t g = grp + 1 + y * chunk;
+      int64_t ge = g + chunk;
+      if (ge > g_end + 1) ge = g_end + 1;
+      for (; g + 8 <= ge; g += 8) {
+        float4 v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(partials + ((g + u) * 2 + 0) * C + col));
+        for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(partials + ((g + u) * 2 + 0) * C + col));
 #pragma unroll
-      for (int u = 0; u < 8; ++u) acc = f4_add(acc, v[u]);
+        for (int u = 0; u < 8; ++u) sub = f4_add(sub, v[u]);
+      }
+      for (; g < ge; ++g) sub = f4_add(sub, *reinterpret_cast<const float4*>(partials + (g * 2 + 0) * C + col));
     }
-    for (; g <= g_end; ++g) acc = f4_add(acc, *reinterpret_cast<const float4*>(partials + (g * 2 + 0) * C + col));
-    *reinterpret_cast<float4*>(drow + col) = acc;
+    s_sub[y][threadIdx.x] = sub;
+    __syncthreads();
+    if (y == 0 && col < C) {
+      float4 acc = *reinterpret_cast<const float4*>(drow + col);
+      acc = f4_add(acc, *reinterpret_cast<const float4*>(partials + (grp * 2 + head_slot) * C + col));
+#pragma unroll
+      for (int q = 0; q < SEG_SPLIT; ++q) acc = f4_add(acc, s_sub[q][threadIdx.x]);
+      *reinterpret_cast<float4*>(drow + col) = acc;
+    }
   } else {
+    if (threadIdx.y != 0) return;
     for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
       float acc = drow[c] + partials[(grp * 2 + head_slot) * C + c];
       for (int64_t g = grp + 1; g <= g_end; ++g) acc += partials[(g * 2 + 0) * C + c];
@@ -309,7 +416,11 @@ inline ScatterPlan scatter_plan(int64_t n, int C) {
     p.off_keys[b] = off; off += align256((size_t)n * 4);
     p.off_vals[b] = off; off += align256((size_t)n * 4);
   }
-  p.off_hist = off; off += align256((size_t)SORT_DIGITS * p.n_tiles * 4);
+  p.off_hist = off;  // also the per-group head records of the combine step (8 bytes per group)
+  {
+    const size_t hist_bytes = (size_t)SORT_DIGITS * p.n_tiles * 4, head_bytes = (size_t)p.n_groups * 8;
+    off += align256(hist_bytes > head_bytes ? hist_bytes : head_bytes);
+  }
   p.off_partials = off; off += align256((size_t)p.n_groups * 2 * C * 4);
   p.total = off;
   return p;
@@ -364,39 +475,43 @@ extern "C" int ag_gather_backward(ag_ctx* ctx, const int32_t* ids, const float* 
   uint32_t* vals[2] = {reinterpret_cast<uint32_t*>(base + p.off_vals[0]), reinterpret_cast<uint32_t*>(base + p.off_vals[1])};
   uint32_t* hist = reinterpret_cast<uint32_t*>(base + p.off_hist);
   float* partials = reinterpret_cast<float*>(base + p.off_partials);
+  // the histogram area is free once the keys are sorted: it holds the per-group head records
+  // (8 bytes per group of 32 ids, the histogram has 2 KB per 1024 ids)
+  long long* heads = reinterpret_cast<long long*>(base + p.off_hist);
   const int n_tiles = (int)p.n_tiles;
 
-  sort_init_kernel<<<n_tiles, SORT_TILE, 0, ctx->stream>>>(ids, keys[0], vals[0], n_ids, V, ctx->d_status);
-  AG_LAUNCHED(ctx, "sort_init_kernel");
+  AG_LAUNCH_PDL(ctx, "sort_init_kernel", sort_init_kernel, n_tiles, SORT_TILE, 0, ids, keys[0], vals[0], n_ids, V,
+                ctx->d_status);
   // keys are in [0, V]: sort just enough 9-bit digits to cover V
   int bits = 1;
   while (((int64_t)1 << bits) <= (int64_t)V) ++bits;
   int cur = 0;
   for (int shift = 0; shift < bits; shift += SORT_BITS) {
-    sort_hist_kernel<<<n_tiles, SORT_TILE, 0, ctx->stream>>>(keys[cur], hist, n_ids, shift, n_tiles);
-    AG_LAUNCHED(ctx, "sort_hist_kernel");
-    sort_scan_kernel<<<1, 1024, 0, ctx->stream>>>(hist, (int64_t)SORT_DIGITS * n_tiles);
-    AG_LAUNCHED(ctx, "sort_scan_kernel");
-    sort_scatter_kernel<<<n_tiles, SORT_TILE, 0, ctx->stream>>>(keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], hist,
-                                                                 n_ids, shift, n_tiles);
-    AG_LAUNCHED(ctx, "sort_scatter_kernel");
+    AG_LAUNCH_PDL(ctx, "sort_hist_kernel", sort_hist_kernel, n_tiles, SORT_TILE, 0, (const uint32_t*)keys[cur], hist, n_ids,
+                  shift, n_tiles);
+    AG_LAUNCH_PDL(ctx, "sort_scan_kernel", sort_scan_kernel, 1, 1024, 0, hist, (int64_t)SORT_DIGITS * n_tiles);
+    AG_LAUNCH_PDL(ctx, "sort_scatter_kernel", sort_scatter_kernel, n_tiles, SORT_TILE, 0, (const uint32_t*)keys[cur],
+                  (const uint32_t*)vals[cur], keys[cur ^ 1], vals[cur ^ 1], (const uint32_t*)hist, n_ids, shift, n_tiles);
     cur ^= 1;
   }
   const bool vec = (C % 4 == 0) && ag_aligned16(dout) && ag_aligned16(dtable);
   dim3 grid((unsigned)p.n_groups, (unsigned)((C + SEG_COLS - 1) / SEG_COLS));
   if (vec) {
-    scatter_groups_kernel<true><<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials,
-                                                                        n_ids, C, V);
-    AG_LAUNCHED(ctx, "scatter_groups_kernel");
-    scatter_combine_kernel<true><<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], dtable, partials, n_ids,
-                                                                         (int)p.n_groups, C, V);
-    AG_LAUNCHED(ctx, "scatter_combine_kernel");
+    AG_LAUNCH_PDL(ctx, "scatter_groups_kernel", scatter_groups_kernel<true>, grid, SEG_THREADS, 0,
+                  (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], dout, dtable, partials, n_ids, C, V);
+    AG_LAUNCH_PDL(ctx, "segment_heads_kernel", segment_heads_kernel, (unsigned)((p.n_groups + 3) / 4), 128, 0,
+                  (const uint32_t*)keys[cur], heads, n_ids, (int)p.n_groups, V);
+    AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", scatter_combine_kernel<true>, grid, dim3(SEG_THREADS, SEG_SPLIT), 0,
+                  (const uint32_t*)keys[cur], (const long long*)heads, dtable, (const float*)partials, n_ids, C);
   } else {
     scatter_groups_kernel<false><<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials,
                                                                          n_ids, C, V);
     AG_LAUNCHED(ctx, "scatter_groups_kernel");
-    scatter_combine_kernel<false><<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], dtable, partials, n_ids,
-                                                                          (int)p.n_groups, C, V);
+    segment_heads_kernel<<<(unsigned)((p.n_groups + 3) / 4), 128, 0, ctx->stream>>>(keys[cur], heads, n_ids,
+                                                                                     (int)p.n_groups, V);
+    AG_LAUNCHED(ctx, "segment_heads_kernel");
+    scatter_combine_kernel<false><<<grid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, dtable,
+                                                                                           partials, n_ids, C);
     AG_LAUNCHED(ctx, "scatter_combine_kernel");
   }
   return AG_OK;
