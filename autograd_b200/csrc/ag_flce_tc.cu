@@ -106,41 +106,74 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                : "memory");
 }
 
-template <bool TF32>
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
+// One MMA from the two halves of each shared-memory descriptor (low word: address and leading byte
+// offset, high word: stride byte offset, version, layout).  ACC = 2: accumulate flag from a register
+// (the first MMA of a stage), ACC = 1: always accumulate (no predicate set-up instruction).
+template <bool TF32, int ACC>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                       uint32_t idesc, uint32_t accumulate) {
   if (TF32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if (ACC == 2) {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+          "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+          : "memory");
+    } else {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+          "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+          : "memory");
+    }
   } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if (ACC == 2) {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+          "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+          : "memory");
+    } else {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+          "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+          : "memory");
+    }
   }
 }
 
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups of
-// 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// MN-major operand: the tile is stored as [MN group][k row][128 bytes of MN]; consecutive MN groups are
-// `group_bytes` apart (leading byte offset).  16-bit operands use the plain 128-byte swizzle, whose
-// atom is 8 k rows (1024 bytes, the stride byte offset).  32-bit operands can only be transposed by
-// the tensor core from the 128-byte swizzle with 32-byte atomicity (layout type 1): its atom is 4 k
-// rows (512 bytes), and the matching TMA mode swizzles 32-byte chunks by the row index modulo 4.
+// Shared-memory matrix descriptors (version 1, Blackwell), as two 32-bit words.
+//   low word : bits 0-13 start address >> 4, bits 16-29 leading byte offset >> 4
+//   high word: bits 0-13 stride byte offset >> 4, bit 14 version, bits 29-31 layout type
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart (stride byte
+// offset 64), leading byte offset unused (1), layout 2; one MMA consumes 32 bytes of K inside the row,
+// so consecutive MMAs advance the start address by 2 units.
+// MN-major operand: the tile is stored as [MN group][k row][128 bytes of MN]; consecutive MN groups
+// are BK * 128 bytes apart (leading byte offset).  16-bit operands use the plain 128-byte swizzle,
+// whose atom is 8 k rows (stride byte offset 64, layout 2).  32-bit operands can only be transposed
+// by the tensor core from the 128-byte swizzle with 32-byte atomicity (layout 1): its atom is 4 k rows
+// (stride byte offset 32), and the matching TMA mode swizzles 32-byte chunks by the row index modulo
+// 4.  One MMA consumes umma_k k-rows of 128 bytes: 64 (tf32) or 128 (bf16) address units.
 template <bool TF32>
-__device__ __forceinline__ uint64_t tc_smem_desc_mn(uint32_t smem_addr, uint32_t group_bytes) {
-  constexpr uint64_t sbo = TF32 ? 32ull : 64ull, layout = TF32 ? 1ull : 2ull;
-  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((group_bytes >> 4) & 0x3FFFu) << 16) | (sbo << 32) |
-         (1ull << 46) | (layout << 61);
-}
+struct TcDesc {
+  uint32_t lo_const, hi, step;
+  __device__ __forceinline__ void init(int mn_major, uint32_t group_bytes) {
+    if (mn_major) {
+      lo_const = ((group_bytes >> 4) & 0x3FFFu) << 16;
+      hi = TF32 ? (32u | (1u << 14) | (1u << 29)) : (64u | (1u << 14) | (2u << 29));
+      step = TF32 ? 64u : 128u;
+    } else {
+      lo_const = 1u << 16;
+      hi = 64u | (1u << 14) | (2u << 29);
+      step = 2u;
+    }
+  }
+};
 
 __device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -290,7 +323,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       uint32_t stage = 0, phase = 0;
       uint32_t acc_par[2] = {0, 0};
       int local = 0;
-      const int k_sub = p.BK / p.umma_k;  // MMAs per stage along K (4)
+      // Everything an MMA needs beyond two additions is prepared outside the k loop: this one thread
+      // issues 12 (3xTF32) or 4 (bf16) MMAs per stage and its instruction stream is on the critical path.
+      TcDesc<TF32> dA, dB;
+      dA.init(p.a_mn, (uint32_t)p.BK * 128u);
+      dB.init(p.b_mn, (uint32_t)p.BK * 128u);
+      const uint32_t a_lo_off = p.a_bytes >> 4, b_lo_off = p.b_bytes >> 4;
+      const uint32_t b_off = (TF32 ? 2u * p.a_bytes : p.a_bytes) >> 4;
+      const uint32_t stage_units = stage_bytes >> 4;
+      const uint32_t tiles_u = ag_smem_u32(tiles) >> 4;
       for (int tile = blockIdx.x; tile < total_tiles && !expired; tile += gridDim.x, ++local) {
         const int buf = local & 1;
         if (!tc_wait(&acc_empty[buf], acc_par[buf] ^ 1u, abort_flag)) {
@@ -308,24 +349,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             break;
           }
           tc_fence_after();
-          const uint32_t s = ag_smem_u32(tiles + (size_t)stage * stage_bytes);
-          const uint32_t a_hi = s, a_lo = s + p.a_bytes;
-          const uint32_t b_hi = p.split ? s + 2 * p.a_bytes : s + p.a_bytes;
-          const uint32_t b_lo = b_hi + p.b_bytes;
-          const uint32_t gbytes = (uint32_t)p.BK * 128u;
-          for (int kk = 0; kk < k_sub; ++kk) {
-            // K-major: 32 bytes of K per MMA inside the 128-byte row.  MN-major: umma_k k-rows of
-            // 128 bytes per MMA.
-            const uint32_t first = (k == k_begin && kk == 0) ? 0u : 1u;
-            const uint32_t offk = (uint32_t)kk * 32u, offm = (uint32_t)kk * (uint32_t)p.umma_k * 128u;
-            auto da = [&](uint32_t base) { return p.a_mn ? tc_smem_desc_mn<TF32>(base + offm, gbytes) : tc_smem_desc(base + offk); };
-            auto db = [&](uint32_t base) { return p.b_mn ? tc_smem_desc_mn<TF32>(base + offm, gbytes) : tc_smem_desc(base + offk); };
-            if (p.split) {
-              tc_mma<TF32>(tacc, da(a_hi), db(b_lo), p.idesc, first);
-              tc_mma<TF32>(tacc, da(a_lo), db(b_hi), p.idesc, 1u);
-              tc_mma<TF32>(tacc, da(a_hi), db(b_hi), p.idesc, 1u);
+          const uint32_t su = tiles_u + stage * stage_units;
+          const uint32_t ah = su + dA.lo_const, al = ah + a_lo_off;   // A hi / lo tiles
+          const uint32_t bh = su + b_off + dB.lo_const, bl = bh + b_lo_off;
+          const uint32_t not_first = (k != k_begin) ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {  // BK / umma_k = 4 MMAs along K per stage in both modes
+            const uint32_t ao = (uint32_t)kk * dA.step, bo = (uint32_t)kk * dB.step;
+            if (TF32) {
+              if (kk == 0)
+                tc_mma<TF32, 2>(tacc, ah + ao, dA.hi, bl + bo, dB.hi, p.idesc, not_first);
+              else
+                tc_mma<TF32, 1>(tacc, ah + ao, dA.hi, bl + bo, dB.hi, p.idesc, 1u);
+              tc_mma<TF32, 1>(tacc, al + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
+              tc_mma<TF32, 1>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
             } else {
-              tc_mma<TF32>(tacc, da(a_hi), db(b_hi), p.idesc, first);
+              if (kk == 0)
+                tc_mma<TF32, 2>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, not_first);
+              else
+                tc_mma<TF32, 1>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
             }
           }
           tc_commit(&empty[stage]);  // stage reusable once these MMAs have read it

@@ -448,7 +448,8 @@ def test_flce_golden(golden, case, precision):
     G.check_clean_status()
 
 
-@pytest.mark.parametrize("N,C,V,precision", [(2048, 384, 8192, 0), (2048, 384, 8192, 1), (1024, 1280, 8192, 1)])
+@pytest.mark.parametrize("N,C,V,precision", [(2048, 384, 8192, 0), (2048, 384, 8192, 1), (1024, 1280, 8192, 1),
+                                             (1000, 388, 4104, 1)])  # ragged: rows, width and last panel (8 columns)
 def test_flce_mid_size_vs_oracle(N, C, V, precision):
     """Config 2 shapes at a reduced token / vocab count, vocab chunk 4096 (two panels)."""
     ctx, alloc, be = G.env()
@@ -494,7 +495,7 @@ def test_flce_config2_full_size(C):
     G.check_clean_status()
 
 
-@pytest.mark.parametrize("N,C,V", [(2048, 384, 8192), (1000, 1280, 4104)])
+@pytest.mark.parametrize("N,C,V", [(2048, 384, 8192), (1000, 1280, 4104), (1000, 392, 4104)])
 def test_flce_bf16_mode_vs_oracle(N, C, V):
     """The stated bf16 tensor-core mode of the CE GEMMs: 2e-2 against the fp32 oracle run on the
     same bf16-rounded operands (the rounding of X and W is the mode's definition; an element of
