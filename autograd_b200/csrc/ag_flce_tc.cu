@@ -26,6 +26,7 @@
 // Every mbarrier wait is bounded; on expiry the CTA raises AG_STATUS_WAIT_EXPIRED, all roles
 // leave their loops, TMEM is released and the kernel returns.  Every CTA loads its own tiles; no thread-block clusters.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "ag_flce.cuh"
 
@@ -109,42 +110,72 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 // One MMA from the two halves of each shared-memory descriptor (low word: address and leading byte
 // offset, high word: stride byte offset, version, layout).  ACC = 2: accumulate flag from a register
 // (the first MMA of a stage), ACC = 1: always accumulate (no predicate set-up instruction).
-template <bool TF32, int ACC>
+// PAIR: the instruction spans a pair of CTAs (cta_group::2, M = 256): issued by the leader CTA only,
+// it reads A rows and B columns from the shared memory of both CTAs at the same offsets and writes
+// 128 accumulator rows into the tensor memory of each.
+#define TC_MMA_ASM(GROUP, KIND, SETP)                                                              \
+  "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t" SETP "\n\t"                                     \
+  "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"                                           \
+  "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t}"
+template <bool TF32, int ACC, bool PAIR>
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                        uint32_t idesc, uint32_t accumulate) {
+#define TC_MMA_CASE(GROUP, KIND)                                                                                 \
+  if (ACC == 2)                                                                                                  \
+    asm volatile(TC_MMA_ASM(GROUP, KIND, "setp.ne.b32 p, %6, 0;")::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), \
+                 "r"(b_hi), "r"(idesc), "r"(accumulate)                                                          \
+                 : "memory");                                                                                    \
+  else                                                                                                           \
+    asm volatile(TC_MMA_ASM(GROUP, KIND, "setp.eq.b32 p, 0, 0;")::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo),  \
+                 "r"(b_hi), "r"(idesc)                                                                           \
+                 : "memory");
   if (TF32) {
-    if (ACC == 2) {
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-          "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
-          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-          : "memory");
-    } else {
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.eq.b32 p, 0, 0;\n\t"
-          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-          "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
-          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
-          : "memory");
-    }
+    if (PAIR) { TC_MMA_CASE("2", "tf32") } else { TC_MMA_CASE("1", "tf32") }
   } else {
-    if (ACC == 2) {
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-          "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
-          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-          : "memory");
-    } else {
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.eq.b32 p, 0, 0;\n\t"
-          "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-          "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
-          "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
-          : "memory");
-    }
+    if (PAIR) { TC_MMA_CASE("2", "f16") } else { TC_MMA_CASE("1", "f16") }
   }
+#undef TC_MMA_CASE
+}
+
+// ---- CTA pair (thread-block cluster of 2) helpers
+__device__ __forceinline__ uint32_t tc_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t tc_map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void tc_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// commit whose mbarrier may live in either CTA of the pair
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tile loads of a CTA of the pair: destination in the own shared memory, completion bytes counted on
+// the mbarrier at `mbar_cluster_addr`, which is the leader's
+__device__ __forceinline__ void tc_tma_load_2d_pair(const CUtensorMap* tm, void* smem_dst, uint32_t mbar_cluster_addr,
+                                                    int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+          "r"(ag_smem_u32(smem_dst)),
+      "l"(tm), "r"(mbar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_tma_load_3d_pair(const CUtensorMap* tm, void* smem_dst, uint32_t mbar_cluster_addr,
+                                                    int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], "
+      "[%2];" ::"r"(ag_smem_u32(smem_dst)),
+      "l"(tm), "r"(mbar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
 }
 
 // Shared-memory matrix descriptors (version 1, Blackwell), as two 32-bit words.
@@ -226,7 +257,12 @@ __device__ __forceinline__ float tc_tf32_rna(float x) {
   return __uint_as_float(r);
 }
 
-template <bool TF32, int EPI>
+// PAIR: launched as clusters of two CTAs that share every 256-row output tile (see tc_mma): CTA `rank`
+// owns rows [128 rank, 128 rank + 128) of the tile and loads its own A rows and half of the B columns,
+// so a pair pulls a third less operand data through shared memory than two single CTAs.  All stage
+// barriers that the MMA waits on live in the leader (rank 0); the leader's commits arrive on the
+// barriers of both CTAs.
+template <bool TF32, int EPI, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant__ CUtensorMap tmA_lo,
                const __grid_constant__ CUtensorMap tmB_hi, const __grid_constant__ CUtensorMap tmB_lo,
@@ -245,6 +281,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? tc_cluster_rank() : 0u;
+  // this CTA's (pair's) position in the stream of output tiles, and the stream's stride
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int unit_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int row_off = PAIR ? (int)rank * TC_BM : 0;        // first row of this CTA inside the tile
+  const int bm_tile = PAIR ? 2 * TC_BM : TC_BM;            // rows of an output tile
+  const int bn_cta = PAIR ? p.BN / 2 : p.BN;               // B columns this CTA loads
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -253,18 +296,28 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       ag_mbar_init(&acc_full[b], 1);
-      ag_mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+      ag_mbar_init(&acc_empty[b], PAIR ? 16 : 8);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
-    ag_fence_mbar_init();
+    if (PAIR)
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    else
+      ag_fence_mbar_init();
   }
-  __syncthreads();
+  if (PAIR) tc_cluster_sync(); else __syncthreads();  // the peer's barriers exist before anything arrives on them
   if (warp == 1) {
     // 512 columns: two accumulators of up to 256 fp32 columns each (this kernel owns the SM)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ag_smem_u32(tmem_slot)),
-                 "r"(512u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ag_smem_u32(tmem_slot)),
+                   "r"(512u)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ag_smem_u32(tmem_slot)),
+                   "r"(512u)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -277,23 +330,40 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !expired; tile += gridDim.x) {
+      for (int tile = unit; tile < total_tiles && !expired; tile += unit_stride) {
         int tm, tn, k_begin, k_end, split_id;
         tc_tile_coords(p, tile, tm, tn, k_begin, k_end, split_id);
-        const int m0 = tm * TC_BM, n0 = tn * p.BN;
+        const int m0 = tm * bm_tile + row_off, n0 = tn * p.BN + (PAIR ? (int)rank * bn_cta : 0);
         for (int k = k_begin; k < k_end; ++k) {
           if (!tc_wait(&empty[stage], phase ^ 1u, abort_flag)) {
             expired = true;
             break;
           }
           unsigned char* s = tiles + (size_t)stage * stage_bytes;
-          ag_mbar_expect_tx(&full[stage], stage_bytes);
+          // pair: the leader's barrier counts the bytes of both CTAs' loads; a completion that arrives
+          // before the leader has posted its expectation only makes the pending count negative for a while
+          uint32_t full_addr = ag_smem_u32(&full[stage]);
+          if (PAIR) {
+            if (rank == 0) ag_mbar_expect_tx(&full[stage], 2u * stage_bytes);
+            full_addr = tc_map_to_cta(full_addr, 0u);
+          } else {
+            ag_mbar_expect_tx(&full[stage], stage_bytes);
+          }
           const int kx = k * p.BK;
           // K-major operand: one box {BK, rows}.  MN-major operand: one box {128 bytes of MN, BK rows} per
           // MN group, stored group after group.
           const uint32_t gbytes = (uint32_t)p.BK * 128u;
           auto load_operand = [&](const CUtensorMap* tm, unsigned char* dst, int mn0, int mn_rows, int mn_major, int is3d) {
-            if (!mn_major) {
+            if (PAIR) {
+              if (!mn_major) {
+                tc_tma_load_2d_pair(tm, dst, full_addr, kx, mn0);
+              } else if (is3d) {
+                tc_tma_load_3d_pair(tm, dst, full_addr, 0, kx, mn0 / p.mn_group);
+              } else {
+                for (int g = 0; g * p.mn_group < mn_rows; ++g)
+                  tc_tma_load_2d_pair(tm, dst + (size_t)g * gbytes, full_addr, mn0 + g * p.mn_group, kx);
+              }
+            } else if (!mn_major) {
               tc_tma_load_2d(tm, dst, &full[stage], kx, mn0);
             } else if (is3d) {
               tc_tma_load_3d(tm, dst, &full[stage], 0, kx, mn0 / p.mn_group);
@@ -305,10 +375,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           load_operand(&tmA_hi, s, m0, TC_BM, p.a_mn, p.a_3d);
           if (p.split) {
             load_operand(&tmA_lo, s + p.a_bytes, m0, TC_BM, p.a_mn, p.a_3d);
-            load_operand(&tmB_hi, s + 2 * p.a_bytes, n0, p.BN, p.b_mn, p.b_3d);
-            load_operand(&tmB_lo, s + 2 * p.a_bytes + p.b_bytes, n0, p.BN, p.b_mn, p.b_3d);
+            load_operand(&tmB_hi, s + 2 * p.a_bytes, n0, bn_cta, p.b_mn, p.b_3d);
+            load_operand(&tmB_lo, s + 2 * p.a_bytes + p.b_bytes, n0, bn_cta, p.b_mn, p.b_3d);
           } else {
-            load_operand(&tmB_hi, s + p.a_bytes, n0, p.BN, p.b_mn, p.b_3d);
+            load_operand(&tmB_hi, s + p.a_bytes, n0, bn_cta, p.b_mn, p.b_3d);
           }
           if (++stage == (uint32_t)p.stages) {
             stage = 0;
@@ -318,8 +388,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (pair: the leader only)
+    if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0;
       uint32_t acc_par[2] = {0, 0};
       int local = 0;
@@ -332,7 +402,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       const uint32_t b_off = (TF32 ? 2u * p.a_bytes : p.a_bytes) >> 4;
       const uint32_t stage_units = stage_bytes >> 4;
       const uint32_t tiles_u = ag_smem_u32(tiles) >> 4;
-      for (int tile = blockIdx.x; tile < total_tiles && !expired; tile += gridDim.x, ++local) {
+      for (int tile = unit; tile < total_tiles && !expired; tile += unit_stride, ++local) {
         const int buf = local & 1;
         if (!tc_wait(&acc_empty[buf], acc_par[buf] ^ 1u, abort_flag)) {
           expired = true;
@@ -358,26 +428,40 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             const uint32_t ao = (uint32_t)kk * dA.step, bo = (uint32_t)kk * dB.step;
             if (TF32) {
               if (kk == 0)
-                tc_mma<TF32, 2>(tacc, ah + ao, dA.hi, bl + bo, dB.hi, p.idesc, not_first);
+                tc_mma<TF32, 2, PAIR>(tacc, ah + ao, dA.hi, bl + bo, dB.hi, p.idesc, not_first);
               else
-                tc_mma<TF32, 1>(tacc, ah + ao, dA.hi, bl + bo, dB.hi, p.idesc, 1u);
-              tc_mma<TF32, 1>(tacc, al + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
-              tc_mma<TF32, 1>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
+                tc_mma<TF32, 1, PAIR>(tacc, ah + ao, dA.hi, bl + bo, dB.hi, p.idesc, 1u);
+              tc_mma<TF32, 1, PAIR>(tacc, al + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
+              tc_mma<TF32, 1, PAIR>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
             } else {
               if (kk == 0)
-                tc_mma<TF32, 2>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, not_first);
+                tc_mma<TF32, 2, PAIR>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, not_first);
               else
-                tc_mma<TF32, 1>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
+                tc_mma<TF32, 1, PAIR>(tacc, ah + ao, dA.hi, bh + bo, dB.hi, p.idesc, 1u);
             }
           }
-          tc_commit(&empty[stage]);  // stage reusable once these MMAs have read it
+          // stage reusable once these MMAs have read it (pair: in both CTAs)
+          if (PAIR) {
+            const uint32_t e = ag_smem_u32(&empty[stage]);
+            tc_commit_pair(tc_map_to_cta(e, 0u));
+            tc_commit_pair(tc_map_to_cta(e, 1u));
+          } else {
+            tc_commit(&empty[stage]);
+          }
           if (++stage == (uint32_t)p.stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (expired) break;
-        tc_commit(&acc_full[buf]);  // accumulator complete
+        // accumulator complete (pair: each CTA's epilogue waits on its own barrier)
+        if (PAIR) {
+          const uint32_t f = ag_smem_u32(&acc_full[buf]);
+          tc_commit_pair(tc_map_to_cta(f, 0u));
+          tc_commit_pair(tc_map_to_cta(f, 1u));
+        } else {
+          tc_commit(&acc_full[buf]);
+        }
       }
     }
   } else {
@@ -392,11 +476,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     const bool vec_ok = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) &&
                         (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) &&
                         (!p.resid || (((p.ld_resid & 3) == 0) && (reinterpret_cast<uintptr_t>(p.resid) & 15u) == 0));
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+    for (int tile = unit; tile < total_tiles; tile += unit_stride, ++local) {
       const int buf = local & 1;
       int tm, tn, k_begin, k_end, split_id;
       tc_tile_coords(p, tile, tm, tn, k_begin, k_end, split_id);
-      const int m0 = tm * TC_BM, n0 = tn * p.BN;
+      const int m0 = tm * bm_tile + row_off, n0 = tn * p.BN;
       if (!tc_wait(&acc_full[buf], full_par[buf], abort_flag)) {
         expired = true;
         break;
@@ -567,15 +651,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) ag_mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) {
+        if (PAIR)
+          tc_mbar_arrive_cluster(tc_map_to_cta(ag_smem_u32(&acc_empty[buf]), 0u));  // the leader's MMA thread waits
+        else
+          ag_mbar_arrive(&acc_empty[buf]);
+      }
     }
   }
   if (expired && lane == 0) atomicOr(p.status, AG_STATUS_WAIT_EXPIRED);
   tc_fence_before();
-  __syncthreads();
+  // pair: neither CTA may leave, or free its tensor memory, while the other can still read its shared
+  // memory or arrive on its barriers
+  if (PAIR) tc_cluster_sync(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
@@ -664,24 +758,77 @@ splitk_reduce_kernel(const float* __restrict__ P, int splits, int M, int N, floa
   }
 }
 
+// Largest number of CTA pairs (clusters of 2) of this kernel that are resident at once; 0 on error.
 template <bool TF32, int EPI>
+int tc_max_pairs(ag_ctx* ctx, size_t smem) {
+  static int cached = -1;
+  static size_t cached_smem = 0;
+  if (cached >= 0 && cached_smem == smem) return cached;
+  auto kern = tc_gemm_kernel<TF32, EPI, true>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * ctx->sm_count);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  cached = n;
+  cached_smem = smem;
+  return n;
+}
+
+template <bool TF32, int EPI, bool PAIR>
 int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const CUtensorMap& a_lo,
               const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
   static bool attr_done = false;
+  auto kern = tc_gemm_kernel<TF32, EPI, PAIR>;
   if (!attr_done) {
-    AG_CUDA(ctx, cudaFuncSetAttribute(tc_gemm_kernel<TF32, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      TC_SMEM_LIMIT));
+    AG_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT));
     attr_done = true;
   }
   int rc_ev;
   if (ctx->tc_timing && (rc_ev = ag_event_record(ctx, ctx->tc_timing_base + 2 * ctx->tc_timing_count))) return rc_ev;
-  tc_gemm_kernel<TF32, EPI><<<grid, TC_THREADS, smem, ctx->stream>>>(a_hi, a_lo, b_hi, b_lo, p);
-  AG_LAUNCHED(ctx, "tc_gemm_kernel");
+  if (PAIR) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    AG_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, a_hi, a_lo, b_hi, b_lo, p));
+    ctx->launches++;
+  } else {
+    kern<<<grid, TC_THREADS, smem, ctx->stream>>>(a_hi, a_lo, b_hi, b_lo, p);
+    AG_LAUNCHED(ctx, "tc_gemm_kernel");
+  }
   if (ctx->tc_timing) {
     if ((rc_ev = ag_event_record(ctx, ctx->tc_timing_base + 2 * ctx->tc_timing_count + 1))) return rc_ev;
     ctx->tc_timing_count++;
   }
   return AG_OK;
+}
+
+template <bool TF32, int EPI>
+int tc_launch_any(ag_ctx* ctx, bool pair, int grid, size_t smem, const CUtensorMap& a_hi, const CUtensorMap& a_lo,
+                  const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
+  return pair ? tc_launch<TF32, EPI, true>(ctx, grid, smem, a_hi, a_lo, b_hi, b_lo, p)
+              : tc_launch<TF32, EPI, false>(ctx, grid, smem, a_hi, a_lo, b_hi, b_lo, p);
 }
 
 // `epi` (may be null = EPI_STORE) carries the fields of the fused cross-entropy epilogues.
@@ -694,44 +841,64 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   p.BK = bf16 ? 64 : 32;
   p.umma_k = bf16 ? 16 : 8;
   p.split = bf16 ? 0 : 1;
-  // Tile width and split-K factor.  Measured behaviour of this kernel: a k-step costs time in
-  // proportion to the operand bytes it pulls through shared memory (128 + BN rows), a tile costs
-  // about 8 k-steps of prologue / epilogue on top, and CTAs work in rounds over the SMs.  Split-K
-  // is only considered for plain accumulate outputs with a workspace and few tiles.
+  // Tile width, split-K factor and CTA pairing.  Measured behaviour of this kernel: a k-step costs
+  // time in proportion to the operand bytes a CTA pulls through shared memory (128 A rows + the B rows
+  // it loads: BN, or BN/2 as one CTA of a pair), a tile costs about 8 k-steps of prologue / epilogue on
+  // top, and CTAs (pairs) work in rounds over the SMs (SM pairs).  Split-K is only considered for
+  // plain accumulate outputs with a workspace and few tiles.
   const int cand[] = {256, 192, 160, 128};
-  int best_bn = 128, best_s = 1;
+  int best_bn = 128, best_s = 1, best_pair = 0;
   double best_cost = 1e300;
-  const int tiles_m = (M + TC_BM - 1) / TC_BM;
   const int k_iters_all = (K + p.BK - 1) / p.BK;
   p.a_mn = A.mn_major ? 1 : 0;
   p.b_mn = B.mn_major ? 1 : 0;
   p.mn_group = bf16 ? 64 : 32;
-  for (int bn : cand) {
-    if (p.b_mn && bn % p.mn_group != 0) continue;
-    const int tn = (N + bn - 1) / bn;
-    const int64_t tiles = (int64_t)tiles_m * tn;
-    int s_max = 1;
-    if (epi_kind == EPI_STORE && splitk_ws && tiles < 2 * (int64_t)ctx->sm_count) {
-      s_max = k_iters_all / 16;
-      if (s_max > 16) s_max = 16;
-      const int64_t fit = (int64_t)(splitk_ws_bytes / ((size_t)M * N * sizeof(float)));
-      if (s_max > fit) s_max = (int)fit;
-      if (s_max < 1) s_max = 1;
-    }
-    for (int sp = 1; sp <= s_max; ++sp) {
-      const int k_per = (k_iters_all + sp - 1) / sp;
-      const int s_eff = (k_iters_all + k_per - 1) / k_per;
-      const int64_t rounds = (tiles * s_eff + ctx->sm_count - 1) / ctx->sm_count;
-      double cost = (double)rounds * (k_per + 8) * (128 + bn);
-      if (s_eff > 1) cost += 0.02 * cost;  // the ordered reduction of the partial outputs
-      if (cost < best_cost) {
-        best_cost = cost;
-        best_bn = bn;
-        best_s = s_eff;
+  // CTA pairs: measured faster for 3xTF32 (0.56-0.67 ms against 0.61-0.75 ms per 16384 x 4096 x 1280
+  // panel) and no gain for bf16, whose stages are half as large.  AG_B200_TC_PAIR=0 keeps single CTAs.
+  int n_pairs = 0;
+  if (!bf16 && M > TC_BM) {
+    const char* e = getenv("AG_B200_TC_PAIR");
+    if (!(e && e[0] == '0')) n_pairs = tc_max_pairs<true, EPI_STORE>(ctx, 200 * 1024);
+  }
+  for (int pair = 0; pair <= (n_pairs > 0 ? 1 : 0); ++pair) {
+    const int units = pair ? n_pairs : ctx->sm_count;
+    const int tiles_m_c = (M + (pair ? 2 : 1) * TC_BM - 1) / ((pair ? 2 : 1) * TC_BM);
+    for (int bn : cand) {
+      const int bn_cta = pair ? bn / 2 : bn;
+      if (p.b_mn && bn_cta % p.mn_group != 0) continue;
+      if (pair && bn % 32 != 0) continue;
+      const int tn = (N + bn - 1) / bn;
+      const int64_t tiles = (int64_t)tiles_m_c * tn;
+      int s_max = 1;
+      if (epi_kind == EPI_STORE && splitk_ws && tiles < 2 * (int64_t)units) {
+        s_max = k_iters_all / 16;
+        if (s_max > 16) s_max = 16;
+        const int64_t fit = (int64_t)(splitk_ws_bytes / ((size_t)M * N * sizeof(float)));
+        if (s_max > fit) s_max = (int)fit;
+        if (s_max < 1) s_max = 1;
+      }
+      for (int sp = 1; sp <= s_max; ++sp) {
+        const int k_per = (k_iters_all + sp - 1) / sp;
+        const int s_eff = (k_iters_all + k_per - 1) / k_per;
+        const int64_t rounds = (tiles * s_eff + units - 1) / units;
+        // (a pair works on half as many, twice as tall tiles with half as many units: same rounds)
+        double cost = (double)rounds * (k_per + 8) * (128 + bn_cta);
+        if (s_eff > 1) cost += 0.02 * cost;  // the ordered reduction of the partial outputs
+        if (cost < best_cost) {
+          best_cost = cost;
+          best_bn = bn;
+          best_s = s_eff;
+          best_pair = pair;
+        }
       }
     }
   }
+  const bool pair = best_pair != 0;
+  const int bm_tile = pair ? 2 * TC_BM : TC_BM;
+  const int tiles_m = (M + bm_tile - 1) / bm_tile;
+  const int units = pair ? n_pairs : ctx->sm_count;
   p.BN = best_bn;
+  const int bn_cta = pair ? p.BN / 2 : p.BN;
   p.tiles_m = tiles_m;
   p.tiles_n = (N + p.BN - 1) / p.BN;
   if (tiles_n_out) *tiles_n_out = p.tiles_n;
@@ -740,7 +907,7 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   p.splits = (p.k_iters + p.k_per_split - 1) / p.k_per_split;
   p.split_stride = 0;
   p.a_bytes = (uint32_t)TC_BM * 128u;
-  p.b_bytes = (uint32_t)p.BN * 128u;
+  p.b_bytes = (uint32_t)bn_cta * 128u;
   const uint32_t stage_bytes = (p.a_bytes + p.b_bytes) * (p.split ? 2u : 1u);
   int stages = (TC_SMEM_LIMIT - 1024 - 256) / (int)stage_bytes;
   if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
@@ -748,15 +915,17 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   p.stages = stages;
   // per-wave operand footprint decides the tile order (keep the re-read operand in L2)
   {
-    const int64_t sm = ctx->sm_count;
-    const int64_t fp_m_fast = (tiles_m < sm ? tiles_m : sm) * (int64_t)p.a_bytes + ((sm + tiles_m - 1) / tiles_m) * (int64_t)p.b_bytes;
-    const int64_t fp_n_fast = (p.tiles_n < sm ? p.tiles_n : sm) * (int64_t)p.b_bytes + ((sm + p.tiles_n - 1) / p.tiles_n) * (int64_t)p.a_bytes;
+    const int64_t sm = units;
+    const int64_t ab = (int64_t)p.a_bytes * (pair ? 2 : 1), bb = (int64_t)p.b_bytes * (pair ? 2 : 1);
+    const int64_t fp_m_fast = (tiles_m < sm ? tiles_m : sm) * ab + ((sm + tiles_m - 1) / tiles_m) * bb;
+    const int64_t fp_n_fast = (p.tiles_n < sm ? p.tiles_n : sm) * bb + ((sm + p.tiles_n - 1) / p.tiles_n) * ab;
     p.n_fastest = fp_n_fast <= fp_m_fast ? 1 : 0;
   }
-  // instruction descriptor: D fp32, A/B tf32 or bf16, both K-major, N>>3 at bit 17, M>>4 at bit 24
+  // instruction descriptor: D fp32, A/B tf32 or bf16, operand majors, N>>3 at bit 17, M>>4 at bit 24
+  // (M = 256 for the instruction that spans a CTA pair)
   const uint32_t fmt = bf16 ? 1u : 2u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
-            ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(bm_tile >> 4) << 24);
   p.D = D; p.ldd = ldd; p.accumulate = accumulate ? 1 : 0;
   if (p.splits > 1) {  // partial outputs [splits][M][N] in the workspace, summed in order afterwards
     p.D = splitk_ws;
@@ -780,27 +949,27 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
     return tc_encode(ctx, tm, ptr, bf16, mn_extent, K, op.ld, p.mn_group, p.BK, /*atom32=*/!bf16);
   };
   if ((rc = encode_operand(&tA_hi, A.hi, A, M, TC_BM))) return rc;
-  if ((rc = encode_operand(&tB_hi, B.hi, B, N, p.BN))) return rc;
+  if ((rc = encode_operand(&tB_hi, B.hi, B, N, bn_cta))) return rc;
   if (p.split) {
     if ((rc = encode_operand(&tA_lo, A.lo, A, M, TC_BM))) return rc;
-    if ((rc = encode_operand(&tB_lo, B.lo, B, N, p.BN))) return rc;
+    if ((rc = encode_operand(&tB_lo, B.lo, B, N, bn_cta))) return rc;
   } else {
     tA_lo = tA_hi;
     tB_lo = tB_hi;
   }
   const size_t smem = 1024 + (size_t)stages * stage_bytes + 256;
   const int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.splits;
-  const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+  const int grid = (int)(total < units ? total : units) * (pair ? 2 : 1);
   if (epi_kind == EPI_STATS) {
     AG_REQUIRE(ctx, p.part_ld >= M, "tc_gemm: partial-statistics rows too short");
-    return bf16 ? tc_launch<false, EPI_STATS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
-                : tc_launch<true, EPI_STATS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+    return bf16 ? tc_launch_any<false, EPI_STATS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
+                : tc_launch_any<true, EPI_STATS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
   }
   if (epi_kind == EPI_DLOGITS)
-    return bf16 ? tc_launch<false, EPI_DLOGITS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
-                : tc_launch<true, EPI_DLOGITS>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
-  rc = bf16 ? tc_launch<false, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
-            : tc_launch<true, EPI_STORE>(ctx, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+    return bf16 ? tc_launch_any<false, EPI_DLOGITS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
+                : tc_launch_any<true, EPI_DLOGITS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+  rc = bf16 ? tc_launch_any<false, EPI_STORE>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
+            : tc_launch_any<true, EPI_STORE>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
   if (rc || p.splits == 1) return rc;
   const int64_t n4 = ((int64_t)M * N + 3) / 4;
   int64_t want = (n4 + 255) / 256;
