@@ -51,7 +51,7 @@ def parse_args():
                     help="step: the fused-layer step (the benchmark); kernels: one JSON line per fused layer "
                          "kernel at the shapes of BASELINE configs 1-4, each against its own roofline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--only", default="", help="--workload kernels: comma-separated sections (cfg1,gelu,cfg3,cfg4,cfg2)")
+    ap.add_argument("--only", default="", help="--workload kernels: comma-separated sections (cfg1,gelu,cfg3,cfg4,cfg2,next)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=2048)
     ap.add_argument("--cpu-sample-layers", type=int, default=2)
     return ap.parse_args()
@@ -630,7 +630,32 @@ def run_kernels(a):
                      extra={"scratch_bytes": sbytes})
                 free_all()
 
-    sections = {"cfg1": sec_cfg1, "gelu": sec_gelu, "cfg3": sec_cfg3, "cfg4": sec_cfg4, "cfg2": sec_cfg2}
+    def sec_next():
+        # ---- the rows after the core path: linear + bias + residual projection, AdamW
+        N = 16384
+        for (K, C, what) in ((1280, 1280, "attention out-projection"), (5120, 1280, "MLP down-projection")):
+            for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16", ag.AG_CE_BF16)):
+                x, act, w, b, out = dev(N * C), dev(N * K, std=1.0), dev(K * C, std=0.02), dev(C), dev(N * C)
+                dout, dx, dact, dw, db = dev(N * C), dev(N * C), dev(N * K), dev(K * C), dev(C)
+                sbytes = ctx.linear_add_scratch_bytes(N, K, C, prec)
+                scr = alloc.alloc((sbytes,), np.uint8); bufs.append(scr)
+                ms_f = time_it(lambda i: ctx.linear_add_forward(x, act, w, b, out, N, K, C, prec, scr.ptr.address, sbytes), 1)
+                ms_b = time_it(lambda i: ctx.linear_add_backward(dout, act, w, dx, dact, dw, db, N, K, C, prec,
+                                                                 scr.ptr.address, sbytes), 1)
+                fl = 2.0 * N * K * C
+                emit("next", f"linear_add forward N16384 K{K} C{C} ({what})", ms_f, N, useful_flops=fl, dtype=pname)
+                emit("next", f"linear_add backward N16384 K{K} C{C}", ms_b, N, useful_flops=2 * fl, dtype=pname)
+                free_all()
+        n = 32768 * 1280
+        n_sets = sets_for(4 * n * f4)
+        ps = [dev(n, std=0.02) for _ in range(n_sets)]; gs = [dev(n, std=0.01) for _ in range(n_sets)]
+        ms_ = [dev(n, std=0.0) for _ in range(n_sets)]; vs = [dev(n, std=0.0) for _ in range(n_sets)]
+        ms = time_it(lambda i: ctx.adamw_step(ps[i], gs[i], ms_[i], vs[i], n, 1e-3, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1.0), n_sets)
+        emit("next", "adamw_step 32768x1280 parameters (read p,g,m,v; write p,m,v)", ms, n, alg_bytes=7 * n * f4)
+        free_all()
+
+    sections = {"cfg1": sec_cfg1, "gelu": sec_gelu, "cfg3": sec_cfg3, "cfg4": sec_cfg4, "cfg2": sec_cfg2,
+                "next": sec_next}
     wanted = [s for s in (a.only.split(",") if a.only else sections) if s]
     for name in wanted:
         if name not in sections:
