@@ -649,3 +649,75 @@ def test_errors_are_exceptions_not_aborts():
         ctx.gelu_forward(0, x.storage.ptr.address, 32)
     ctx.synchronize()
     G.free(x)
+
+
+def test_fused_layer_step_matches_oracle():
+    """The kernel sequence that bench.py times (gather, add+LayerNorm, RoPE, GELU, fused linear+CE,
+    their backward passes with the fused residual-gradient add, scatter-add into the tied table), at a
+    small size, replayed with the oracle on the same buffers: loss, every dgamma/dbeta, the tied
+    table gradient, the residual-stream gradient and the in-place rotated q/k must agree."""
+    from autograd_b200.step import FusedLayerStep, StepConfig
+    ctx, alloc, be = G.env()
+    cfg = StepConfig(n_layer=2, n_embd=128, n_head=1, head_dim=128, seq_len=64, batch=3, vocab=640)
+    st = FusedLayerStep(ctx, alloc, be, cfg, seed=77)
+    Nn, C, V, L, I = st.N, st.C, st.V, st.L, st.I
+    B, T, H, D = cfg.batch, cfg.seq_len, cfg.n_head, cfg.head_dim
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, V, size=Nn).astype(np.int32)
+    ids[:40] = 7                                   # a hot row for the scatter-add
+    tg = rng.integers(0, V, size=Nn).astype(np.int32)
+    tg[rng.random(Nn) < 0.1] = -1
+    ctx.copy_from_host(st.ids, ids)
+    ctx.copy_from_host(st.targets, tg)
+    f = np.float32
+    get = lambda addr, shape: ctx.copy_to_host(addr, shape, f).copy()
+    table = get(st.table, (V, C))
+    gam, bet = get(st.gamma, (st.n_norms, C)), get(st.beta, (st.n_norms, C))
+    branch = [get(a, (Nn, C)) for a in st.branch]
+    u = [get(a, (Nn, I)) for a in st.u]
+    dy = [get(st.dy[0], (Nn, C)), get(st.dy[1], (Nn, C))]
+    dg = get(st.dg, (Nn, I))
+    q0, k0 = get(st.q, (B, T, H, D)), get(st.k, (B, T, H, D))
+    cos, sin = get(st.cos, (T, D // 2)), get(st.sin, (T, D // 2))
+
+    st.step()
+    ctx.synchronize()
+    G.check_clean_status()
+
+    # ---- the same sequence with the oracle
+    x = O.gather_forward(ids.reshape(B, T), table).reshape(Nn, C)
+    q, k = q0.copy(), k0.copy()
+    h1s, h2s = [], []
+    for l in range(L):
+        h1, _, _, _ = O.add_layernorm_forward(x, branch[(2 * l) % 4], gam[2 * l], bet[2 * l], cfg.eps)
+        O.rope_apply(q, cos, sin, -1); O.rope_apply(k, cos, sin, -1)
+        h2, _, _, _ = O.add_layernorm_forward(h1, branch[(2 * l + 1) % 4], gam[2 * l + 1], bet[2 * l + 1], cfg.eps)
+        h1s.append(h1); h2s.append(h2)
+        x = h2
+    hf, yf, _, _ = O.add_layernorm_forward(x, branch[0], gam[2 * L], bet[2 * L], cfg.eps)
+    res = O.flce_masked(yf, table, tg)
+    zc = np.zeros(C, f)
+    dgam, dbet = np.zeros((st.n_norms, C), f), np.zeros((st.n_norms, C), f)
+    dh, dgam[2 * L], dbet[2 * L] = O.layernorm_backward(hf, gam[2 * L], res["dX"], cfg.eps, np.zeros_like(hf), zc, zc)
+    du_last = None
+    for l in reversed(range(L)):
+        du_last = O.gelu_backward(u[l], dg, np.zeros_like(dg))
+        dh, dgam[2 * l + 1], dbet[2 * l + 1] = O.layernorm_backward(h2s[l], gam[2 * l + 1], dy[1], cfg.eps, dh, zc, zc)
+        O.rope_apply(q, cos, sin, +1); O.rope_apply(k, cos, sin, +1)
+        # dy[0] was overwritten by the head's dX before the layer loop read it
+        dyl = res["dX"] if l % 2 == 0 else dy[1]
+        dh, dgam[2 * l], dbet[2 * l] = O.layernorm_backward(h1s[l], gam[2 * l], dyl, cfg.eps, dh, zc, zc)
+    dtable = O.gather_backward(ids.reshape(B, T), dh.reshape(B, T, C), res["dW"])
+
+    loss = st.read_loss()
+    assert abs(loss - float(res["loss"])) <= TOL_FWD * abs(loss)
+    small = get(st.small_bucket, (st.n_norms, 2, C))
+    assert_close(small[:, 0], dgam, TOL_BWD, "dgamma of every norm")
+    assert_close(small[:, 1], dbet, TOL_BWD, "dbeta of every norm")
+    assert_close(get(st.dh, (Nn, C)), dh, TOL_BWD, "residual-stream gradient")
+    assert_close(get(st.dtable, (V, C)), dtable, TOL_BWD, "tied table gradient")
+    assert_close(get(st.du, (Nn, I)), du_last, TOL_BWD, "GELU input gradient")
+    # forward rotation followed by the transposed rotation L times: back to the start within rounding
+    assert_close(get(st.q, (B, T, H, D)), q, TOL_FWD * 4, "q after the step")
+    assert_close(get(st.h_final, (Nn, C)), hf, TOL_FWD, "final residual stream")
+    st.close()
