@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(HERE, "libautograd_b200.so")
 AG_OK, AG_ERR_INVALID, AG_ERR_CUDA, AG_ERR_SCRATCH, AG_ERR_DEVICE = range(5)
 AG_F32, AG_BF16 = 0, 1
 AG_STATUS_BAD_INDEX, AG_STATUS_WAIT_EXPIRED, AG_STATUS_STAGE_FALLBACK = 1, 2, 4
-AG_CE_FP32, AG_CE_3XTF32, AG_CE_BF16 = 0, 1, 2
+AG_CE_FP32, AG_CE_3XTF32, AG_CE_BF16, AG_CE_BF16X3 = 0, 1, 2, 3
 AG_CE_MEAN_ALL_ROWS, AG_CE_MEAN_VALID = 0, 1
 AG_CE_IGNORE_MASKED, AG_CE_IGNORE_COMPAT_UNMASKED = 0, 1
 

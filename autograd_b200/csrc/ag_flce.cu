@@ -10,7 +10,7 @@
 // Every dX row tile and every dW vocab panel has exactly one writer CTA per output tile,
 // so the accumulation order is fixed.  The GEMMs of this file are the exact-fp32 (FFMA)
 // implementation used for AG_CE_FP32 and for shapes the tensor-core path does not take;
-// ag_flce_tc.cu provides the tcgen05 panels for AG_CE_3XTF32 / AG_CE_BF16.
+// ag_flce_tc.cu provides the tcgen05 panels for AG_CE_3XTF32 / AG_CE_BF16 / AG_CE_BF16X3.
 #include <math.h>
 
 #include "ag_common.cuh"
@@ -255,7 +255,7 @@ int check_desc(ag_ctx* ctx, const ag_flce_desc* d) {
   AG_REQUIRE(ctx, d->N > 0 && d->C > 0 && d->V > 0 && d->vocab_chunk > 0, "flce: bad shape N=%lld C=%d V=%d chunk=%d",
              (long long)d->N, d->C, d->V, d->vocab_chunk);
   AG_REQUIRE(ctx, d->N < (1ll << 31), "flce: N too large");
-  AG_REQUIRE(ctx, d->precision >= AG_CE_FP32 && d->precision <= AG_CE_BF16, "flce: unknown precision %d", d->precision);
+  AG_REQUIRE(ctx, d->precision >= AG_CE_FP32 && d->precision <= AG_CE_BF16X3, "flce: unknown precision %d", d->precision);
   AG_REQUIRE(ctx, d->reduction == AG_CE_MEAN_ALL_ROWS || d->reduction == AG_CE_MEAN_VALID, "flce: unknown reduction %d",
              d->reduction);
   AG_REQUIRE(ctx, d->ignore_mode == AG_CE_IGNORE_MASKED || d->ignore_mode == AG_CE_IGNORE_COMPAT_UNMASKED,

@@ -23,6 +23,10 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
                      const int32_t* targets, const float* lse, const float* row_scale, const float* dloss,
                      const float* denom, float* dX, float* dW);
 
+// Operand modes of the tensor-core GEMM: tf32 (hi, lo) pairs (3 MMAs per k-step, fp32-grade), bf16
+// values (1 MMA), bf16 (hi, lo) pairs (3 MMAs at the bf16 rate).
+enum AgTcMode { AG_TC_TF32X3 = 0, AG_TC_BF16 = 1, AG_TC_BF16X3 = 2 };
+
 // ---- the tensor-core GEMM as a building block (used by the linear + bias + residual op) --------
 struct AgTcOperand {
   const void* hi;   // tf32 "hi" parts, or the bf16 values
@@ -33,9 +37,9 @@ struct AgTcOperand {
 // D[M,N] (+)= A . B^T with A logically [M][K] and B logically [N][K], each stored K-major or MN-major
 // (+ bias[n]) (+ resid[m,n]); split-K with an ordered reduction when a
 // workspace is given and the problem has few tiles.
-int ag_tc_gemm(ag_ctx* ctx, bool bf16, const AgTcOperand& A, const AgTcOperand& B, float* D, int64_t ldd, int M, int N,
+int ag_tc_gemm(ag_ctx* ctx, int mode, const AgTcOperand& A, const AgTcOperand& B, float* D, int64_t ldd, int M, int N,
                int K, bool accumulate, const float* bias, const float* resid, int64_t ld_resid, float* splitk_ws,
                size_t splitk_ws_bytes);
 // src[R][Cc] (row stride lds) -> operand form [R][Cc] (row stride ldo): (hi, lo) tf32 pairs or bf16 in `hi`.
-int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R,
+int ag_tc_split(ag_ctx* ctx, int mode, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R,
                 int Cc);

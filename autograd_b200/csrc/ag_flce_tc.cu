@@ -15,6 +15,10 @@
 //            issues hi*lo + lo*hi + hi*hi into the same fp32 accumulator (error ~2^-22 of the
 //            product, i.e. fp32-grade logits from tf32 tensor cores);
 //   BF16   : operands rounded to bf16 once, a single MMA per k-step.
+//   BF16X3 : every fp32 operand is split once into hi = bf16(x), lo = bf16(x - hi); the same three
+//            MMAs per k-step at the bf16 rate on half the operand bytes (error ~2^-17 of the
+//            product: inside the 1e-4 bound of the gradients and far inside 1e-5 on the loss, not
+//            on a per-element forward output).
 // The three GEMMs of the head read X, W and dl as stored; no transposed copy exists:
 //   logits  = X   . W^T       A = X  [rows,C] K-major     B = W [vc,C]   K-major
 //   dX     += dl  . W         A = dl [rows,vc] K-major    B = W [vc,C]   MN-major (contraction over vc)
@@ -81,6 +85,10 @@ struct TcParams {
 };
 
 enum { EPI_STORE = 0, EPI_STATS = 1, EPI_DLOGITS = 2 };
+// operand modes (AgTcMode of ag_flce.cuh): tf32 (hi, lo) pairs, bf16 values, bf16 (hi, lo) pairs
+enum { TC_TF32X3 = AG_TC_TF32X3, TC_BF16 = AG_TC_BF16, TC_BF16X3 = AG_TC_BF16X3 };
+constexpr bool tc_mode_tf32(int mode) { return mode == TC_TF32X3; }
+constexpr bool tc_mode_split(int mode) { return mode != TC_BF16; }
 
 // ---------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ void tc_tma_load_2d(const CUtensorMap* tm, void* smem_dst, uint64_t* bar, int x, int y) {
@@ -262,15 +270,17 @@ __device__ __forceinline__ float tc_tf32_rna(float x) {
 // so a pair pulls a third less operand data through shared memory than two single CTAs.  All stage
 // barriers that the MMA waits on live in the leader (rank 0); the leader's commits arrive on the
 // barriers of both CTAs.
-template <bool TF32, int EPI, bool PAIR>
+template <int MODE, int EPI, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant__ CUtensorMap tmA_lo,
                const __grid_constant__ CUtensorMap tmB_hi, const __grid_constant__ CUtensorMap tmB_lo,
                const TcParams p) {
+  constexpr bool TF32 = tc_mode_tf32(MODE);    // element type of the operands: tf32 (in fp32 words) or bf16
+  constexpr bool SPLIT = tc_mode_split(MODE);  // operands come as (hi, lo) pairs, three MMAs per k-step
   extern __shared__ unsigned char tc_smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-  const uint32_t stage_bytes = (p.a_bytes + p.b_bytes) * (p.split ? 2u : 1u);
+  const uint32_t stage_bytes = (p.a_bytes + p.b_bytes) * (SPLIT ? 2u : 1u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)p.stages * stage_bytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + TC_MAX_STAGES;
@@ -373,7 +383,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             }
           };
           load_operand(&tmA_hi, s, m0, TC_BM, p.a_mn, p.a_3d);
-          if (p.split) {
+          if (SPLIT) {
             load_operand(&tmA_lo, s + p.a_bytes, m0, TC_BM, p.a_mn, p.a_3d);
             load_operand(&tmB_hi, s + 2 * p.a_bytes, n0, bn_cta, p.b_mn, p.b_3d);
             load_operand(&tmB_lo, s + 2 * p.a_bytes + p.b_bytes, n0, bn_cta, p.b_mn, p.b_3d);
@@ -399,7 +409,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
       dA.init(p.a_mn, (uint32_t)p.BK * 128u);
       dB.init(p.b_mn, (uint32_t)p.BK * 128u);
       const uint32_t a_lo_off = p.a_bytes >> 4, b_lo_off = p.b_bytes >> 4;
-      const uint32_t b_off = (TF32 ? 2u * p.a_bytes : p.a_bytes) >> 4;
+      const uint32_t b_off = (SPLIT ? 2u * p.a_bytes : p.a_bytes) >> 4;
       const uint32_t stage_units = stage_bytes >> 4;
       const uint32_t tiles_u = ag_smem_u32(tiles) >> 4;
       for (int tile = unit; tile < total_tiles && !expired; tile += unit_stride, ++local) {
@@ -426,7 +436,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {  // BK / umma_k = 4 MMAs along K per stage in both modes
             const uint32_t ao = (uint32_t)kk * dA.step, bo = (uint32_t)kk * dB.step;
-            if (TF32) {
+            if (SPLIT) {
               if (kk == 0)
                 tc_mma<TF32, 2, PAIR>(tacc, ah + ao, dA.hi, bl + bo, dB.hi, p.idesc, not_first);
               else
@@ -610,6 +620,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             if (TF32) {
               hi[j] = tc_tf32_rna(d);
               lo[j] = tc_tf32_rna(d - hi[j]);
+            } else if (SPLIT) {
+              hi[j] = __bfloat162float(__float2bfloat16_rn(d));  // stored as bf16 below without further rounding
+              lo[j] = d - hi[j];
             } else {
               hi[j] = d;
             }
@@ -629,23 +642,28 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
                 if (col + j < p.N) { dh[j] = hi[j]; dlo[j] = lo[j]; }
             }
           } else {
-            __nv_bfloat16* dh = static_cast<__nv_bfloat16*>(p.dl_hi) + (int64_t)row * p.ld_dl + col;
-            if (row_vec && col + 32 <= p.N) {
+            // bf16 operands: the values, or for the split mode the (hi, lo) pair of bf16 arrays
+            auto store_bf16 = [&](void* base, const float (&val)[32]) {
+              __nv_bfloat16* dh = static_cast<__nv_bfloat16*>(base) + (int64_t)row * p.ld_dl + col;
+              if (row_vec && col + 32 <= p.N) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint32_t w[4];
+                for (int j = 0; j < 32; j += 8) {
+                  uint32_t w[4];
 #pragma unroll
-                for (int q2 = 0; q2 < 4; ++q2) {
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(hi[j + 2 * q2], hi[j + 2 * q2 + 1]);
-                  w[q2] = *reinterpret_cast<uint32_t*>(&h2);
+                  for (int q2 = 0; q2 < 4; ++q2) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(val[j + 2 * q2], val[j + 2 * q2 + 1]);
+                    w[q2] = *reinterpret_cast<uint32_t*>(&h2);
+                  }
+                  *reinterpret_cast<uint4*>(dh + j) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                *reinterpret_cast<uint4*>(dh + j) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            } else {
+              } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col + j < p.N) dh[j] = __float2bfloat16_rn(hi[j]);
-            }
+                for (int j = 0; j < 32; ++j)
+                  if (col + j < p.N) dh[j] = __float2bfloat16_rn(val[j]);
+              }
+            };
+            store_bf16(p.dl_hi, hi);
+            if (SPLIT) store_bf16(p.dl_lo, lo);
           }
         }
       }
@@ -759,12 +777,12 @@ splitk_reduce_kernel(const float* __restrict__ P, int splits, int M, int N, floa
 }
 
 // Largest number of CTA pairs (clusters of 2) of this kernel that are resident at once; 0 on error.
-template <bool TF32, int EPI>
+template <int MODE, int EPI>
 int tc_max_pairs(ag_ctx* ctx, size_t smem) {
   static int cached = -1;
   static size_t cached_smem = 0;
   if (cached >= 0 && cached_smem == smem) return cached;
-  auto kern = tc_gemm_kernel<TF32, EPI, true>;
+  auto kern = tc_gemm_kernel<MODE, EPI, true>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * ctx->sm_count);
@@ -787,11 +805,11 @@ int tc_max_pairs(ag_ctx* ctx, size_t smem) {
   return n;
 }
 
-template <bool TF32, int EPI, bool PAIR>
+template <int MODE, int EPI, bool PAIR>
 int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const CUtensorMap& a_lo,
               const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
   static bool attr_done = false;
-  auto kern = tc_gemm_kernel<TF32, EPI, PAIR>;
+  auto kern = tc_gemm_kernel<MODE, EPI, PAIR>;
   if (!attr_done) {
     AG_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT));
     attr_done = true;
@@ -824,23 +842,31 @@ int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const
   return AG_OK;
 }
 
-template <bool TF32, int EPI>
-int tc_launch_any(ag_ctx* ctx, bool pair, int grid, size_t smem, const CUtensorMap& a_hi, const CUtensorMap& a_lo,
-                  const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
-  return pair ? tc_launch<TF32, EPI, true>(ctx, grid, smem, a_hi, a_lo, b_hi, b_lo, p)
-              : tc_launch<TF32, EPI, false>(ctx, grid, smem, a_hi, a_lo, b_hi, b_lo, p);
+template <int EPI>
+int tc_launch_any(ag_ctx* ctx, int mode, bool pair, int grid, size_t smem, const CUtensorMap& a_hi,
+                  const CUtensorMap& a_lo, const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
+#define TC_LAUNCH_MODE(M)                                                                      \
+  return pair ? tc_launch<M, EPI, true>(ctx, grid, smem, a_hi, a_lo, b_hi, b_lo, p)            \
+              : tc_launch<M, EPI, false>(ctx, grid, smem, a_hi, a_lo, b_hi, b_lo, p);
+  switch (mode) {
+    case TC_TF32X3: TC_LAUNCH_MODE(TC_TF32X3)
+    case TC_BF16: TC_LAUNCH_MODE(TC_BF16)
+    default: TC_LAUNCH_MODE(TC_BF16X3)
+  }
+#undef TC_LAUNCH_MODE
 }
 
 // `epi` (may be null = EPI_STORE) carries the fields of the fused cross-entropy epilogues.
-int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, float* D, int64_t ldd, int M, int N, int K,
+int tc_gemm(ag_ctx* ctx, int mode, const TcOperand& A, const TcOperand& B, float* D, int64_t ldd, int M, int N, int K,
             bool accumulate, int epi_kind = EPI_STORE, const TcParams* epi = nullptr, int* tiles_n_out = nullptr,
             float* splitk_ws = nullptr, size_t splitk_ws_bytes = 0) {
   TcParams p = {};
   if (epi) p = *epi;
   p.M = M; p.N = N; p.K = K;
+  const bool bf16 = !tc_mode_tf32(mode);  // element type of the operands
   p.BK = bf16 ? 64 : 32;
   p.umma_k = bf16 ? 16 : 8;
-  p.split = bf16 ? 0 : 1;
+  p.split = tc_mode_split(mode) ? 1 : 0;
   // Tile width, split-K factor and CTA pairing.  Measured behaviour of this kernel: a k-step costs
   // time in proportion to the operand bytes a CTA pulls through shared memory (128 A rows + the B rows
   // it loads: BN, or BN/2 as one CTA of a pair), a tile costs about 8 k-steps of prologue / epilogue on
@@ -854,11 +880,13 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   p.b_mn = B.mn_major ? 1 : 0;
   p.mn_group = bf16 ? 64 : 32;
   // CTA pairs: measured faster for 3xTF32 (0.56-0.67 ms against 0.61-0.75 ms per 16384 x 4096 x 1280
-  // panel) and no gain for bf16, whose stages are half as large.  AG_B200_TC_PAIR=0 keeps single CTAs.
+  // panel) and no gain for plain bf16, whose stages are half as large: pairs are used by the split
+  // modes.  AG_B200_TC_PAIR=0 keeps single CTAs.
   int n_pairs = 0;
-  if (!bf16 && M > TC_BM) {
+  if (p.split && M > TC_BM) {
     const char* e = getenv("AG_B200_TC_PAIR");
-    if (!(e && e[0] == '0')) n_pairs = tc_max_pairs<true, EPI_STORE>(ctx, 200 * 1024);
+    if (!(e && e[0] == '0'))
+      n_pairs = bf16 ? tc_max_pairs<TC_BF16X3, EPI_STORE>(ctx, 200 * 1024) : tc_max_pairs<TC_TF32X3, EPI_STORE>(ctx, 200 * 1024);
   }
   for (int pair = 0; pair <= (n_pairs > 0 ? 1 : 0); ++pair) {
     const int units = pair ? n_pairs : ctx->sm_count;
@@ -962,14 +990,10 @@ int tc_gemm(ag_ctx* ctx, bool bf16, const TcOperand& A, const TcOperand& B, floa
   const int grid = (int)(total < units ? total : units) * (pair ? 2 : 1);
   if (epi_kind == EPI_STATS) {
     AG_REQUIRE(ctx, p.part_ld >= M, "tc_gemm: partial-statistics rows too short");
-    return bf16 ? tc_launch_any<false, EPI_STATS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
-                : tc_launch_any<true, EPI_STATS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+    return tc_launch_any<EPI_STATS>(ctx, mode, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
   }
-  if (epi_kind == EPI_DLOGITS)
-    return bf16 ? tc_launch_any<false, EPI_DLOGITS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
-                : tc_launch_any<true, EPI_DLOGITS>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
-  rc = bf16 ? tc_launch_any<false, EPI_STORE>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p)
-            : tc_launch_any<true, EPI_STORE>(ctx, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+  if (epi_kind == EPI_DLOGITS) return tc_launch_any<EPI_DLOGITS>(ctx, mode, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
+  rc = tc_launch_any<EPI_STORE>(ctx, mode, pair, grid, smem, tA_hi, tA_lo, tB_hi, tB_lo, p);
   if (rc || p.splits == 1) return rc;
   const int64_t n4 = ((int64_t)M * N + 3) / 4;
   int64_t want = (n4 + 255) / 256;
@@ -993,7 +1017,7 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
 
 // src[R][Cc] (row stride lds) -> operand form [R][Cc] (row stride ldo): (hi, lo) tf32 pairs, or bf16
 // values in `hi`.  Cc, lds and ldo are multiples of 4; one thread converts 4 consecutive elements.
-template <bool BF16>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 split_kernel(const float* __restrict__ src, int64_t lds, void* __restrict__ hi, void* __restrict__ lo, int64_t ldo,
              int R, int Cc) {
@@ -1004,11 +1028,7 @@ split_kernel(const float* __restrict__ src, int64_t lds, void* __restrict__ hi, 
     const int64_t r = i / c4;
     const int c = (int)(i - r * c4) << 2;
     const float4 x = *reinterpret_cast<const float4*>(src + r * lds + c);
-    if (BF16) {
-      __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
-      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(hi) + r * ldo + c) =
-          make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-    } else {
+    if (MODE == TC_TF32X3) {
       float4 h, l;
       split_tf32(x.x, h.x, l.x);
       split_tf32(x.y, h.y, l.y);
@@ -1016,6 +1036,16 @@ split_kernel(const float* __restrict__ src, int64_t lds, void* __restrict__ hi, 
       split_tf32(x.w, h.w, l.w);
       *reinterpret_cast<float4*>(static_cast<float*>(hi) + r * ldo + c) = h;
       *reinterpret_cast<float4*>(static_cast<float*>(lo) + r * ldo + c) = l;
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(hi) + r * ldo + c) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+      if (MODE == TC_BF16X3) {  // lo = bf16(x - hi)
+        const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+        __nv_bfloat162 la = __floats2bfloat162_rn(x.x - fa.x, x.y - fa.y), lb = __floats2bfloat162_rn(x.z - fb.x, x.w - fb.y);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(lo) + r * ldo + c) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&la), *reinterpret_cast<uint32_t*>(&lb));
+      }
     }
   }
 }
@@ -1047,6 +1077,10 @@ ce_merge_partials_kernel(const float2* __restrict__ part, int64_t part_ld, int t
 }
 
 // ---------------------------------------------------------------------------- workspace plan
+inline int tc_mode_of(int precision) {
+  return precision == AG_CE_BF16 ? TC_BF16 : (precision == AG_CE_BF16X3 ? TC_BF16X3 : TC_TF32X3);
+}
+
 struct TcPlan {
   int64_t rows_tile, vc;
   size_t es;  // operand element size
@@ -1059,8 +1093,9 @@ inline int64_t up8(int64_t x) { return (x + 7) & ~(int64_t)7; }
 
 TcPlan tc_plan(const ag_flce_desc* d) {
   TcPlan p;
-  const bool bf16 = d->precision == AG_CE_BF16;
-  p.es = bf16 ? 2 : 4;
+  const int mode = tc_mode_of(d->precision);
+  const bool bf16 = mode == TC_BF16;  // one array per operand (no lo part)
+  p.es = tc_mode_tf32(mode) ? 4 : 2;
   p.rows_tile = d->N < 16384 ? d->N : 16384;
   p.vc = d->vocab_chunk < d->V ? d->vocab_chunk : d->V;
   const int64_t ldr = up8(p.rows_tile), ldc = up8(p.vc);
@@ -1084,15 +1119,17 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   return p;
 }
 
-int tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R, int Cc) {
+int tc_split(ag_ctx* ctx, int mode, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R, int Cc) {
   AG_REQUIRE(ctx, Cc % 4 == 0 && lds % 4 == 0 && ldo % 4 == 0 && R < (1ll << 31), "tc_split: rows must be whole 16-byte packets");
   int64_t want = (R * (Cc / 4) + 255) / 256;
   if (want > (int64_t)ctx->sm_count * 16) want = (int64_t)ctx->sm_count * 16;
   if (want < 1) want = 1;
-  if (bf16)
-    split_kernel<true><<<(int)want, 256, 0, ctx->stream>>>(src, lds, hi, lo, ldo, (int)R, Cc);
+  if (mode == TC_TF32X3)
+    split_kernel<TC_TF32X3><<<(int)want, 256, 0, ctx->stream>>>(src, lds, hi, lo, ldo, (int)R, Cc);
+  else if (mode == TC_BF16)
+    split_kernel<TC_BF16><<<(int)want, 256, 0, ctx->stream>>>(src, lds, hi, lo, ldo, (int)R, Cc);
   else
-    split_kernel<false><<<(int)want, 256, 0, ctx->stream>>>(src, lds, hi, lo, ldo, (int)R, Cc);
+    split_kernel<TC_BF16X3><<<(int)want, 256, 0, ctx->stream>>>(src, lds, hi, lo, ldo, (int)R, Cc);
   AG_LAUNCHED(ctx, "split_kernel");
   return AG_OK;
 }
@@ -1100,7 +1137,7 @@ int tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, vo
 }  // namespace
 
 // ---- entry points for other translation units (ag_flce.cuh) ---------------------------------
-int ag_tc_gemm(ag_ctx* ctx, bool bf16, const AgTcOperand& A, const AgTcOperand& B, float* D, int64_t ldd, int M, int N,
+int ag_tc_gemm(ag_ctx* ctx, int mode, const AgTcOperand& A, const AgTcOperand& B, float* D, int64_t ldd, int M, int N,
                int K, bool accumulate, const float* bias, const float* resid, int64_t ld_resid, float* splitk_ws,
                size_t splitk_ws_bytes) {
   TcParams e = {};
@@ -1108,19 +1145,19 @@ int ag_tc_gemm(ag_ctx* ctx, bool bf16, const AgTcOperand& A, const AgTcOperand& 
   e.resid = resid;
   e.ld_resid = ld_resid;
   TcOperand a{A.hi, A.lo, A.ld, A.mn_major}, b{B.hi, B.lo, B.ld, B.mn_major};
-  return tc_gemm(ctx, bf16, a, b, D, ldd, M, N, K, accumulate, EPI_STORE, &e, nullptr, splitk_ws, splitk_ws_bytes);
+  return tc_gemm(ctx, mode, a, b, D, ldd, M, N, K, accumulate, EPI_STORE, &e, nullptr, splitk_ws, splitk_ws_bytes);
 }
 
-int ag_tc_split(ag_ctx* ctx, bool bf16, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R,
+int ag_tc_split(ag_ctx* ctx, int mode, const float* src, int64_t lds, void* hi, void* lo, int64_t ldo, int64_t R,
                 int Cc) {
-  return tc_split(ctx, bf16, src, lds, hi, lo, ldo, R, Cc);
+  return tc_split(ctx, mode, src, lds, hi, lo, ldo, R, Cc);
 }
 
 // =========================================================================================
 bool ag_flce_tc_supported(const ag_flce_desc* d) {
-  if (d->precision != AG_CE_3XTF32 && d->precision != AG_CE_BF16) return false;
+  if (d->precision != AG_CE_3XTF32 && d->precision != AG_CE_BF16 && d->precision != AG_CE_BF16X3) return false;
   // TMA needs 16-byte aligned row starts: rows of X / W are C elements long
-  const int q = d->precision == AG_CE_BF16 ? 8 : 4;
+  const int q = d->precision == AG_CE_3XTF32 ? 4 : 8;
   if (d->C % q != 0) return false;
   if (d->vocab_chunk % 8 != 0 && d->vocab_chunk < d->V) return false;
   if (d->C < 32 || d->V < 32 || d->N < 1) return false;
@@ -1132,10 +1169,10 @@ size_t ag_flce_tc_scratch_bytes(const ag_flce_desc* d) { return tc_plan(d).total
 int ag_flce_tc_prepare(ag_ctx* ctx, const ag_flce_desc* d, const float* X, const float* W, void* tc_scratch) {
   const TcPlan p = tc_plan(d);
   unsigned char* b = static_cast<unsigned char*>(tc_scratch);
-  const bool bf16 = d->precision == AG_CE_BF16;
+  const int mode = tc_mode_of(d->precision);
   int rc;
-  if ((rc = tc_split(ctx, bf16, X, d->C, b + p.X_hi, b + p.X_lo, d->C, d->N, d->C))) return rc;
-  return tc_split(ctx, bf16, W, d->C, b + p.W_hi, b + p.W_lo, d->C, d->V, d->C);
+  if ((rc = tc_split(ctx, mode, X, d->C, b + p.X_hi, b + p.X_lo, d->C, d->N, d->C))) return rc;
+  return tc_split(ctx, mode, W, d->C, b + p.W_hi, b + p.W_lo, d->C, d->V, d->C);
 }
 
 int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64_t r0, int rows, int v0,
@@ -1143,7 +1180,7 @@ int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratc
                              bool first_panel) {
   const TcPlan p = tc_plan(d);
   unsigned char* b = static_cast<unsigned char*>(tc_scratch);
-  const bool bf16 = d->precision == AG_CE_BF16;
+  const int mode = tc_mode_of(d->precision);
   const size_t row_bytes = (size_t)d->C * p.es;
   TcOperand A{b + p.X_hi + (size_t)r0 * row_bytes, b + p.X_lo + (size_t)r0 * row_bytes, d->C};
   TcOperand B{b + p.W_hi + (size_t)v0 * row_bytes, b + p.W_lo + (size_t)v0 * row_bytes, d->C};
@@ -1155,7 +1192,7 @@ int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratc
   e.part_ld = p.part_ld;
   e.tgt_logit = tgt_logit + r0;
   int tiles_n = 0;
-  int rc = tc_gemm(ctx, bf16, A, B, nullptr, 0, rows, vc, d->C, false, EPI_STATS, &e, &tiles_n);
+  int rc = tc_gemm(ctx, mode, A, B, nullptr, 0, rows, vc, d->C, false, EPI_STATS, &e, &tiles_n);
   if (rc) return rc;
   ce_merge_partials_kernel<<<(rows + 255) / 256, 256, 0, ctx->stream>>>(e.part, e.part_ld, tiles_n * 2, rows, run_max + r0,
                                                                       run_sum + r0, first_panel ? 1 : 0);
@@ -1168,7 +1205,7 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
                      const float* denom, float* dX, float* dW) {
   const TcPlan p = tc_plan(d);
   unsigned char* b = static_cast<unsigned char*>(tc_scratch);
-  const bool bf16 = d->precision == AG_CE_BF16;
+  const int mode = tc_mode_of(d->precision);
   const int64_t ldc = up8(p.vc);
   const size_t row_bytes = (size_t)d->C * p.es;
   int rc;
@@ -1186,21 +1223,21 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
     e.denom = denom;
     e.ignore_mode = d->ignore_mode;
     e.dl_hi = b + p.dl_hi; e.dl_lo = b + p.dl_lo; e.ld_dl = ldc;
-    if ((rc = tc_gemm(ctx, bf16, A, B, nullptr, 0, rows, vc, d->C, false, EPI_DLOGITS, &e))) return rc;
+    if ((rc = tc_gemm(ctx, mode, A, B, nullptr, 0, rows, vc, d->C, false, EPI_DLOGITS, &e))) return rc;
   }
   if (dX) {
     // dX[r0:r0+rows, :] += dl [rows, vc] . W[v0:v0+vc, :]; W as stored has the contraction index
     // (vocabulary) as its row index, i.e. it is the MN-major form of the B operand
     TcOperand A{b + p.dl_hi, b + p.dl_lo, ldc, 0};
     TcOperand B{b + p.W_hi + (size_t)v0 * row_bytes, b + p.W_lo + (size_t)v0 * row_bytes, d->C, 1};
-    if ((rc = tc_gemm(ctx, bf16, A, B, dX + r0 * d->C, d->C, rows, d->C, vc, true))) return rc;
+    if ((rc = tc_gemm(ctx, mode, A, B, dX + r0 * d->C, d->C, rows, d->C, vc, true))) return rc;
   }
   if (dW) {
     // dW[v0:v0+vc, :] += dl^T . X[r0:r0+rows, :]; the contraction index (row) is the row index of
     // both dl and X as stored: both operands MN-major
     TcOperand A{b + p.dl_hi, b + p.dl_lo, ldc, 1};
     TcOperand B{b + p.X_hi + (size_t)r0 * row_bytes, b + p.X_lo + (size_t)r0 * row_bytes, d->C, 1};
-    if ((rc = tc_gemm(ctx, bf16, A, B, dW + (int64_t)v0 * d->C, d->C, vc, d->C, rows, true, EPI_STORE, nullptr, nullptr,
+    if ((rc = tc_gemm(ctx, mode, A, B, dW + (int64_t)v0 * d->C, d->C, vc, d->C, rows, true, EPI_STORE, nullptr, nullptr,
                       reinterpret_cast<float*>(b + p.splitk), p.splitk_bytes)))
       return rc;
   }

@@ -106,12 +106,12 @@ extern "C" int ag_linear_add_forward(ag_ctx* ctx, const float* x, const float* a
   AG_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "ag_linear_add_forward: scratch not 256-byte aligned");
   unsigned char* s = static_cast<unsigned char*>(scratch);
   const bool bf16 = precision == AG_CE_BF16;
-  if ((rc = ag_tc_split(ctx, bf16, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
-  if ((rc = ag_tc_split(ctx, bf16, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
+  if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
+  if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
   // B[n = C][k = K] is W[K][C] as stored with the contraction index as row index: MN-major
   AgTcOperand A{s + p.act, s + p.act_lo, K, 0};
   AgTcOperand B{s + p.w, s + p.w_lo, C, 1};
-  return ag_tc_gemm(ctx, bf16, A, B, out, C, (int)N, C, K, false, b, x, C, nullptr, 0);
+  return ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, out, C, (int)N, C, K, false, b, x, C, nullptr, 0);
 }
 
 extern "C" int ag_linear_add_backward(ag_ctx* ctx, const float* dout, const float* act, const float* w, float* dx,
@@ -141,20 +141,20 @@ extern "C" int ag_linear_add_backward(ag_ctx* ctx, const float* dout, const floa
     AG_LAUNCHED(ctx, "colsum_final_kernel");
   }
   if (!dact && !dw) return AG_OK;
-  if ((rc = ag_tc_split(ctx, bf16, dout, C, s + p.dout, s + p.dout_lo, C, N, C))) return rc;
+  if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, dout, C, s + p.dout, s + p.dout_lo, C, N, C))) return rc;
   if (dact) {
     // dact[N,K] += dout[N,C] . (W[K,C])^T : both K-major as stored
-    if ((rc = ag_tc_split(ctx, bf16, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
+    if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
     AgTcOperand A{s + p.dout, s + p.dout_lo, C, 0};
     AgTcOperand B{s + p.w, s + p.w_lo, C, 0};
-    if ((rc = ag_tc_gemm(ctx, bf16, A, B, dact, K, (int)N, K, C, true, nullptr, nullptr, 0, nullptr, 0))) return rc;
+    if ((rc = ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, dact, K, (int)N, K, C, true, nullptr, nullptr, 0, nullptr, 0))) return rc;
   }
   if (dw) {
     // dW[K,C] += act^T . dout : the contraction index (token row) is the row index of both as stored
-    if ((rc = ag_tc_split(ctx, bf16, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
+    if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
     AgTcOperand A{s + p.act, s + p.act_lo, K, 1};
     AgTcOperand B{s + p.dout, s + p.dout_lo, C, 1};
-    if ((rc = ag_tc_gemm(ctx, bf16, A, B, dw, C, K, C, (int)N, true, nullptr, nullptr, 0,
+    if ((rc = ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, dw, C, K, C, (int)N, true, nullptr, nullptr, 0,
                          reinterpret_cast<float*>(s + p.splitk), p.splitk_bytes)))
       return rc;
   }
