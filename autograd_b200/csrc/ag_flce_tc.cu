@@ -763,16 +763,43 @@ int tc_encode_mn3(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int6
 }
 
 // D[m][n] (+)= sum over splits, in split order, of the partial outputs P[s][m][n].
+// VEC: N, ldd multiples of 4 and 16-byte aligned pointers: one 16-byte packet per thread and split,
+// all splits' packets requested before the first add.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ P, int splits, int M, int N, float* D, int64_t ldd, int accumulate) {
   const int64_t total = (int64_t)M * N;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int m = (int)(i / N), n = (int)(i - (int64_t)m * N);
-    float* d = D + (int64_t)m * ldd + n;
-    float acc = accumulate ? *d : 0.0f;
-    for (int sp = 0; sp < splits; ++sp) acc += P[(int64_t)sp * total + i];
-    *d = acc;
+  if (VEC) {
+    const int n4 = N >> 2;
+    const int64_t packets = (int64_t)M * n4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < packets; i += stride) {
+      const int m = (int)(i / n4), n = (int)(i - (int64_t)m * n4) << 2;
+      float4* d = reinterpret_cast<float4*>(D + (int64_t)m * ldd + n);
+      const float* src = P + (int64_t)m * N + n;
+      float4 acc = accumulate ? *d : make_float4(0.f, 0.f, 0.f, 0.f);
+      int sp = 0;
+      for (; sp + 4 <= splits; sp += 4) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(src + (int64_t)(sp + u) * total));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+      }
+      for (; sp < splits; ++sp) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(src + (int64_t)sp * total));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      *d = acc;
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int m = (int)(i / N), n = (int)(i - (int64_t)m * N);
+      float* d = D + (int64_t)m * ldd + n;
+      float acc = accumulate ? *d : 0.0f;
+      for (int sp = 0; sp < splits; ++sp) acc += P[(int64_t)sp * total + i];
+      *d = acc;
+    }
   }
 }
 
@@ -998,7 +1025,12 @@ int tc_gemm(ag_ctx* ctx, int mode, const TcOperand& A, const TcOperand& B, float
   const int64_t n4 = ((int64_t)M * N + 3) / 4;
   int64_t want = (n4 + 255) / 256;
   if (want > (int64_t)ctx->sm_count * 8) want = (int64_t)ctx->sm_count * 8;
-  splitk_reduce_kernel<<<(int)want, 256, 0, ctx->stream>>>(splitk_ws, p.splits, M, N, D, ldd, accumulate ? 1 : 0);
+  const bool vec = (N % 4 == 0) && (ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15u) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(splitk_ws) & 15u) == 0);
+  if (vec)
+    splitk_reduce_kernel<true><<<(int)want, 256, 0, ctx->stream>>>(splitk_ws, p.splits, M, N, D, ldd, accumulate ? 1 : 0);
+  else
+    splitk_reduce_kernel<false><<<(int)want, 256, 0, ctx->stream>>>(splitk_ws, p.splits, M, N, D, ldd, accumulate ? 1 : 0);
   AG_LAUNCHED(ctx, "splitk_reduce_kernel");
   return AG_OK;
 }
