@@ -335,6 +335,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = p.tiles_m * p.tiles_n * p.splits;
   bool expired = false;
+  // Everything above touched no global memory and may overlap the tail of the previous kernel of the
+  // stream; from here on its results are read.  The grid is a single wave, so the next kernel may be
+  // scheduled as soon as this one's CTAs leave their SMs.
+  ag_pdl_wait();
+  ag_pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -768,6 +773,7 @@ int tc_encode_mn3(ag_ctx* ctx, CUtensorMap* tm, const void* ptr, bool bf16, int6
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ P, int splits, int M, int N, float* D, int64_t ldd, int accumulate) {
+  ag_pdl_wait();
   const int64_t total = (int64_t)M * N;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   if (VEC) {
@@ -843,24 +849,30 @@ int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const
   }
   int rc_ev;
   if (ctx->tc_timing && (rc_ev = ag_event_record(ctx, ctx->tc_timing_base + 2 * ctx->tc_timing_count))) return rc_ev;
-  if (PAIR) {
+  {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = 2;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute at[2];
+    int n_at = 0;
+    if (PAIR) {
+      at[n_at].id = cudaLaunchAttributeClusterDimension;
+      at[n_at].val.clusterDim.x = 2;
+      at[n_at].val.clusterDim.y = 1;
+      at[n_at].val.clusterDim.z = 1;
+      ++n_at;
+    }
+    if (ctx->pdl) {
+      at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[n_at].val.programmaticStreamSerializationAllowed = 1;
+      ++n_at;
+    }
     cfg.attrs = at;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = n_at;
     AG_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, a_hi, a_lo, b_hi, b_lo, p));
     ctx->launches++;
-  } else {
-    kern<<<grid, TC_THREADS, smem, ctx->stream>>>(a_hi, a_lo, b_hi, b_lo, p);
-    AG_LAUNCHED(ctx, "tc_gemm_kernel");
   }
   if (ctx->tc_timing) {
     if ((rc_ev = ag_event_record(ctx, ctx->tc_timing_base + 2 * ctx->tc_timing_count + 1))) return rc_ev;
@@ -1028,10 +1040,11 @@ int tc_gemm(ag_ctx* ctx, int mode, const TcOperand& A, const TcOperand& B, float
   const bool vec = (N % 4 == 0) && (ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15u) == 0) &&
                    ((reinterpret_cast<uintptr_t>(splitk_ws) & 15u) == 0);
   if (vec)
-    splitk_reduce_kernel<true><<<(int)want, 256, 0, ctx->stream>>>(splitk_ws, p.splits, M, N, D, ldd, accumulate ? 1 : 0);
+    AG_LAUNCH_PDL(ctx, "splitk_reduce_kernel", splitk_reduce_kernel<true>, (int)want, 256, 0, (const float*)splitk_ws,
+                  p.splits, M, N, D, ldd, accumulate ? 1 : 0);
   else
-    splitk_reduce_kernel<false><<<(int)want, 256, 0, ctx->stream>>>(splitk_ws, p.splits, M, N, D, ldd, accumulate ? 1 : 0);
-  AG_LAUNCHED(ctx, "splitk_reduce_kernel");
+    AG_LAUNCH_PDL(ctx, "splitk_reduce_kernel", splitk_reduce_kernel<false>, (int)want, 256, 0, (const float*)splitk_ws,
+                  p.splits, M, N, D, ldd, accumulate ? 1 : 0);
   return AG_OK;
 }
 
@@ -1087,6 +1100,7 @@ split_kernel(const float* __restrict__ src, int64_t lds, void* __restrict__ hi, 
 __global__ void __launch_bounds__(256)
 ce_merge_partials_kernel(const float2* __restrict__ part, int64_t part_ld, int tiles_n, int rows,
                          float* __restrict__ run_max, float* __restrict__ run_sum, int first_panel) {
+  ag_pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float m, s;
@@ -1226,9 +1240,8 @@ int ag_flce_tc_forward_panel(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratc
   int tiles_n = 0;
   int rc = tc_gemm(ctx, mode, A, B, nullptr, 0, rows, vc, d->C, false, EPI_STATS, &e, &tiles_n);
   if (rc) return rc;
-  ce_merge_partials_kernel<<<(rows + 255) / 256, 256, 0, ctx->stream>>>(e.part, e.part_ld, tiles_n * 2, rows, run_max + r0,
-                                                                      run_sum + r0, first_panel ? 1 : 0);
-  AG_LAUNCHED(ctx, "ce_merge_partials_kernel");
+  AG_LAUNCH_PDL(ctx, "ce_merge_partials_kernel", ce_merge_partials_kernel, (rows + 255) / 256, 256, 0,
+                (const float2*)e.part, e.part_ld, tiles_n * 2, rows, run_max + r0, run_sum + r0, first_panel ? 1 : 0);
   return AG_OK;
 }
 
