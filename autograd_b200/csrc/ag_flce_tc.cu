@@ -17,8 +17,8 @@
 //   BF16   : operands rounded to bf16 once, a single MMA per k-step.
 //   BF16X3 : every fp32 operand is split once into hi = bf16(x), lo = bf16(x - hi); the same three
 //            MMAs per k-step at the bf16 rate on half the operand bytes (error ~2^-17 of the
-//            product: inside the 1e-4 bound of the gradients and far inside 1e-5 on the loss, not
-//            on a per-element forward output).
+//            product: measured like 3xTF32 on the gradients, 3e-5 to 5e-5 of their rms, and 1e-7 on the
+//            loss; not good enough for a per-element forward output held to 1e-5).
 // The three GEMMs of the head read X, W and dl as stored; no transposed copy exists:
 //   logits  = X   . W^T       A = X  [rows,C] K-major     B = W [vc,C]   K-major
 //   dX     += dl  . W         A = dl [rows,vc] K-major    B = W [vc,C]   MN-major (contraction over vc)
@@ -936,15 +936,28 @@ int tc_gemm(ag_ctx* ctx, int mode, const TcOperand& A, const TcOperand& B, float
       if (pair && bn % 32 != 0) continue;
       const int tn = (N + bn - 1) / bn;
       const int64_t tiles = (int64_t)tiles_m_c * tn;
-      int s_max = 1;
-      if (epi_kind == EPI_STORE && splitk_ws && tiles < 2 * (int64_t)units) {
-        s_max = k_iters_all / 16;
-        if (s_max > 16) s_max = 16;
+      // Split-K serves two purposes.  Speed: few tiles are spread over more CTAs.  Accuracy: the tensor
+      // core adds every MMA into the fp32 accumulator with truncation, a bias that grows with the length
+      // of the accumulation chain (measured on dW, 16384 rows: 2.7e-4 of the rms with one chain, 3.6e-5
+      // with 8, for tf32; bf16 MMAs about three times that); the partial sums of the splits are added
+      // with round-to-nearest.  So K per chain is bounded whenever a workspace allows it.
+      int s_max = 1, s_min = 1;
+      if (epi_kind == EPI_STORE && splitk_ws) {
         const int64_t fit = (int64_t)(splitk_ws_bytes / ((size_t)M * N * sizeof(float)));
-        if (s_max > fit) s_max = (int)fit;
+        const int k_chain = bf16 ? 1024 : 2048;  // contraction elements per accumulation chain
+        s_min = (K + k_chain - 1) / k_chain;
+        if (s_min > 16) s_min = 16;
+        if (s_min > fit) s_min = fit < 1 ? 1 : (int)fit;
+        if (tiles < 2 * (int64_t)units) {
+          s_max = k_iters_all / 16;
+          if (s_max > 16) s_max = 16;
+          if (s_max > fit) s_max = (int)fit;
+        }
+        if (s_max < s_min) s_max = s_min;
         if (s_max < 1) s_max = 1;
+        if (p.split == 0) s_min = 1;  // plain bf16 (2e-2): no accuracy constraint
       }
-      for (int sp = 1; sp <= s_max; ++sp) {
+      for (int sp = s_min; sp <= s_max; ++sp) {
         const int k_per = (k_iters_all + sp - 1) / sp;
         const int s_eff = (k_iters_all + k_per - 1) / k_per;
         const int64_t rounds = (tiles * s_eff + units - 1) / units;

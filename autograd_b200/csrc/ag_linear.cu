@@ -152,11 +152,18 @@ extern "C" int ag_linear_add_backward(ag_ctx* ctx, const float* dout, const floa
   if (dw) {
     // dW[K,C] += act^T . dout : the contraction index (token row) is the row index of both as stored
     if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
-    AgTcOperand A{s + p.act, s + p.act_lo, K, 1};
-    AgTcOperand B{s + p.dout, s + p.dout_lo, C, 1};
-    if ((rc = ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, dw, C, K, C, (int)N, true, nullptr, nullptr, 0,
-                         reinterpret_cast<float*>(s + p.splitk), p.splitk_bytes)))
-      return rc;
+    // Row tiles of at most 32768 tokens: with the 16 splits the workspace allows, an accumulation chain
+    // inside the tensor core then covers at most 2048 rows (its truncating adds bias long chains); the
+    // tiles' results are added into dW by the epilogue of the split-K reduction, round-to-nearest.
+    const size_t es = bf16 ? 2 : 4;
+    for (int64_t r0 = 0; r0 < N; r0 += 32768) {
+      const int rows = (int)(N - r0 < 32768 ? N - r0 : 32768);
+      AgTcOperand A{s + p.act + (size_t)r0 * K * es, s + p.act_lo + (size_t)r0 * K * es, K, 1};
+      AgTcOperand B{s + p.dout + (size_t)r0 * C * es, s + p.dout_lo + (size_t)r0 * C * es, C, 1};
+      if ((rc = ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, dw, C, K, C, rows, true, nullptr, nullptr, 0,
+                           reinterpret_cast<float*>(s + p.splitk), p.splitk_bytes)))
+        return rc;
+    }
   }
   return AG_OK;
 }

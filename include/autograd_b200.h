@@ -190,8 +190,9 @@ int ag_gather_backward(ag_ctx* ctx, const int32_t* ids, const float* dout, float
  * backend.py:3155-3301 + metal_ops.metal:8808-9180 (Metal path).
  * logits = X (N,C) . W (V,C)^T are produced one vocab chunk at a time and never stored
  * whole.  A row takes part when 0 <= target < V. */
-/* precision: exact fp32 FFMA; 3xTF32 tensor cores (fp32-grade); bf16 tensor cores (2e-2); bf16 (hi, lo)
- * pairs, three MMAs at the bf16 rate (products to ~2^-17: loss to 1e-5, gradients to 1e-4) */
+/* precision: exact fp32 FFMA; 3xTF32 tensor cores (fp32-grade, the default); bf16 tensor cores (2e-2);
+ * bf16 (hi, lo) pairs, three MMAs at the bf16 rate (products to ~2^-17; measured like 3xTF32: loss to
+ * 1e-5, gradients to 1e-4) */
 enum { AG_CE_FP32 = 0, AG_CE_3XTF32 = 1, AG_CE_BF16 = 2, AG_CE_BF16X3 = 3 };
 enum { AG_CE_MEAN_ALL_ROWS = 0, AG_CE_MEAN_VALID = 1 };              /* reduction        */
 enum { AG_CE_IGNORE_MASKED = 0, AG_CE_IGNORE_COMPAT_UNMASKED = 1 };  /* ignored-row grads */

@@ -84,4 +84,3 @@ def assert_close(got, ref, tol, what=""):
 TOL_FWD = 1e-5      # fp32 forward
 TOL_BWD = 1e-4      # fp32 backward reductions
 TOL_BF16 = 2e-2     # bf16 storage mode
-TOL_BF16X3_DW = 3e-4   # dW of the bf16 (hi, lo) pair mode of the CE head: a stated mode, not fp32-grade

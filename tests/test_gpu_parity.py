@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import gpu_util as G
-from conftest import TOL_BF16, TOL_BF16X3_DW, TOL_BWD, TOL_FWD, assert_close, mixed_rel_err
+from conftest import TOL_BF16, TOL_BWD, TOL_FWD, assert_close, mixed_rel_err
 from oracle import fused_layers as O
 
 pytestmark = pytest.mark.gpu
@@ -463,7 +463,7 @@ def test_flce_mid_size_vs_oracle(N, C, V, precision):
     loss, dX, dW = _run_flce(be, X_, W_, Y_, precision, ignore_mode=0, chunk=4096, dloss=0.5)
     assert abs(loss - float(ref["loss"])) <= TOL_FWD * abs(loss)
     assert_close(dX[0], ref["dX"], TOL_BWD, "dX")
-    assert_close(dW, ref["dW"], TOL_BF16X3_DW if precision == 3 else TOL_BWD, "dW")
+    assert_close(dW, ref["dW"], TOL_BWD, "dW")
     G.check_clean_status()
 
 
@@ -498,10 +498,9 @@ def test_flce_config2_full_size(C):
 
 @pytest.mark.parametrize("C", [384, 1280])
 def test_flce_bf16x3_config2_full_size(C):
-    """The bf16 (hi, lo) pair mode (three MMAs at the bf16 rate) at the full config-2 size: loss 1e-5
-    and dX 1e-4 as for fp32; dW, a sum over 16384 token rows accumulated inside the tensor core, is
-    held to 3e-4 (measured 0.6e-4 to 2.0e-4 over the shapes tried, 3xTF32: 0.4e-4 to 0.5e-4).  It is a
-    stated faster mode, not the fp32-grade default."""
+    """The bf16 (hi, lo) pair mode (three MMAs at the bf16 rate) at the full config-2 size against the
+    fp32 tolerances of the path: loss 1e-5, dX and dW 1e-4 (measured 3e-5 to 5e-5, like 3xTF32, once
+    the accumulation chains of dW are bounded by split-K); the measured errors are printed."""
     ctx, alloc, be = G.env()
     N, V = 16384, 32768
     rng = np.random.default_rng(1235 + C)
@@ -515,9 +514,29 @@ def test_flce_bf16x3_config2_full_size(C):
           f"dX {mixed_rel_err(dX[0], ref['dX']):.2e}, dW {mixed_rel_err(dW, ref['dW']):.2e}")
     assert abs(loss - float(ref["loss"])) <= TOL_FWD * abs(loss)
     assert_close(dX[0], ref["dX"], TOL_BWD, "dX")
-    assert_close(dW, ref["dW"], TOL_BF16X3_DW, "dW")
+    assert_close(dW, ref["dW"], TOL_BWD, "dW")
     ignored = Y_[0] < 0
     assert not dX[0][ignored].any()
+    G.check_clean_status()
+
+
+@pytest.mark.parametrize("precision", [1, 3])
+def test_flce_wide_hidden_keeps_accumulation_chains_short(precision):
+    """16384 rows x hidden 4096: the dW panel has enough tiles to fill the GPU without split-K, and one
+    accumulation chain over 16384 rows inside the tensor core is measurably biased (2.7e-4 of the rms
+    at hidden 384).  The plan must split K for accuracy, not only for occupancy."""
+    ctx, alloc, be = G.env()
+    N, C, V = 16384, 4096, 4096
+    rng = np.random.default_rng(99)
+    X_ = (rng.standard_normal((1, N, C)) / np.sqrt(C)).astype(np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C))).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(1, N)).astype(np.int32)
+    ref = O.flce_masked(X_[0], W_, Y_[0])
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, precision, ignore_mode=0, chunk=4096)
+    print(f"precision {precision}: dX {mixed_rel_err(dX[0], ref['dX']):.2e}, dW {mixed_rel_err(dW, ref['dW']):.2e}")
+    assert abs(loss - float(ref["loss"])) <= TOL_FWD * abs(loss)
+    assert_close(dX[0], ref["dX"], TOL_BWD, "dX")
+    assert_close(dW, ref["dW"], TOL_BWD, "dW")
     G.check_clean_status()
 
 
