@@ -46,15 +46,16 @@ class StepConfig:
 class FamilyTimer:
     """Collects (start, end) event index pairs per kernel family for one or more steps."""
 
-    def __init__(self, ctx):
+    def __init__(self, ctx, base=0):
         self.ctx = ctx
         self.pairs = {}
-        self.next = 0
+        self.base = base          # first event index this timer may use
+        self.next = base
         self.enabled = False
 
     def reset(self):
         self.pairs = {}
-        self.next = 0
+        self.next = self.base
 
     def begin(self, family):
         if not self.enabled:

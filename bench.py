@@ -293,7 +293,14 @@ def run_b200(a):
         one_step(i, e2e=True)
     ctx.check_status()
 
-    EV0, EV1 = (1 << 20), (1 << 20) + 1   # event indices outside the family timer's range
+    # Event indices: 0, 1 bracket the timed regions, the family timer uses [16, TC_BASE), the per-launch
+    # events of the tensor-core GEMM [TC_BASE, ...).  The pool is grown to its final size here: growing
+    # it at the first use inside a pass would delay the ranks by different amounts, and the early ranks
+    # would then wait for the late ones inside their timed region (at the allreduce).
+    EV0, EV1 = 0, 1
+    TC_BASE = 1 << 14
+    step.timer.base = 16
+    ctx.event_record(TC_BASE + 4 * 64 * (a.steps + 1))
 
     # ---- device-resident timing: exactly `steps` steps between two events, nothing else in the stream
     barrier()
@@ -311,7 +318,6 @@ def run_b200(a):
     # kernels from overlapping their launch, so this pass is a little slower than the one above.
     step.timer.reset()
     step.timer.enabled = True
-    TC_BASE = 1 << 19                     # events of the per-launch timing of the tensor-core GEMM
     barrier()
     ctx.tc_timing(True, TC_BASE)
     ctx.event_record(EV0)
@@ -516,7 +522,7 @@ def run_kernels(a):
         for i in range(a.warmup):
             fn(i % n_sets)
         ctx.synchronize()
-        E0, E1 = (1 << 20) + 2, (1 << 20) + 3
+        E0, E1 = 2, 3
         ctx.event_record(E0)
         for i in range(a.steps):
             fn(i % n_sets)
