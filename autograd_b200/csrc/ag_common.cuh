@@ -23,7 +23,8 @@ struct ag_ctx {
   cudaEvent_t* ev_pool;  // ag_event_record / ag_event_elapsed
   int ev_pool_size;
   int64_t launches;
-  int pdl;              // 1: bandwidth kernels are launched with programmatic stream serialization
+  int pdl;              // 1: kernels are launched with programmatic stream serialization
+  int tc_pair;          // 1: the split-operand tensor-core GEMMs run on CTA pairs (cta_group::2)
   int tc_timing;        // ag_tc_timing: bracket tensor-core GEMM launches with pool events
   int tc_timing_base;
   int tc_timing_count;

@@ -30,7 +30,6 @@
 // Every mbarrier wait is bounded; on expiry the CTA raises AG_STATUS_WAIT_EXPIRED, all roles
 // leave their loops, TMEM is released and the kernel returns.  Every CTA loads its own tiles; no thread-block clusters.
 #include <cuda.h>
-#include <stdlib.h>
 
 #include "ag_flce.cuh"
 
@@ -922,11 +921,8 @@ int tc_gemm(ag_ctx* ctx, int mode, const TcOperand& A, const TcOperand& B, float
   // panel) and no gain for plain bf16, whose stages are half as large: pairs are used by the split
   // modes.  AG_B200_TC_PAIR=0 keeps single CTAs.
   int n_pairs = 0;
-  if (p.split && M > TC_BM) {
-    const char* e = getenv("AG_B200_TC_PAIR");
-    if (!(e && e[0] == '0'))
-      n_pairs = bf16 ? tc_max_pairs<TC_BF16X3, EPI_STORE>(ctx, 200 * 1024) : tc_max_pairs<TC_TF32X3, EPI_STORE>(ctx, 200 * 1024);
-  }
+  if (p.split && M > TC_BM && ctx->tc_pair)
+    n_pairs = bf16 ? tc_max_pairs<TC_BF16X3, EPI_STORE>(ctx, 200 * 1024) : tc_max_pairs<TC_TF32X3, EPI_STORE>(ctx, 200 * 1024);
   for (int pair = 0; pair <= (n_pairs > 0 ? 1 : 0); ++pair) {
     const int units = pair ? n_pairs : ctx->sm_count;
     const int tiles_m_c = (M + (pair ? 2 : 1) * TC_BM - 1) / ((pair ? 2 : 1) * TC_BM);
