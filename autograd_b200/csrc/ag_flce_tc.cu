@@ -4,9 +4,10 @@
 // K-major ([MN][K], K contiguous) or MN-major ([K][MN], MN contiguous):
 //   warp 0      : TMA producer  - cp.async.bulk.tensor tiles (128-byte swizzle) into a ring of
 //                 shared-memory stages, completion on mbarriers;
-//   warp 1      : allocates TMEM, then one elected lane issues tcgen05.mma (cta_group::1,
-//                 M = 128, N = BN) from shared-memory descriptors into one of two TMEM
-//                 accumulators; tcgen05.commit releases stages and publishes accumulators;
+//   warp 1      : allocates TMEM, then one elected lane issues tcgen05.mma (M = 128, N = BN with
+//                 cta_group::1; M = 256 over a pair of CTAs with cta_group::2) from shared-memory
+//                 descriptors into one of two TMEM accumulators; tcgen05.commit releases stages and
+//                 publishes accumulators;
 //   warps 2..9  : epilogue - tcgen05.ld of the finished accumulator (one TMEM lane = one output
 //                 row per thread), store / accumulate to global memory, while the MMA warp
 //                 already works on the next tile in the other accumulator.
@@ -25,10 +26,14 @@
 //   dW     += dl^T. X         A = dl [rows,vc] MN-major   B = X [rows,C] MN-major (contraction over rows)
 // An MN-major tile is fetched as one 3-d TMA box {128 bytes of MN, BK k-rows, MN groups} (one 2-d box per
 // group when the MN extent is ragged) and described to the MMA with the transposing descriptor forms
-// (see tc_smem_desc_mn).
+// (see TcDesc).
 // Every output tile has exactly one writer, so accumulation order is fixed.
 // Every mbarrier wait is bounded; on expiry the CTA raises AG_STATUS_WAIT_EXPIRED, all roles
-// leave their loops, TMEM is released and the kernel returns.  Every CTA loads its own tiles; no thread-block clusters.
+// leave their loops, TMEM is released and the kernel returns.  The split-operand modes run on clusters
+// of two CTAs (see tc_gemm_kernel); every CTA loads its own tiles with plain (single-destination) TMA
+// loads.
+// Accumulation inside the tensor core truncates, so the length of an accumulation chain is bounded by
+// split-K where a workspace exists (see tc_gemm).
 #include <cuda.h>
 
 #include "ag_flce.cuh"
