@@ -108,10 +108,22 @@ extern "C" int ag_linear_add_forward(ag_ctx* ctx, const float* x, const float* a
   const bool bf16 = precision == AG_CE_BF16;
   if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, act, K, s + p.act, s + p.act_lo, K, N, K))) return rc;
   if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
-  // B[n = C][k = K] is W[K][C] as stored with the contraction index as row index: MN-major
-  AgTcOperand A{s + p.act, s + p.act_lo, K, 0};
-  AgTcOperand B{s + p.w, s + p.w_lo, C, 1};
-  return ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, out, C, (int)N, C, K, false, b, x, C, nullptr, 0);
+  // B[n = C][k = K] is W[K][C] as stored with the contraction index as row index: MN-major.
+  // K is taken in chunks of at most 2048: an accumulation chain inside the tensor core is biased in
+  // proportion to its length (its adds truncate), the chunks' results are added by the epilogue with
+  // round-to-nearest.  The first chunk carries bias and residual.
+  const size_t es = bf16 ? 2 : 4;
+  const int k_chunk = bf16 ? K : 2048;
+  for (int k0 = 0; k0 < K; k0 += k_chunk) {
+    const int kc = K - k0 < k_chunk ? K - k0 : k_chunk;
+    AgTcOperand A{s + p.act + (size_t)k0 * es, s + p.act_lo + (size_t)k0 * es, K, 0};
+    AgTcOperand B{s + p.w + (size_t)k0 * C * es, s + p.w_lo + (size_t)k0 * C * es, C, 1};
+    const bool first = k0 == 0;
+    if ((rc = ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, out, C, (int)N, C, kc, !first, first ? b : nullptr,
+                         first ? x : nullptr, C, nullptr, 0)))
+      return rc;
+  }
+  return AG_OK;
 }
 
 extern "C" int ag_linear_add_backward(ag_ctx* ctx, const float* dout, const float* act, const float* w, float* dx,
@@ -145,9 +157,17 @@ extern "C" int ag_linear_add_backward(ag_ctx* ctx, const float* dout, const floa
   if (dact) {
     // dact[N,K] += dout[N,C] . (W[K,C])^T : both K-major as stored
     if ((rc = ag_tc_split(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, w, C, s + p.w, s + p.w_lo, C, K, C))) return rc;
-    AgTcOperand A{s + p.dout, s + p.dout_lo, C, 0};
-    AgTcOperand B{s + p.w, s + p.w_lo, C, 0};
-    if ((rc = ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, dact, K, (int)N, K, C, true, nullptr, nullptr, 0, nullptr, 0))) return rc;
+    // contraction over C in chunks of at most 2048 (bounded accumulation chains, see the forward)
+    const size_t es_ = bf16 ? 2 : 4;
+    const int c_chunk = bf16 ? C : 2048;
+    for (int c0 = 0; c0 < C; c0 += c_chunk) {
+      const int cc = C - c0 < c_chunk ? C - c0 : c_chunk;
+      AgTcOperand A{s + p.dout + (size_t)c0 * es_, s + p.dout_lo + (size_t)c0 * es_, C, 0};
+      AgTcOperand B{s + p.w + (size_t)c0 * es_, s + p.w_lo + (size_t)c0 * es_, C, 0};
+      if ((rc = ag_tc_gemm(ctx, bf16 ? AG_TC_BF16 : AG_TC_TF32X3, A, B, dact, K, (int)N, K, cc, true, nullptr, nullptr, 0,
+                           nullptr, 0)))
+        return rc;
+    }
   }
   if (dw) {
     // dW[K,C] += act^T . dout : the contraction index (token row) is the row index of both as stored
