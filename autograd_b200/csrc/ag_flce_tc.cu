@@ -1286,10 +1286,15 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
   }
   if (dX) {
     // dX[r0:r0+rows, :] += dl [rows, vc] . W[v0:v0+vc, :]; W as stored has the contraction index
-    // (vocabulary) as its row index, i.e. it is the MN-major form of the B operand
-    TcOperand A{b + p.dl_hi, b + p.dl_lo, ldc, 0};
-    TcOperand B{b + p.W_hi + (size_t)v0 * row_bytes, b + p.W_lo + (size_t)v0 * row_bytes, d->C, 1};
-    if ((rc = tc_gemm(ctx, mode, A, B, dX + r0 * d->C, d->C, rows, d->C, vc, true))) return rc;
+    // (vocabulary) as its row index, i.e. it is the MN-major form of the B operand.  Panels wider than
+    // 4096 are taken in pieces of 4096 columns: bounded accumulation chains (see tc_gemm), the pieces
+    // are added by the accumulating epilogue.
+    for (int k0 = 0; k0 < vc; k0 += 4096) {
+      const int kc = vc - k0 < 4096 ? vc - k0 : 4096;
+      TcOperand A{b + p.dl_hi + (size_t)k0 * p.es, b + p.dl_lo + (size_t)k0 * p.es, ldc, 0};
+      TcOperand B{b + p.W_hi + (size_t)(v0 + k0) * row_bytes, b + p.W_lo + (size_t)(v0 + k0) * row_bytes, d->C, 1};
+      if ((rc = tc_gemm(ctx, mode, A, B, dX + r0 * d->C, d->C, rows, d->C, kc, true))) return rc;
+    }
   }
   if (dW) {
     // dW[v0:v0+vc, :] += dl^T . X[r0:r0+rows, :]; the contraction index (row) is the row index of

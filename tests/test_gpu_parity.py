@@ -467,6 +467,24 @@ def test_flce_mid_size_vs_oracle(N, C, V, precision):
     G.check_clean_status()
 
 
+@pytest.mark.parametrize("precision", [1, 3])
+def test_flce_wide_vocab_panel(precision):
+    """Vocabulary panels wider than 4096 columns: the dX contraction is taken in pieces of 4096."""
+    ctx, alloc, be = G.env()
+    N, C, V = 768, 256, 8192 + 40
+    rng = np.random.default_rng(4321)
+    X_ = (rng.standard_normal((1, N, C)) / np.sqrt(C)).astype(np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C))).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(1, N)).astype(np.int32)
+    Y_[rng.random((1, N)) < 0.05] = -1
+    ref = O.flce_masked(X_[0], W_, Y_[0])
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, precision, ignore_mode=0, chunk=8192)
+    assert abs(loss - float(ref["loss"])) <= TOL_FWD * abs(loss)
+    assert_close(dX[0], ref["dX"], TOL_BWD, "dX")
+    assert_close(dW, ref["dW"], TOL_BWD, "dW")
+    G.check_clean_status()
+
+
 @pytest.mark.parametrize("C", [384, 1280])
 def test_flce_config2_full_size(C):
     """Config 2 at full size: 16384 tokens, vocab 32768, chunk 4096, 5 % ignored, 3xTF32 tensor-core
