@@ -432,6 +432,8 @@ def run_b200(a):
             if isinstance(tr, dict):   # measured on a smaller capture: bytes per launch and what it scales with
                 roofline["traffic"] = tr.get("bytes_per_launch")
                 roofline["traffic_note"] = tr.get("note")
+                if tr.get("tensor_pipe_note"):
+                    roofline["tensor_pipe_note"] = tr.get("tensor_pipe_note")
             else:
                 roofline["traffic"] = tr
 
