@@ -87,6 +87,10 @@ __device__ __forceinline__ void ag_pdl_wait() { asm volatile("griddepcontrol.wai
 __device__ __forceinline__ void ag_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
 
+// Per-device slots of the small host-side caches (function attributes and occupancy are per device).
+constexpr int AG_MAX_DEVICES = 64;
+static inline int ag_dev_slot(const ag_ctx* ctx) { return ctx->device >= 0 && ctx->device < AG_MAX_DEVICES ? ctx->device : 0; }
+
 static inline bool ag_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static inline int ag_ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }

@@ -816,8 +816,15 @@ splitk_reduce_kernel(const float* __restrict__ P, int splits, int M, int N, floa
 // Largest number of CTA pairs (clusters of 2) of this kernel that are resident at once; 0 on error.
 template <int MODE, int EPI>
 int tc_max_pairs(ag_ctx* ctx, size_t smem) {
-  static int cached = -1;
-  static size_t cached_smem = 0;
+  static int cached_dev[AG_MAX_DEVICES];
+  static size_t cached_smem_dev[AG_MAX_DEVICES];
+  static bool init_done = false;
+  if (!init_done) {
+    for (int i = 0; i < AG_MAX_DEVICES; ++i) cached_dev[i] = -1;
+    init_done = true;
+  }
+  int& cached = cached_dev[ag_dev_slot(ctx)];
+  size_t& cached_smem = cached_smem_dev[ag_dev_slot(ctx)];
   if (cached >= 0 && cached_smem == smem) return cached;
   auto kern = tc_gemm_kernel<MODE, EPI, true>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT) != cudaSuccess) return 0;
@@ -845,11 +852,11 @@ int tc_max_pairs(ag_ctx* ctx, size_t smem) {
 template <int MODE, int EPI, bool PAIR>
 int tc_launch(ag_ctx* ctx, int grid, size_t smem, const CUtensorMap& a_hi, const CUtensorMap& a_lo,
               const CUtensorMap& b_hi, const CUtensorMap& b_lo, const TcParams& p) {
-  static bool attr_done = false;
+  static bool attr_done[AG_MAX_DEVICES] = {};
   auto kern = tc_gemm_kernel<MODE, EPI, PAIR>;
-  if (!attr_done) {
+  if (!attr_done[ag_dev_slot(ctx)]) {
     AG_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT));
-    attr_done = true;
+    attr_done[ag_dev_slot(ctx)] = true;
   }
   int rc_ev;
   if (ctx->tc_timing && (rc_ev = ag_event_record(ctx, ctx->tc_timing_base + 2 * ctx->tc_timing_count))) return rc_ev;

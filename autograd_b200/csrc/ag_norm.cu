@@ -554,7 +554,7 @@ inline int persistent_grid(const ag_ctx* ctx, int64_t N, int ctas_per_sm, int64_
 }
 
 // Resident CTAs per SM of one kernel instantiation at a given dynamic shared-memory size;
-// queried once per (kernel, smem) and cached (single host thread per context).
+// queried once per (kernel, device, smem) and cached (single host thread per context).
 template <typename K>
 int resident_ctas(ag_ctx* ctx, K kern, size_t smem, int* cache, size_t* cache_smem) {
   if (*cache > 0 && *cache_smem == smem) return *cache;
@@ -574,9 +574,9 @@ int launch_fwd_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const
                   float* s1, int64_t N, int C, float eps) {
   const size_t smem = (size_t)2 * C * sizeof(float);
   auto kern = norm_forward_kernel<T, KP, KIND>;
-  static int occ_cache = 0;
-  static size_t occ_smem = 0;
-  const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
+  static int occ_cache[AG_MAX_DEVICES] = {};
+  static size_t occ_smem[AG_MAX_DEVICES] = {};
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache[ag_dev_slot(ctx)], &occ_smem[ag_dev_slot(ctx)]);
   if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_forward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
   const int grid = persistent_grid(ctx, N, occ);
   AG_LAUNCH_PDL(ctx, "norm_forward_kernel", kern, grid, NORM_THREADS, smem, x, r, gamma, beta, h, y, s0, s1, N, C, eps,
@@ -620,9 +620,9 @@ int launch_bwd_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, cons
                   int wg, int wb, int64_t N, int C, float eps, int* grid_out) {
   const size_t smem = norm_bwd_smem<KIND>(C);
   auto kern = norm_backward_kernel<T, KP, KIND>;
-  static int occ_cache = 0;
-  static size_t occ_smem = 0;
-  const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
+  static int occ_cache[AG_MAX_DEVICES] = {};
+  static size_t occ_smem[AG_MAX_DEVICES] = {};
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache[ag_dev_slot(ctx)], &occ_smem[ag_dev_slot(ctx)]);
   if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
   const int grid = persistent_grid(ctx, N, occ, max_partial_rows(ctx));
   AG_LAUNCH_PDL(ctx, "norm_backward_kernel", kern, grid, NORM_THREADS, smem, dy, x, gamma, dres, dx, partials, wg, wb, N, C,
@@ -795,9 +795,9 @@ int ln_noalloc_launch_kp(ag_ctx* ctx, const float* dy, const float* x, const flo
                          float* partials, int wg, int wb, int64_t N, int C, float eps, int max_grid, int* grid_out) {
   const size_t smem = norm_bwd_smem<kLayerNorm>(C);
   auto kern = norm_backward_kernel<float, KP, kLayerNorm>;
-  static int occ_cache = 0;
-  static size_t occ_smem = 0;
-  const int occ = resident_ctas(ctx, kern, smem, &occ_cache, &occ_smem);
+  static int occ_cache[AG_MAX_DEVICES] = {};
+  static size_t occ_smem[AG_MAX_DEVICES] = {};
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache[ag_dev_slot(ctx)], &occ_smem[ag_dev_slot(ctx)]);
   if (occ < 0)
     AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
   int grid = persistent_grid(ctx, N, occ);
