@@ -642,7 +642,7 @@ def run_kernels(a):
         tg_ = rng.integers(0, V, size=N).astype(np.int32)
         tg_[rng.random(N) < 0.05] = -1
         for C in (384, 1280):
-            for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16", ag.AG_CE_BF16)):
+            for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16", ag.AG_CE_BF16), ("bf16x3", ag.AG_CE_BF16X3)):
                 X = dev(N * C, std=1.0 / np.sqrt(C)); W = dev(V * C, std=0.02)
                 dX, dW = dev(N * C), dev(V * C)
                 tg = dev(N, np.int32, ints=tg_)
