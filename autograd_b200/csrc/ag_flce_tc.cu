@@ -233,6 +233,28 @@ __device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) 
 
 __device__ __forceinline__ void tc_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 32-byte (whole sector) global accesses of one lane: the epilogues give every lane 128 contiguous
+// bytes of its own row, which four of these cover with full-sector writes (16-byte stores fill half a
+// sector per request).  Addresses must be 32-byte aligned.
+struct F8 { float v[8]; };
+__device__ __forceinline__ F8 tc_ld_global_v8(const float* p) {
+  F8 r;
+  asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7])
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void tc_st_global_v8(float* p, const float* v) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]),
+               "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
+}
+__device__ __forceinline__ void tc_st_global_v8_b32(void* p, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
 // Bounded wait that also gives up when another role of the CTA has already given up.
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
@@ -492,9 +514,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     const int c_first = half * 32;
     uint32_t full_par[2] = {0, 0};
     int local = 0;
-    const bool vec_ok = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) &&
-                        (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) &&
-                        (!p.resid || (((p.ld_resid & 3) == 0) && (reinterpret_cast<uintptr_t>(p.resid) & 15u) == 0));
+    // 32-byte accesses: rows and bases aligned to a sector
+    const bool vec_ok = ((p.ldd & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 31u) == 0) &&
+                        (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 31u) == 0) &&
+                        (!p.resid || (((p.ld_resid & 7) == 0) && (reinterpret_cast<uintptr_t>(p.resid) & 31u) == 0));
     for (int tile = unit; tile < total_tiles; tile += unit_stride, ++local) {
       const int buf = local & 1;
       int tm, tn, k_begin, k_end, split_id;
@@ -519,37 +542,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             if (vec_ok && col + 32 <= p.N) {
               // all loads of a source are issued before anything is stored: with a load and a store per
               // packet in one loop the eight round trips to memory would be taken one after the other
-              float4* dst = reinterpret_cast<float4*>(drow + col);
-              float4 v[8];
+              float* dst = drow + col;
+              float v[32];
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                v[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                                   __uint_as_float(r[4 * j + 3]));
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
               if (p.accumulate) {
-                float4 o[8];
+                F8 o[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = dst[j];
+                for (int j = 0; j < 4; ++j) o[j] = tc_ld_global_v8(dst + 8 * j);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { v[j].x += o[j].x; v[j].y += o[j].y; v[j].z += o[j].z; v[j].w += o[j].w; }
+                for (int j = 0; j < 32; ++j) v[j] += o[j >> 3].v[j & 7];
               }
               if (p.bias) {
-                const float4* bsrc = reinterpret_cast<const float4*>(p.bias + col);
-                float4 o[8];
+                F8 o[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = __ldg(bsrc + j);
+                for (int j = 0; j < 4; ++j) o[j] = tc_ld_global_v8(p.bias + col + 8 * j);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { v[j].x += o[j].x; v[j].y += o[j].y; v[j].z += o[j].z; v[j].w += o[j].w; }
+                for (int j = 0; j < 32; ++j) v[j] += o[j >> 3].v[j & 7];
               }
               if (p.resid) {
-                const float4* rsrc = reinterpret_cast<const float4*>(p.resid + (int64_t)row * p.ld_resid + col);
-                float4 o[8];
+                const float* rsrc = p.resid + (int64_t)row * p.ld_resid + col;
+                F8 o[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = rsrc[j];
+                for (int j = 0; j < 4; ++j) o[j] = tc_ld_global_v8(rsrc + 8 * j);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { v[j].x += o[j].x; v[j].y += o[j].y; v[j].z += o[j].z; v[j].w += o[j].w; }
+                for (int j = 0; j < 32; ++j) v[j] += o[j >> 3].v[j & 7];
               }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) dst[j] = v[j];
+              for (int j = 0; j < 4; ++j) tc_st_global_v8(dst + 8 * j, v + 8 * j);
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -610,7 +630,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
           e = p.lse[row];
           tcol = valid ? t - p.v0 : -1;
         }
-        const bool row_vec = ((p.ld_dl & 7) == 0);
+        // 32-byte stores: whole-sector rows (8 floats, 16 bf16) on sector-aligned bases
+        const bool row_vec = ((p.ld_dl & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.dl_hi) & 31u) == 0) &&
+                             (!p.dl_lo || (reinterpret_cast<uintptr_t>(p.dl_lo) & 31u) == 0);
         for (int c0 = c_first; c0 < p.BN; c0 += 64) {
           uint32_t r[32];
           tc_tmem_ld32(tacc + (uint32_t)c0, r);
@@ -641,9 +663,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             float* dlo = static_cast<float*>(p.dl_lo) + (int64_t)row * p.ld_dl + col;
             if (row_vec && col + 32 <= p.N) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                *reinterpret_cast<float4*>(dh + j) = make_float4(hi[j], hi[j + 1], hi[j + 2], hi[j + 3]);
-                *reinterpret_cast<float4*>(dlo + j) = make_float4(lo[j], lo[j + 1], lo[j + 2], lo[j + 3]);
+              for (int j = 0; j < 32; j += 8) {
+                tc_st_global_v8(dh + j, hi + j);
+                tc_st_global_v8(dlo + j, lo + j);
               }
             } else {
 #pragma unroll
@@ -656,14 +678,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
               __nv_bfloat16* dh = static_cast<__nv_bfloat16*>(base) + (int64_t)row * p.ld_dl + col;
               if (row_vec && col + 32 <= p.N) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint32_t w[4];
+                for (int j = 0; j < 32; j += 16) {
+                  uint32_t w[8];
 #pragma unroll
-                  for (int q2 = 0; q2 < 4; ++q2) {
+                  for (int q2 = 0; q2 < 8; ++q2) {
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(val[j + 2 * q2], val[j + 2 * q2 + 1]);
                     w[q2] = *reinterpret_cast<uint32_t*>(&h2);
                   }
-                  *reinterpret_cast<uint4*>(dh + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                  tc_st_global_v8_b32(dh + j, w);
                 }
               } else {
 #pragma unroll
@@ -1157,6 +1179,7 @@ struct TcPlan {
 
 inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 inline int64_t up8(int64_t x) { return (x + 7) & ~(int64_t)7; }
+inline int64_t up16(int64_t x) { return (x + 15) & ~(int64_t)15; }  // dl rows: whole 32-byte sectors in bf16 too
 
 TcPlan tc_plan(const ag_flce_desc* d) {
   TcPlan p;
@@ -1165,7 +1188,7 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   p.es = tc_mode_tf32(mode) ? 4 : 2;
   p.rows_tile = d->N < 16384 ? d->N : 16384;
   p.vc = d->vocab_chunk < d->V ? d->vocab_chunk : d->V;
-  const int64_t ldr = up8(p.rows_tile), ldc = up8(p.vc);
+  const int64_t ldr = up8(p.rows_tile), ldc = up16(p.vc);
   size_t off = 0;
   auto take = [&](size_t elems) { size_t o = off; off += up256(elems * p.es); return o; };
   p.X_hi = take((size_t)d->N * d->C);
@@ -1272,7 +1295,7 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
   const TcPlan p = tc_plan(d);
   unsigned char* b = static_cast<unsigned char*>(tc_scratch);
   const int mode = tc_mode_of(d->precision);
-  const int64_t ldc = up8(p.vc);
+  const int64_t ldc = up16(p.vc);
   const size_t row_bytes = (size_t)d->C * p.es;
   int rc;
   {
