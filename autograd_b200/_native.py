@@ -80,6 +80,10 @@ SIGNATURES = {
     "ag_linear_add_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _int, _int, _int, _ptr, _sz]),
     "ag_linear_add_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _int, _int, _int, _ptr, _sz]),
     "ag_adamw_step": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _i64, _f64, _f64, _f64, _f64, _f64, _f64, _f64]),
+    "ag_f32_to_bf16": (_int, [_ctx, _ptr, _ptr, _i64, _int]),
+    "ag_bf16_to_f32": (_int, [_ctx, _ptr, _ptr, _i64]),
+    "ag_gather_backward_bf16": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _sz, _i64, _int, _int]),
+    "ag_adamw_step_bf16grad": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _i64, _f64, _f64, _f64, _f64, _f64, _f64, _f64]),
 }
 
 

@@ -69,6 +69,7 @@ class CudaBackend:
         self.ce_reduction = N.AG_CE_MEAN_ALL_ROWS
         self.ce_ignore_mode = N.AG_CE_IGNORE_MASKED
         self._workspace = None       # grow-only scratch for calls that arrive without arena scratch
+        self._grad_stage = None      # grow-only fp32 staging of gradients whose storage is bf16
         self._side = {}              # id(loss tensor) -> Storage holding lse (forward -> backward)
         self._forward = {
             "LayerNormOp": self._layernorm_forward,
@@ -171,8 +172,10 @@ class CudaBackend:
     def adamw_step(self, p_storage, g_storage, m_storage, v_storage, tmp_storage, lr, lr_t, b1, b2, eps,
                    weight_decay, grad_scale=1.0, **_ignored):
         n = int(prod(p_storage.shape))
+        grad_bf16 = np.dtype(g_storage.dtype) == np.dtype(np.uint16)  # backend.py:5128, :5139
         self._context.adamw_step(address_of(p_storage), address_of(g_storage), address_of(m_storage),
-                                 address_of(v_storage), n, lr, lr_t, b1, b2, eps, weight_decay, grad_scale)
+                                 address_of(v_storage), n, lr, lr_t, b1, b2, eps, weight_decay, grad_scale,
+                                 grad_bf16=grad_bf16)
 
     # ------------------------------------------------------------------ Add / MatMul binding
     def bind_add_forward(self, node):
@@ -219,6 +222,42 @@ class CudaBackend:
                 self._allocator.free(self._workspace)
             self._workspace = self._allocator.alloc((nbytes,), np.uint8)
         return self._workspace
+
+    def _grad_targets(self, *params):
+        """Where the kernels accumulate the gradients of `params`, and a function to call after them.
+
+        fp32 gradient storage: the storage itself.  Gradient stored as bf16 bit patterns (uint16 storage,
+        the reference's grad_dtype="bf16", runtime.py:185-202): a zeroed fp32 staging area; the returned
+        function then adds it into the stored values with one rounding, the reference's
+        fp32_to_bf16(accumulate) step after a gradient GEMM (backend.py:3298, :4743)."""
+        addrs, staged, off = [], [], 0
+        for t in params:
+            if t is None or not t.requires_grad or t.grad is None:
+                addrs.append(0)
+            elif np.dtype(t.grad.storage.dtype) != np.dtype(np.uint16):
+                addrs.append(_addr(t.grad))
+            else:
+                n = int(prod(t.shape))
+                staged.append((len(addrs), off, n))
+                addrs.append(None)
+                off += (n * 4 + 255) // 256 * 256
+        if not staged:
+            return addrs, lambda: None
+        stage = self._grad_stage
+        if stage is None or stage.nbytes < off:
+            if stage is not None:
+                self._allocator.free(stage)
+            stage = self._grad_stage = self._allocator.alloc((off,), np.uint8)
+        base = address_of(stage)
+        self._context.fill_f32(base, 0.0, off // 4)
+        for i, o, _n in staged:
+            addrs[i] = base + o
+
+        def flush():
+            for i, o, n in staged:
+                self._context.f32_to_bf16(base + o, _addr(params[i].grad), n, accumulate=True)
+
+        return addrs, flush
 
     def _slot(self, scratch, name, nbytes):
         """Address and size of scratch[name] if the runtime planned it, else of the workspace."""
@@ -268,10 +307,10 @@ class CudaBackend:
         need = self._context.norm_partials_bytes(c)
         part, part_bytes = self._slot(scratch, "partials", need)
         dx = _addr(x.grad) if x.requires_grad else 0
-        dgamma = _addr(gamma.grad) if gamma.requires_grad else 0
-        dbeta = _addr(beta.grad) if beta.requires_grad else 0
+        (dgamma, dbeta), flush = self._grad_targets(gamma, beta)
         self._context.layernorm_backward(_addr(out.grad), _addr(x), _addr(gamma), dx, dx, dgamma, dbeta, part,
                                          part_bytes, n, c, op.eps)
+        flush()
 
     # ------------------------------------------------------------------ GELU
     def _gelu_forward(self, inputs, outputs, scratch=None):
@@ -302,7 +341,10 @@ class CudaBackend:
         n = int(prod(ids.shape))
         need = self._context.scatter_add_scratch_bytes(n, c, v)
         sc, sc_bytes = self._slot(scratch, "scatter", need)
-        self._context.gather_backward(_addr(ids), _addr(out.grad), _addr(table.grad), sc, sc_bytes, n, c, v)
+        if np.dtype(table.grad.storage.dtype) == np.dtype(np.uint16):  # backend.py:2807-2812
+            self._context.gather_backward_bf16(_addr(ids), _addr(out.grad), _addr(table.grad), sc, sc_bytes, n, c, v)
+        else:
+            self._context.gather_backward(_addr(ids), _addr(out.grad), _addr(table.grad), sc, sc_bytes, n, c, v)
 
     # ------------------------------------------------------------------ fused linear + CE
     def _flce_desc(self, n, c, v):
@@ -346,9 +388,10 @@ class CudaBackend:
         if lse is None:
             raise RuntimeError("FusedLinearCrossEntropy backward called before forward")
         dx = _addr(x.grad) if x.requires_grad else 0
-        dw = _addr(w.grad) if w.requires_grad else 0
+        (dw,), flush = self._grad_targets(w)
         self._context.flce_backward(desc, _addr(x), _addr(w), _addr(targets), _addr(row_scale), _addr(out.grad),
                                     address_of(lse), dx, dw, sc, sc_bytes)
+        flush()
 
     # ------------------------------------------------------------------ linear + bias + residual
     def _linear_precision(self):
@@ -380,11 +423,12 @@ class CudaBackend:
         c = w.shape[1]
         prec = self._linear_precision()
         sc, sc_bytes = self._slot(scratch, "linear_add", self._context.linear_add_scratch_bytes(n, k, c, prec))
+        (dw, db), flush = self._grad_targets(w, b)
         self._context.linear_add_backward(_addr(out.grad), _addr(act), _addr(w),
                                           _addr(x.grad) if x.requires_grad else 0,
                                           _addr(act.grad) if act.requires_grad else 0,
-                                          _addr(w.grad) if w.requires_grad else 0,
-                                          _addr(b.grad) if b.requires_grad else 0, n, k, c, prec, sc, sc_bytes)
+                                          dw, db, n, k, c, prec, sc, sc_bytes)
+        flush()
 
     # ------------------------------------------------------------------ RMSNorm + linear + CE
     def _rms_flce_layout(self, n, c, v):
@@ -429,13 +473,14 @@ class CudaBackend:
         need_dz = x.requires_grad or gamma.requires_grad
         if need_dz:
             self._context.fill_f32(dz, 0.0, n * c)
+        (dw, dg), flush = self._grad_targets(w, gamma)
         self._context.flce_backward(desc, z, _addr(w), _addr(targets), _addr(row_scale), _addr(out.grad),
-                                    address_of(lse), dz if need_dz else 0, _addr(w.grad) if w.requires_grad else 0,
+                                    address_of(lse), dz if need_dz else 0, dw,
                                     base + 2 * z_bytes + part_bytes, flce_bytes)
         if need_dz:
             dx = _addr(x.grad) if x.requires_grad else 0
-            dg = _addr(gamma.grad) if gamma.requires_grad else 0
             self._context.rmsnorm_backward(dz, _addr(x), _addr(gamma), dx, dx, dg, part, part_bytes, n, c, eps)
+        flush()
 
     # ------------------------------------------------------------------ stage kernels without a reference op
     # RMSNorm, SwiGLU and RoPE are stages inside the reference's fused ops (backend.py:1097-1126,

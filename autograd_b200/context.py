@@ -191,6 +191,17 @@ class CudaContext:
         self._check(lib.ag_gather_backward(self._h, _p(ids), _p(dout), _p(dtable), _p(scratch), int(scratch_bytes),
                                            int(n_ids), int(C_), int(V_)))
 
+    def gather_backward_bf16(self, ids, dout, dtable_bits, scratch, scratch_bytes, n_ids, C_, V_):
+        """Table gradient kept as bf16 bit patterns: row = bf16(float(row) + fp32 sum of its dout rows)."""
+        self._check(lib.ag_gather_backward_bf16(self._h, _p(ids), _p(dout), _p(dtable_bits), _p(scratch),
+                                                int(scratch_bytes), int(n_ids), int(C_), int(V_)))
+
+    def f32_to_bf16(self, src, dst_bits, n, accumulate=False):
+        self._check(lib.ag_f32_to_bf16(self._h, _p(src), _p(dst_bits), int(n), 1 if accumulate else 0))
+
+    def bf16_to_f32(self, src_bits, dst, n):
+        self._check(lib.ag_bf16_to_f32(self._h, _p(src_bits), _p(dst), int(n)))
+
     @staticmethod
     def flce_desc(N_, C_, V_, vocab_chunk=4096, precision=N.AG_CE_3XTF32, reduction=N.AG_CE_MEAN_ALL_ROWS,
                   ignore_mode=N.AG_CE_IGNORE_MASKED):
@@ -222,6 +233,7 @@ class CudaContext:
                                                int(N_), int(K_), int(C_), int(precision), _p(scratch),
                                                int(scratch_bytes)))
 
-    def adamw_step(self, p, g, m, v, n, lr, lr_t, b1, b2, eps, weight_decay, grad_scale=1.0):
-        self._check(lib.ag_adamw_step(self._h, _p(p), _p(g), _p(m), _p(v), int(n), float(lr), float(lr_t), float(b1),
-                                      float(b2), float(eps), float(weight_decay), float(grad_scale)))
+    def adamw_step(self, p, g, m, v, n, lr, lr_t, b1, b2, eps, weight_decay, grad_scale=1.0, grad_bf16=False):
+        fn = lib.ag_adamw_step_bf16grad if grad_bf16 else lib.ag_adamw_step
+        self._check(fn(self._h, _p(p), _p(g), _p(m), _p(v), int(n), float(lr), float(lr_t), float(b1), float(b2),
+                       float(eps), float(weight_decay), float(grad_scale)))

@@ -362,9 +362,12 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_backward_scalar_kernel(T* _
 }
 
 // ---------------------------------------------------------------------------- AdamW
+// GT = float, or uint16_t for gradients stored as bf16 bit patterns (the reference's
+// grad_dtype="bf16" storage, backend.py:5128-5140: the kernel widens g before anything else).
+template <typename GT>
 struct AdamW {
   float* p;
-  const float* g;
+  const GT* g;
   float* m;
   float* v;
   float lr_wd, lr_t, b1, b2, one_minus_b1, one_minus_b2, eps, grad_scale;
@@ -384,7 +387,13 @@ struct AdamW {
     for (int u = 0; u < U; ++u) {
       const int64_t o = (i + u * stride) * 4;
       Pack<float>::load(p + o, pv[u]);
-      Pack<float>::load_stream(g + o, gv[u]);
+      if constexpr (sizeof(GT) == 4) {
+        Pack<float>::load_stream(reinterpret_cast<const float*>(g) + o, gv[u]);
+      } else {
+        const uint2 w = __ldcs(reinterpret_cast<const uint2*>(g + o));
+        gv[u][0] = __uint_as_float(w.x << 16); gv[u][1] = __uint_as_float(w.x & 0xffff0000u);
+        gv[u][2] = __uint_as_float(w.y << 16); gv[u][3] = __uint_as_float(w.y & 0xffff0000u);
+      }
       Pack<float>::load(m + o, mv[u]);
       Pack<float>::load(v + o, vv[u]);
     }
@@ -398,10 +407,93 @@ struct AdamW {
       Pack<float>::store(v + o, vv[u]);
     }
   }
-  __device__ __forceinline__ void scalar(int64_t j) { one(p[j], g[j], m[j], v[j]); }
+  __device__ __forceinline__ void scalar(int64_t j) {
+    float gg;
+    if constexpr (sizeof(GT) == 4) gg = g[j];
+    else gg = __uint_as_float((uint32_t)g[j] << 16);
+    one(p[j], gg, m[j], v[j]);
+  }
 };
 
-__global__ void __launch_bounds__(EW_THREADS) adamw_kernel(AdamW f, int64_t n, int early) { ew_drive<4>(n, f, early); }
+template <typename GT>
+__global__ void __launch_bounds__(EW_THREADS) adamw_kernel(AdamW<GT> f, int64_t n, int early) { ew_drive<4>(n, f, early); }
+
+// ------------------------------------------------------- fp32 <-> bf16 gradient storage
+// Round to nearest, ties to even; Inf kept, NaN stays NaN after the cut (utils.py:20-27,
+// metal_ops.metal:12010-12041).
+__device__ __forceinline__ uint32_t bf16_bits_rne(float value) {
+  const uint32_t bits = __float_as_uint(value);
+  if ((bits & 0x7f800000u) == 0x7f800000u) return ((bits >> 16) | ((bits & 0x007fffffu) ? 0x0040u : 0u)) & 0xffffu;
+  return ((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16) & 0xffffu;
+}
+
+// dst = bf16(src), or bf16(src + float(dst)) when accumulate: 8 elements per packet (two 16-byte loads,
+// one 16-byte store)
+struct F32ToBf16 {
+  const float* src;
+  uint16_t* dst;
+  bool accumulate;
+  template <int U>
+  __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
+    float a[U][8];
+    uint4 old[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t o = (i + u * stride) * 8;
+      const float4 x = __ldcs(reinterpret_cast<const float4*>(src + o));
+      const float4 y = __ldcs(reinterpret_cast<const float4*>(src + o + 4));
+      a[u][0] = x.x; a[u][1] = x.y; a[u][2] = x.z; a[u][3] = x.w;
+      a[u][4] = y.x; a[u][5] = y.y; a[u][6] = y.z; a[u][7] = y.w;
+      if (accumulate) old[u] = *reinterpret_cast<const uint4*>(dst + o);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t o = (i + u * stride) * 8;
+      if (accumulate) {
+        const uint32_t w[4] = {old[u].x, old[u].y, old[u].z, old[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          a[u][2 * e] += __uint_as_float(w[e] << 16);
+          a[u][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) w[e] = bf16_bits_rne(a[u][2 * e]) | (bf16_bits_rne(a[u][2 * e + 1]) << 16);
+      *reinterpret_cast<uint4*>(dst + o) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  __device__ __forceinline__ void scalar(int64_t j) {
+    float v = src[j];
+    if (accumulate) v += __uint_as_float((uint32_t)dst[j] << 16);
+    dst[j] = (uint16_t)bf16_bits_rne(v);
+  }
+};
+
+__global__ void __launch_bounds__(EW_THREADS) f32_to_bf16_kernel(F32ToBf16 f, int64_t n, int early) { ew_drive<8>(n, f, early); }
+
+struct Bf16ToF32 {
+  const uint16_t* src;
+  float* dst;
+  template <int U>
+  __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
+    uint4 t[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) t[u] = __ldcs(reinterpret_cast<const uint4*>(src + (i + u * stride) * 8));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t o = (i + u * stride) * 8;
+      const uint32_t w[4] = {t[u].x, t[u].y, t[u].z, t[u].w};
+      *reinterpret_cast<float4*>(dst + o) = make_float4(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xffff0000u),
+                                                         __uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xffff0000u));
+      *reinterpret_cast<float4*>(dst + o + 4) = make_float4(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xffff0000u),
+                                                             __uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xffff0000u));
+    }
+  }
+  __device__ __forceinline__ void scalar(int64_t j) { dst[j] = __uint_as_float((uint32_t)src[j] << 16); }
+};
+
+__global__ void __launch_bounds__(EW_THREADS) bf16_to_f32_kernel(Bf16ToF32 f, int64_t n, int early) { ew_drive<8>(n, f, early); }
 
 template <typename... P>
 bool all_aligned16(P... p) {
@@ -510,14 +602,11 @@ extern "C" int ag_swiglu_backward(ag_ctx* ctx, void* gu, const void* dhidden, in
                          : swiglu_backward_t<__nv_bfloat16>(ctx, gu, dhidden, N, I);
 }
 
-extern "C" int ag_adamw_step(ag_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, double lr,
-                             double lr_t, double b1, double b2, double eps, double weight_decay,
-                             double grad_scale) {
-  if (!ctx) return AG_ERR_INVALID;
-  if (n == 0) return AG_OK;
-  AG_REQUIRE(ctx, p && g && m && v && n > 0, "ag_adamw_step: null pointer or negative n");
-  AG_REQUIRE(ctx, all_aligned16(p, g, m, v), "ag_adamw_step: pointers must be 16-byte aligned");
-  AdamW f;
+namespace {
+template <typename GT>
+int adamw_launch(ag_ctx* ctx, float* p, const GT* g, float* m, float* v, int64_t n, double lr, double lr_t, double b1,
+                 double b2, double eps, double weight_decay, double grad_scale) {
+  AdamW<GT> f;
   f.p = p; f.g = g; f.m = m; f.v = v;
   // the reference multiplies fp32 arrays by python doubles: the scalar expression is
   // evaluated in double, then rounded once to fp32 (backend.py:2022, :2026, :2031)
@@ -527,9 +616,50 @@ extern "C" int ag_adamw_step(ag_ctx* ctx, float* p, const float* g, float* m, fl
   f.one_minus_b2 = (float)(1.0 - b2);
   f.eps = (float)eps; f.grad_scale = (float)grad_scale;
   f.decay = weight_decay > 0.0;
-  {
-    const int grid = ew_grid(ctx, n / 4, 4);
-    AG_LAUNCH_PDL(ctx, "adamw_kernel", adamw_kernel, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
-  }
+  const int grid = ew_grid(ctx, n / 4, 4);
+  AG_LAUNCH_PDL(ctx, "adamw_kernel", adamw_kernel<GT>, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
+  return AG_OK;
+}
+}  // namespace
+
+extern "C" int ag_adamw_step(ag_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, double lr,
+                             double lr_t, double b1, double b2, double eps, double weight_decay,
+                             double grad_scale) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, p && g && m && v && n > 0, "ag_adamw_step: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(p, g, m, v), "ag_adamw_step: pointers must be 16-byte aligned");
+  return adamw_launch<float>(ctx, p, g, m, v, n, lr, lr_t, b1, b2, eps, weight_decay, grad_scale);
+}
+
+extern "C" int ag_adamw_step_bf16grad(ag_ctx* ctx, float* p, const uint16_t* g, float* m, float* v, int64_t n,
+                                      double lr, double lr_t, double b1, double b2, double eps,
+                                      double weight_decay, double grad_scale) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, p && g && m && v && n > 0, "ag_adamw_step_bf16grad: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(p, g, m, v), "ag_adamw_step_bf16grad: pointers must be 16-byte aligned");
+  return adamw_launch<uint16_t>(ctx, p, g, m, v, n, lr, lr_t, b1, b2, eps, weight_decay, grad_scale);
+}
+
+extern "C" int ag_f32_to_bf16(ag_ctx* ctx, const float* src, uint16_t* dst, int64_t n, int accumulate) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, src && dst && n > 0, "ag_f32_to_bf16: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(src, dst), "ag_f32_to_bf16: pointers must be 16-byte aligned");
+  F32ToBf16 f{src, dst, accumulate != 0};
+  const int grid = ew_grid(ctx, n / 8, 0);
+  AG_LAUNCH_PDL(ctx, "f32_to_bf16_kernel", f32_to_bf16_kernel, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
+  return AG_OK;
+}
+
+extern "C" int ag_bf16_to_f32(ag_ctx* ctx, const uint16_t* src, float* dst, int64_t n) {
+  if (!ctx) return AG_ERR_INVALID;
+  if (n == 0) return AG_OK;
+  AG_REQUIRE(ctx, src && dst && n > 0, "ag_bf16_to_f32: null pointer or negative n");
+  AG_REQUIRE(ctx, all_aligned16(src, dst), "ag_bf16_to_f32: pointers must be 16-byte aligned");
+  Bf16ToF32 f{src, dst};
+  const int grid = ew_grid(ctx, n / 8, 0);
+  AG_LAUNCH_PDL(ctx, "bf16_to_f32_kernel", bf16_to_f32_kernel, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
   return AG_OK;
 }

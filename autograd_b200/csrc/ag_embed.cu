@@ -198,6 +198,31 @@ __device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
   return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
 }
 
+// Table-gradient rows are fp32, or bf16 bit patterns (TT = uint16_t: the reference's bf16
+// parameter-gradient storage, metal_ops.metal:12395-12446: the sum of a row's contributions is
+// formed in fp32 from zero, in position order, and the row becomes bf16(old + sum), rounded once,
+// to nearest even).
+__device__ __forceinline__ uint32_t seg_bf16_rne(float value) {
+  const uint32_t bits = __float_as_uint(value);
+  if ((bits & 0x7f800000u) == 0x7f800000u) return ((bits >> 16) | ((bits & 0x007fffffu) ? 0x0040u : 0u)) & 0xffffu;
+  return ((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16) & 0xffffu;
+}
+__device__ __forceinline__ float4 seg_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 seg_load4(const uint16_t* p) {
+  const uint2 w = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16),
+                     __uint_as_float(w.y & 0xffff0000u));
+}
+__device__ __forceinline__ void seg_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void seg_store4(uint16_t* p, float4 v) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(seg_bf16_rne(v.x) | (seg_bf16_rne(v.y) << 16),
+                                            seg_bf16_rne(v.z) | (seg_bf16_rne(v.w) << 16));
+}
+__device__ __forceinline__ float seg_load1(const float* p) { return *p; }
+__device__ __forceinline__ float seg_load1(const uint16_t* p) { return __uint_as_float((uint32_t)*p << 16); }
+__device__ __forceinline__ void seg_store1(float* p, float v) { *p = v; }
+__device__ __forceinline__ void seg_store1(uint16_t* p, float v) { *p = (uint16_t)seg_bf16_rne(v); }
+
 // grid = (n_groups, ceil(C/512)).  VEC: C % 4 == 0 and pointers 16-byte aligned.
 // partials: [n_groups][2][C] floats; slot 0 = the group's first run when it continues from
 // the previous group or is the cut part of a longer segment, slot 1 = its last run when
@@ -206,11 +231,12 @@ __device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
 constexpr uint32_t RUN_BEGIN = 1u, RUN_END = 2u, RUN_COMPLETE = 4u, RUN_SLOT1 = 8u, RUN_VALID = 16u;
 constexpr int SEG_BATCH = 8;  // sorted entries whose rows are requested together
 
-template <bool VEC>
+template <bool VEC, typename TT>
 __global__ void __launch_bounds__(SEG_THREADS)
 scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ pos,
-                      const float* __restrict__ dout, float* dtable, float* __restrict__ partials, int64_t n, int C,
+                      const float* __restrict__ dout, TT* dtable, float* __restrict__ partials, int64_t n, int C,
                       int V) {
+  constexpr bool BF = sizeof(TT) == 2;  // rounded storage: sum from zero, add the old row last
   ag_pdl_wait();
   __shared__ uint32_t s_key[SEG_GROUP + 2];  // [0] = key before the group, [1..G] group, [G+1] = key after
   __shared__ uint32_t s_pos[SEG_GROUP];
@@ -251,6 +277,7 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
     // requested together; the adds then run in sorted (= position) order, each complete run starting
     // from its dtable row: the same sequence of additions as an unbuffered add-at.
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j0 = 0; j0 < cnt; j0 += SEG_BATCH) {
       float4 v[SEG_BATCH], d[SEG_BATCH];
 #pragma unroll
@@ -262,7 +289,7 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
           if (info & RUN_VALID) {
             v[u] = __ldcs(reinterpret_cast<const float4*>(dout + (int64_t)s_pos[j] * C + col));
             if ((info & (RUN_BEGIN | RUN_COMPLETE)) == (RUN_BEGIN | RUN_COMPLETE))
-              d[u] = *reinterpret_cast<const float4*>(dtable + (int64_t)s_key[j + 1] * C + col);
+              d[u] = seg_load4(dtable + (int64_t)s_key[j + 1] * C + col);
           }
         }
       }
@@ -272,13 +299,16 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
         if (j < cnt) {
           const uint32_t info = s_info[j];
           if (info & RUN_VALID) {
-            if (info & RUN_BEGIN) acc = d[u];  // zero for a cut run
+            if (info & RUN_BEGIN) {
+              if (BF) { old = d[u]; acc = make_float4(0.f, 0.f, 0.f, 0.f); }
+              else acc = d[u];  // zero for a cut run
+            }
             acc = f4_add(acc, v[u]);
             if (info & RUN_END) {
-              float* dst = (info & RUN_COMPLETE)
-                               ? dtable + (int64_t)s_key[j + 1] * C
-                               : partials + ((int64_t)blockIdx.x * 2 + ((info & RUN_SLOT1) ? 1 : 0)) * C;
-              *reinterpret_cast<float4*>(dst + col) = acc;
+              if (info & RUN_COMPLETE)
+                seg_store4(dtable + (int64_t)s_key[j + 1] * C + col, BF ? f4_add(old, acc) : acc);
+              else
+                *reinterpret_cast<float4*>(partials + ((int64_t)blockIdx.x * 2 + ((info & RUN_SLOT1) ? 1 : 0)) * C + col) = acc;
             }
           }
         }
@@ -292,12 +322,13 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
       int end = j;
       while (!(s_info[end] & RUN_END)) ++end;
       const bool complete = (info & RUN_COMPLETE) != 0;
-      float* drow = dtable + (int64_t)s_key[j + 1] * C;
+      TT* drow = dtable + (int64_t)s_key[j + 1] * C;
       float* prow = partials + ((int64_t)blockIdx.x * 2 + ((info & RUN_SLOT1) ? 1 : 0)) * C;
       for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
-        float acc = complete ? drow[c] : 0.0f;
+        float acc = (complete && !BF) ? seg_load1(drow + c) : 0.0f;
         for (int e = j; e <= end; ++e) acc += dout[(int64_t)s_pos[e] * C + c];
-        (complete ? drow : prow)[c] = acc;
+        if (complete) seg_store1(drow + c, BF ? seg_load1(drow + c) + acc : acc);
+        else prow[c] = acc;
       }
     }
   }
@@ -348,10 +379,11 @@ segment_heads_kernel(const uint32_t* __restrict__ keys, long long* __restrict__ 
 // slots of the segment's following groups are split into SEG_SPLIT consecutive sub-ranges; thread row
 // y adds its sub-range in group order (8 loads in flight), then row 0 adds
 // dtable row + head partial + sub-sum 0 + ... + sub-sum 3 and writes the dtable row.  Fixed order.
-template <bool VEC>
+template <bool VEC, typename TT>
 __global__ void __launch_bounds__(SEG_THREADS * SEG_SPLIT)
-scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __restrict__ heads, float* dtable,
+scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __restrict__ heads, TT* dtable,
                        const float* __restrict__ partials, int64_t n, int C) {
+  constexpr bool BF = sizeof(TT) == 2;
   ag_pdl_wait();
   const int64_t grp = blockIdx.x;
   const long long rec = heads[grp];
@@ -362,7 +394,7 @@ scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __res
   const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
   const uint32_t key = keys[g0 + cnt - 1];
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
-  float* drow = dtable + (int64_t)key * C;
+  TT* drow = dtable + (int64_t)key * C;
   if (VEC) {
     __shared__ float4 s_sub[SEG_SPLIT][SEG_THREADS];
     const int y = threadIdx.y;
@@ -384,18 +416,20 @@ scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __res
     s_sub[y][threadIdx.x] = sub;
     __syncthreads();
     if (y == 0 && col < C) {
-      float4 acc = *reinterpret_cast<const float4*>(drow + col);
-      acc = f4_add(acc, *reinterpret_cast<const float4*>(partials + (grp * 2 + head_slot) * C + col));
+      const float4 old = seg_load4(drow + col);
+      const float4 head = *reinterpret_cast<const float4*>(partials + (grp * 2 + head_slot) * C + col);
+      float4 acc = BF ? head : f4_add(old, head);
 #pragma unroll
       for (int q = 0; q < SEG_SPLIT; ++q) acc = f4_add(acc, s_sub[q][threadIdx.x]);
-      *reinterpret_cast<float4*>(drow + col) = acc;
+      seg_store4(drow + col, BF ? f4_add(old, acc) : acc);
     }
   } else {
     if (threadIdx.y != 0) return;
     for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
-      float acc = drow[c] + partials[(grp * 2 + head_slot) * C + c];
+      const float old = seg_load1(drow + c);
+      float acc = BF ? partials[(grp * 2 + head_slot) * C + c] : old + partials[(grp * 2 + head_slot) * C + c];
       for (int64_t g = grp + 1; g <= g_end; ++g) acc += partials[(g * 2 + 0) * C + c];
-      drow[c] = acc;
+      seg_store1(drow + c, BF ? old + acc : acc);
     }
   }
 }
@@ -457,8 +491,10 @@ extern "C" size_t ag_scatter_add_scratch_bytes(int64_t n_ids, int C, int V) {
   return scatter_plan(n_ids, C).total;
 }
 
-extern "C" int ag_gather_backward(ag_ctx* ctx, const int32_t* ids, const float* dout, float* dtable, void* scratch,
-                                  size_t scratch_bytes, int64_t n_ids, int C, int V) {
+namespace {
+template <typename TT>
+int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dtable, void* scratch,
+                      size_t scratch_bytes, int64_t n_ids, int C, int V) {
   if (!ctx) return AG_ERR_INVALID;
   if (n_ids == 0) return AG_OK;
   AG_REQUIRE(ctx, ids && dout && dtable, "ag_gather_backward: null pointer");
@@ -494,25 +530,41 @@ extern "C" int ag_gather_backward(ag_ctx* ctx, const int32_t* ids, const float* 
                   (const uint32_t*)vals[cur], keys[cur ^ 1], vals[cur ^ 1], (const uint32_t*)hist, n_ids, shift, n_tiles);
     cur ^= 1;
   }
+  // 4-element packets of a table row: 16 bytes in fp32, 8 bytes in bf16 storage
   const bool vec = (C % 4 == 0) && ag_aligned16(dout) && ag_aligned16(dtable);
   dim3 grid((unsigned)p.n_groups, (unsigned)((C + SEG_COLS - 1) / SEG_COLS));
+  auto groups_vec = scatter_groups_kernel<true, TT>;
+  auto combine_vec = scatter_combine_kernel<true, TT>;
+  auto groups_scalar = scatter_groups_kernel<false, TT>;
+  auto combine_scalar = scatter_combine_kernel<false, TT>;
   if (vec) {
-    AG_LAUNCH_PDL(ctx, "scatter_groups_kernel", scatter_groups_kernel<true>, grid, SEG_THREADS, 0,
+    AG_LAUNCH_PDL(ctx, "scatter_groups_kernel", groups_vec, grid, SEG_THREADS, 0,
                   (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], dout, dtable, partials, n_ids, C, V);
     AG_LAUNCH_PDL(ctx, "segment_heads_kernel", segment_heads_kernel, (unsigned)((p.n_groups + 3) / 4), 128, 0,
                   (const uint32_t*)keys[cur], heads, n_ids, (int)p.n_groups, V);
-    AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", scatter_combine_kernel<true>, grid, dim3(SEG_THREADS, SEG_SPLIT), 0,
+    AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", combine_vec, grid, dim3(SEG_THREADS, SEG_SPLIT), 0,
                   (const uint32_t*)keys[cur], (const long long*)heads, dtable, (const float*)partials, n_ids, C);
   } else {
-    scatter_groups_kernel<false><<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials,
+    groups_scalar<<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials,
                                                                          n_ids, C, V);
     AG_LAUNCHED(ctx, "scatter_groups_kernel");
     segment_heads_kernel<<<(unsigned)((p.n_groups + 3) / 4), 128, 0, ctx->stream>>>(keys[cur], heads, n_ids,
                                                                                      (int)p.n_groups, V);
     AG_LAUNCHED(ctx, "segment_heads_kernel");
-    scatter_combine_kernel<false><<<grid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, dtable,
+    combine_scalar<<<grid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, dtable,
                                                                                            partials, n_ids, C);
     AG_LAUNCHED(ctx, "scatter_combine_kernel");
   }
   return AG_OK;
+}
+}  // namespace
+
+extern "C" int ag_gather_backward(ag_ctx* ctx, const int32_t* ids, const float* dout, float* dtable, void* scratch,
+                                  size_t scratch_bytes, int64_t n_ids, int C, int V) {
+  return gather_backward_t<float>(ctx, ids, dout, dtable, scratch, scratch_bytes, n_ids, C, V);
+}
+
+extern "C" int ag_gather_backward_bf16(ag_ctx* ctx, const int32_t* ids, const float* dout, uint16_t* dtable,
+                                       void* scratch, size_t scratch_bytes, int64_t n_ids, int C, int V) {
+  return gather_backward_t<uint16_t>(ctx, ids, dout, dtable, scratch, scratch_bytes, n_ids, C, V);
 }

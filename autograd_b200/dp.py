@@ -37,13 +37,21 @@ class GradAllReducer:
     current stream of the backend (NCCL) and returns after enqueueing; gloo is synchronous.
     """
 
-    def __init__(self, buckets, group=None):
+    def __init__(self, buckets, group=None, wires=None):
+        """`wires`: optional list, one entry per bucket, each None or a `Bf16Wire`: that bucket then
+        crosses the links as bf16 (half the bytes): packed before the allreduce, summed in bf16,
+        widened back into the fp32 bucket afterwards.  The reference's counterpart is keeping the
+        parameter gradients themselves as bf16 (grad_dtype="bf16", runtime.py:185-202)."""
         import torch.distributed as dist
         self._dist = dist
         self.group = group
         self.buckets = list(buckets)
+        self.wires = list(wires) if wires is not None else [None] * len(self.buckets)
+        if len(self.wires) != len(self.buckets):
+            raise ValueError("one wire entry (or None) per bucket")
         self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.bytes_per_step = sum(int(b.numel()) * b.element_size() for b in self.buckets)
+        self.bytes_per_step = sum(int(t.numel()) * t.element_size()
+                                  for t in (w.tensor if w is not None else b for b, w in zip(self.buckets, self.wires)))
 
     @property
     def grad_scale(self) -> float:
@@ -54,8 +62,13 @@ class GradAllReducer:
     def reduce(self):
         if self.world_size == 1:
             return
-        for b in self.buckets:
-            self._dist.all_reduce(b, op=self._dist.ReduceOp.SUM, group=self.group)
+        for b, w in zip(self.buckets, self.wires):
+            if w is None:
+                self._dist.all_reduce(b, op=self._dist.ReduceOp.SUM, group=self.group)
+            else:
+                w.pack()
+                self._dist.all_reduce(w.tensor, op=self._dist.ReduceOp.SUM, group=self.group)
+                w.unpack()
 
     def mean_loss(self, loss_tensor):
         """Global mean of the per-rank mean losses (equal token counts per rank)."""
@@ -64,6 +77,36 @@ class GradAllReducer:
         self._dist.all_reduce(loss_tensor, op=self._dist.ReduceOp.SUM, group=self.group)
         loss_tensor /= self.world_size
         return loss_tensor
+
+
+class Bf16Wire:
+    """bf16 transport form of one fp32 gradient bucket.
+
+    `tensor` is what the allreduce sums (dtype torch.bfloat16); `pack()` rounds the fp32 bucket into
+    it (to nearest even, utils.py:20-27) and `unpack()` widens the summed values back.  On a GPU
+    both are this package's conversion kernels on the backend's stream (`for_device`); `for_tensors`
+    is the host form with torch ops, for CPU process groups."""
+
+    def __init__(self, tensor, pack, unpack):
+        self.tensor, self.pack, self.unpack = tensor, pack, unpack
+
+    @classmethod
+    def for_device(cls, ctx, allocator, address: int, n_floats: int, device_index: int = 0):
+        import torch
+        bits = allocator.alloc((int(n_floats),), np.uint16)
+        bits_addr = bits.ptr.address
+        t = torch.as_tensor(DeviceArrayView(bits_addr, n_floats, "<i2"),
+                            device=torch.device("cuda", device_index)).view(torch.bfloat16)
+        wire = cls(t, lambda: ctx.f32_to_bf16(address, bits_addr, n_floats, accumulate=False),
+                   lambda: ctx.bf16_to_f32(bits_addr, address, n_floats))
+        wire.storage = bits  # keeps the device buffer alive
+        return wire
+
+    @classmethod
+    def for_tensors(cls, bucket):
+        import torch
+        t = torch.empty(bucket.shape, dtype=torch.bfloat16, device=bucket.device)
+        return cls(t, lambda: t.copy_(bucket), lambda: bucket.copy_(t))
 
 
 def shard_rows(n_rows: int, rank: int, world_size: int):

@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--ce-precision", default="3xtf32", choices=["fp32", "3xtf32", "bf16", "bf16x3"])
     ap.add_argument("--no-bf16-mode", action="store_true", help="skip the extra timing of the bf16 CE mode")
+    ap.add_argument("--grad-wire", default="fp32", choices=["fp32", "bf16"],
+                    help="N>1: form in which the tied table gradient crosses the links (bf16 = half the bytes)")
     # reduced shapes for profiler captures and tests; the defaults are the benchmark workload
     ap.add_argument("--layers", type=int, default=20)
     ap.add_argument("--batch", type=int, default=16)
@@ -251,7 +253,10 @@ def run_b200(a):
     step = FusedLayerStep(ctx, alloc, be, cfg, seed=1238 + rank, fill_normal=fill_normal)
     Nn = cfg.tokens
     buckets = [dp.as_torch(addr, n, local) for addr, n in step.grad_buckets()]
-    reducer = dp.GradAllReducer(buckets) if world > 1 else None
+    wires = None
+    if world > 1 and a.grad_wire == "bf16":  # the small dgamma/dbeta bucket stays fp32
+        wires = [None, dp.Bf16Wire.for_device(ctx, alloc, *step.grad_buckets()[1], local)]
+    reducer = dp.GradAllReducer(buckets, wires=wires) if world > 1 else None
     loss_t = dp.as_torch(step.loss, 1, local)
     if reducer is not None:
         ctx.fill_f32(step.dloss, reducer.grad_scale, 1)
@@ -451,7 +456,8 @@ def run_b200(a):
                        "vocab_chunk": cfg.ce_vocab_chunk, "parallelism": f"dp{world} token-row sharded",
                        "l2": "every streamed buffer is larger than the L2 cache; no flush needed",
                        "device_bytes": step.device_bytes,
-                       "allreduce_bytes_per_step": reducer.bytes_per_step if reducer else 0},
+                       "allreduce_bytes_per_step": reducer.bytes_per_step if reducer else 0,
+                       "grad_wire": a.grad_wire if reducer else None},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * Nn * 4, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / a.steps},
             "gpu_launches": int(launches),
@@ -682,6 +688,38 @@ def run_kernels(a):
         ms_ = [dev(n, std=0.0) for _ in range(n_sets)]; vs = [dev(n, std=0.0) for _ in range(n_sets)]
         ms = time_it(lambda i: ctx.adamw_step(ps[i], gs[i], ms_[i], vs[i], n, 1e-3, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1.0), n_sets)
         emit("next", "adamw_step 32768x1280 parameters (read p,g,m,v; write p,m,v)", ms, n, alg_bytes=7 * n * f4)
+        free_all()
+        # ---- parameter gradients stored as bf16: conversion (with accumulate), AdamW on bf16 gradients,
+        # scatter-add into a bf16 table gradient
+        n_sets = sets_for(3 * n * f4)
+        src = [dev(n, std=0.01) for _ in range(n_sets)]; bits = [dev(n, np.uint16, std=0.01) for _ in range(n_sets)]
+        ms = time_it(lambda i: ctx.f32_to_bf16(src[i], bits[i], n, accumulate=False), n_sets)
+        emit("next", "f32_to_bf16 32768x1280 (read fp32, write bf16)", ms, n, alg_bytes=6 * n)
+        ms = time_it(lambda i: ctx.f32_to_bf16(src[i], bits[i], n, accumulate=True), n_sets)
+        emit("next", "f32_to_bf16 accumulate 32768x1280 (read fp32 + bf16, write bf16)", ms, n, alg_bytes=8 * n)
+        ms = time_it(lambda i: ctx.bf16_to_f32(bits[i], src[i], n), n_sets)
+        emit("next", "bf16_to_f32 32768x1280", ms, n, alg_bytes=6 * n)
+        free_all()
+        n_sets = sets_for(4 * n * f4)
+        ps = [dev(n, std=0.02) for _ in range(n_sets)]; gb = [dev(n, np.uint16, std=0.01) for _ in range(n_sets)]
+        ms_ = [dev(n, std=0.0) for _ in range(n_sets)]; vs = [dev(n, std=0.0) for _ in range(n_sets)]
+        ms = time_it(lambda i: ctx.adamw_step(ps[i], gb[i], ms_[i], vs[i], n, 1e-3, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1.0,
+                                              grad_bf16=True), n_sets)
+        emit("next", "adamw_step, bf16 gradients, 32768x1280 parameters", ms, n, alg_bytes=26 * n)
+        free_all()
+        V, C, nid = 151936, 1536, 65536
+        rng = np.random.default_rng(1237)
+        p = 1.0 / np.arange(1, V + 1) ** 1.1
+        p /= p.sum()
+        ids_ = rng.choice(V, size=nid, p=p).astype(np.int32)
+        uniq = int(np.unique(ids_).size)
+        ids = dev(nid, np.int32, ints=ids_)
+        dtb = dev(V * C, np.uint16, std=0.0)
+        out = [dev(nid * C) for _ in range(2)]
+        sb = ctx.scatter_add_scratch_bytes(nid, C, V); sc = alloc.alloc((sb,), np.uint8); bufs.append(sc)
+        ms = time_it(lambda i: ctx.gather_backward_bf16(ids, out[i], dtb, sc.ptr.address, sb, nid, C, V), 2)
+        emit("next", "scatter_add into a bf16 table gradient, 65536 Zipf ids x 1536", ms, nid,
+             alg_bytes=nid * C * f4 + 2 * uniq * C * 2, extra={"unique_rows": uniq})
         free_all()
 
     sections = {"cfg1": sec_cfg1, "gelu": sec_gelu, "cfg3": sec_cfg3, "cfg4": sec_cfg4, "cfg2": sec_cfg2,

@@ -241,6 +241,28 @@ int ag_adamw_step(ag_ctx* ctx, float* p, const float* g, float* m, float* v, int
                   double lr_t, double b1, double b2, double eps, double weight_decay,
                   double grad_scale);
 
+/* ---- f4 parameter gradients stored as bf16 ------------------------------------------------
+ * The reference keeps the gradient of a parameter whose grad_dtype is "bf16" as bf16 bit
+ * patterns (uint16, runtime.py:185-202) and halves gradient memory and exchange bytes that way.
+ * Rounding everywhere: to nearest, ties to even, Inf kept, NaN kept NaN (utils.py:20-27).
+ *
+ * ag_f32_to_bf16 replaces the `fp32_to_bf16` kernel (metal_ops.metal:12010-12041; call sites
+ * backend.py:3298, :4743): dst = bf16(src), or bf16(src + float(dst)) when accumulate != 0 - how
+ * a gradient computed in fp32 scratch is added into bf16 storage.  ag_bf16_to_f32 widens (exact).
+ * ag_gather_backward_bf16 replaces `gather_backward_bf16_kernel` (metal_ops.metal:12395-12446,
+ * backend.py:2807-2812): per touched table row, the fp32 sum of its dout rows in ascending
+ * position order starting from zero, then row = bf16(float(row) + sum); untouched rows are not
+ * written.  Scratch as for ag_gather_backward.
+ * ag_adamw_step_bf16grad replaces `adamw_step` with its bf16-gradient flag (backend.py:5125-5140):
+ * g is widened to fp32, then the fp32 step. */
+int ag_f32_to_bf16(ag_ctx* ctx, const float* src, uint16_t* dst, int64_t n, int accumulate);
+int ag_bf16_to_f32(ag_ctx* ctx, const uint16_t* src, float* dst, int64_t n);
+int ag_gather_backward_bf16(ag_ctx* ctx, const int32_t* ids, const float* dout, uint16_t* dtable,
+                            void* scratch, size_t scratch_bytes, int64_t n_ids, int C, int V);
+int ag_adamw_step_bf16grad(ag_ctx* ctx, float* p, const uint16_t* g, float* m, float* v, int64_t n,
+                           double lr, double lr_t, double b1, double b2, double eps,
+                           double weight_decay, double grad_scale);
+
 #ifdef __cplusplus
 }
 #endif

@@ -378,3 +378,38 @@ def adamw_step(p, g, m, v, lr, lr_t, b1, b2, eps, wd):
     step = np.multiply(np.divide(m, np.add(np.sqrt(v), eps)), lr_t)
     p = np.subtract(p, step)
     return p.astype(F32), m.astype(F32), v.astype(F32)
+
+
+# --------------------------------------------------------------------------------------
+# f4  parameter gradients stored as bf16 bit patterns (grad_dtype="bf16", runtime.py:185-202).
+# The reference implements these three only as Metal kernels; each is restated here from the
+# kernel text, out of pieces that are pinned on their own (the rounding rule, np.add.at,
+# cpu_adamw_step).
+# --------------------------------------------------------------------------------------
+def f32_to_bf16_store(src, dst_bits, accumulate):
+    """`fp32_to_bf16` (metal_ops.metal:12010-12041): dst = bf16(src [+ float(dst)])."""
+    value = np.ascontiguousarray(src, dtype=F32)
+    if accumulate:
+        value = np.add(value, bf16_bits_to_f32(dst_bits).reshape(value.shape))
+    return f32_to_bf16_bits(value).reshape(value.shape)
+
+
+def gather_backward_bf16(ids, dout, table_bits):
+    """`gather_backward_bf16_kernel` (metal_ops.metal:12395-12446): per token row that occurs in ids,
+    the fp32 sum of its dout rows in ascending position order starting from zero, then
+    row = bf16(float(row) + sum); rows that do not occur are left as they are."""
+    C = table_bits.shape[-1]
+    flat = ids.astype(np.int64).ravel()
+    sums = np.zeros(table_bits.shape, F32)
+    np.add.at(sums, flat, dout.reshape(-1, C))
+    out = np.array(table_bits, dtype=np.uint16, copy=True)
+    touched = np.unique(flat)
+    out[touched] = f32_to_bf16_bits(np.add(bf16_bits_to_f32(table_bits[touched]), sums[touched])).reshape(-1, C)
+    return out
+
+
+def adamw_step_bf16grad(p, g_bits, m, v, lr, lr_t, b1, b2, eps, wd, grad_scale=1.0):
+    """`adamw_step` with its bf16-gradient flag (backend.py:5125-5140): g is widened to fp32 and
+    scaled, then the fp32 step."""
+    g = np.multiply(bf16_bits_to_f32(g_bits).reshape(p.shape), F32(grad_scale))
+    return adamw_step(p, g, m, v, lr, lr_t, b1, b2, eps, wd)

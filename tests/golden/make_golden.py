@@ -411,6 +411,53 @@ def gen_adamw_bf16(ref, out):
                         bf16_in=vals, bf16_bits=bits)
 
 
+def gen_grad_bf16(ref, out):
+    """Gradients stored as bf16 bit patterns.  The reference has these three steps as Metal kernels only;
+    the vectors are put together from reference functions that do run here, following the kernel text:
+    utils.bf16_bits for every rounding, cpu_gather_backward for the position-ordered sums,
+    cpu_adamw_step for the optimizer step."""
+    import utils as ref_utils
+    rng = np.random.default_rng(SEED + 90)
+    bits_of = lambda a: np.array([ref_utils.bf16_bits(x) for x in np.asarray(a, np.float32).ravel()],
+                                 dtype=np.uint16).reshape(np.shape(a))
+    widen = lambda b: (np.asarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+    # fp32_to_bf16 with and without accumulate (metal_ops.metal:12010-12041)
+    n = 1003
+    src = (rng.standard_normal(n) * 3).astype(np.float32)
+    src[:6] = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1.00390625], np.float32)
+    dst0 = bits_of((rng.standard_normal(n) * 3).astype(np.float32))
+    conv_plain = bits_of(src)
+    conv_acc = bits_of(src + widen(dst0))
+    # gather_backward_bf16_kernel (metal_ops.metal:12395-12446): sums from zero in position order, one rounding
+    V, C, B, T = 50, 24, 3, 40
+    ids = rng.integers(0, V // 2, size=(B, T)).astype(np.int32)   # repeats; rows >= V/2 stay untouched
+    ids[0, :9] = 7                                                 # a hot row
+    dout = rng.standard_normal((B, T, C)).astype(np.float32)
+    table0 = bits_of((0.5 * rng.standard_normal((V, C))).astype(np.float32))
+    sums = np.zeros((V, C), np.float32)
+    w = NS(requires_grad=True, shape=(V, C), grad=NS(storage=NS(data=sums)))
+    ref.backend.cpu_gather_backward((NS(storage=NS(data=ids)), w), (NS(grad=NS(storage=NS(data=dout))),))
+    table1 = table0.copy()
+    touched = np.unique(ids)
+    table1[touched] = bits_of(widen(table0[touched]) + sums[touched])
+    # adamw_step with bf16 gradients (backend.py:5125-5140)
+    m_ = 1000
+    p = rng.standard_normal(m_, dtype=np.float32)
+    g_bits = bits_of(rng.standard_normal(m_, dtype=np.float32))
+    m = (0.1 * rng.standard_normal(m_)).astype(np.float32)
+    v = (0.01 * rng.random(m_)).astype(np.float32)
+    hp = dict(lr=3e-4, lr_t=2.9e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1)
+    grad_scale = 0.5
+    p2, m2, v2 = p.copy(), m.copy(), v.copy()
+    g = widen(g_bits) * np.float32(grad_scale)
+    ref.backend.cpu_adamw_step(NS(data=p2), NS(data=g), NS(data=m2), NS(data=v2), np.zeros(m_, np.float32),
+                               hp["lr"], hp["lr_t"], hp["b1"], hp["b2"], hp["eps"], hp["wd"])
+    np.savez_compressed(os.path.join(out, "grad_bf16.npz"), src=src, dst0=dst0, conv_plain=conv_plain,
+                        conv_acc=conv_acc, ids=ids, dout=dout, table0=table0, table1=table1, p=p, g_bits=g_bits,
+                        m=m, v=v, p_out=p2, m_out=m2, v_out=v2, grad_scale=np.float64(grad_scale),
+                        hp=np.array([hp[k] for k in ("lr", "lr_t", "b1", "b2", "eps", "wd")], np.float64))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("AUTOGRAD_REFERENCE", "/root/reference"))
@@ -418,7 +465,7 @@ def main():
     args = ap.parse_args()
     ref = load_reference(args.reference)
     for fn in (gen_add_layernorm, gen_gelu, gen_gather, gen_flce, gen_rmsnorm_swiglu, gen_rope,
-               gen_rmsnorm_flce, gen_linear_add, gen_adamw_bf16):
+               gen_rmsnorm_flce, gen_linear_add, gen_adamw_bf16, gen_grad_bf16):
         fn(ref, args.out)
         print("wrote", fn.__name__)
 

@@ -85,3 +85,19 @@ def run_backward(n):
 def check_clean_status():
     ctx, _, _ = env()
     assert ctx.status() == 0
+
+
+def bf16_grad(t, bits):
+    """Attach to t a gradient stored as bf16 bit patterns (uint16), preloaded with `bits`."""
+    ctx, alloc, be = env()
+    g = hg.HostTensor(t.shape, np.uint16, requires_grad=False)
+    g.storage = alloc.alloc(g.shape, np.uint16)
+    be.copy_from_host(g, np.ascontiguousarray(bits, dtype=np.uint16))
+    t.grad = g
+    return g
+
+
+def down_bits(t):
+    """The raw 16-bit words of a bf16-stored tensor."""
+    ctx, alloc, be = env()
+    return ctx.copy_to_host(t.storage.ptr.address, tuple(t.shape), np.uint16)

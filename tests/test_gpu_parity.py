@@ -706,6 +706,145 @@ def test_adamw_golden(golden):
     G.free(p, gr, m, v)
 
 
+# ------------------------------------------------------------------------------ bf16 gradient storage
+def _bits_close(got_bits, ref_bits, what, max_off=0.01):
+    """Stored bf16 words: equal, except that a sum formed in another order may land on the neighbouring
+    bf16 value for a few elements (never further)."""
+    got = O.bf16_bits_to_f32(got_bits).astype(np.float64)
+    ref = O.bf16_bits_to_f32(ref_bits).astype(np.float64)
+    off = got_bits != ref_bits
+    assert off.mean() <= max_off, f"{what}: {off.mean():.3%} of the stored words differ"
+    if off.any():
+        assert np.max(np.abs(got[off] - ref[off]) / np.maximum(np.abs(ref[off]), 1e-30)) <= 2.0 ** -7, what
+
+
+def test_grad_bf16_conversion_bit_exact(golden):
+    """fp32 -> bf16 storage with and without accumulate, Inf / NaN / signed zero included, and back."""
+    ctx, alloc, be = G.env()
+    g = golden("grad_bf16")
+    cases = [(g["src"], g["dst0"], g["conv_plain"], g["conv_acc"])]
+    rng = np.random.default_rng(11)
+    n = (1 << 20) + 5
+    src = (rng.standard_normal(n) * 4).astype(np.float32)
+    dst0 = O.f32_to_bf16_bits(rng.standard_normal(n).astype(np.float32))
+    cases.append((src, dst0, O.f32_to_bf16_store(src, dst0, False), O.f32_to_bf16_store(src, dst0, True)))
+    for src, dst0, plain, acc in cases:
+        s = G.up(src, requires_grad=False)
+        d = G.up(dst0, requires_grad=False)
+        ctx.f32_to_bf16(s.storage.ptr.address, d.storage.ptr.address, src.size, accumulate=True)
+        got = G.down_bits(d)
+        # the sum of a NaN and a number is a NaN whose payload is the adder's choice: NaN-ness must agree
+        nan = np.isnan(O.bf16_bits_to_f32(acc))
+        assert np.array_equal(got[~nan], acc[~nan]) and np.all(np.isnan(O.bf16_bits_to_f32(got[nan])))
+        ctx.f32_to_bf16(s.storage.ptr.address, d.storage.ptr.address, src.size, accumulate=False)
+        assert np.array_equal(G.down_bits(d), plain)
+        back = G.empty(src.shape, requires_grad=False)
+        ctx.bf16_to_f32(d.storage.ptr.address, back.storage.ptr.address, src.size)
+        assert np.array_equal(G.down(back).view(np.uint32), O.bf16_bits_to_f32(plain).view(np.uint32))
+        G.free(s, d, back)
+    G.check_clean_status()
+
+
+def test_gather_backward_bf16_golden(golden):
+    ctx, alloc, be = G.env()
+    g = golden("grad_bf16")
+    ids = G.up(g["ids"], requires_grad=False)
+    table = G.up(O.bf16_bits_to_f32(g["table0"]).reshape(g["table0"].shape))
+    G.bf16_grad(table, g["table0"])
+    out = G.empty(g["dout"].shape, grad=g["dout"])
+    n = G.node("GatherOp", (ids, table), (out,))
+    G.run_backward(n)
+    got = G.down_bits(table.grad)
+    _bits_close(got, g["table1"], "dtable bits")
+    untouched = np.setdiff1d(np.arange(g["table0"].shape[0]), g["ids"].ravel())
+    assert np.array_equal(got[untouched], g["table0"][untouched])
+    G.check_clean_status()
+    G.free(ids, table, out)
+
+
+@pytest.mark.parametrize("V,C,n", [(32768, 1280, 32768), (5000, 100, 4099)])
+def test_gather_backward_bf16_vs_oracle(V, C, n):
+    """Zipf ids (hot rows spanning many groups), table gradient preloaded: stored words equal to the
+    position-ordered oracle except for the odd neighbouring value; rows of a single short run and
+    untouched rows exactly equal; run-to-run identical."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(4321)
+    ids_ = _zipf_ids(rng, V, n).reshape(1, n)
+    dout_ = rng.standard_normal((1, n, C), dtype=np.float32)
+    t0 = O.f32_to_bf16_bits((0.5 * rng.standard_normal((V, C))).astype(np.float32))
+    ref = O.gather_backward_bf16(ids_, dout_, t0)
+    ids = G.up(ids_, requires_grad=False)
+    out = G.empty(dout_.shape, grad=dout_)
+    runs = []
+    for _ in range(2):
+        table = G.empty((V, C))
+        G.bf16_grad(table, t0)
+        G.run_backward(G.node("GatherOp", (ids, table), (out,)))
+        runs.append(G.down_bits(table.grad))
+        G.free(table)
+    assert np.array_equal(runs[0], runs[1])
+    _bits_close(runs[0], ref, "dtable bits", max_off=0.002)
+    counts = np.bincount(ids_.ravel(), minlength=V)
+    assert np.array_equal(runs[0][counts == 0], t0[counts == 0])
+    assert np.array_equal(runs[0][counts == 1], ref[counts == 1])
+    G.check_clean_status()
+    G.free(ids, out)
+
+
+def test_adamw_bf16grad_golden(golden):
+    ctx, alloc, be = G.env()
+    g = golden("grad_bf16")
+    lr, lr_t, b1, b2, eps, wd = (float(v) for v in g["hp"])
+    p, gr, m, v = G.up(g["p"]), G.up(g["g_bits"], requires_grad=False), G.up(g["m"]), G.up(g["v"])
+    be.adamw_step(p.storage, gr.storage, m.storage, v.storage, None, lr, lr_t, b1, b2, eps, wd,
+                  grad_scale=float(g["grad_scale"]))
+    assert_close(G.down(p), g["p_out"], TOL_FWD, "p")
+    assert_close(G.down(m), g["m_out"], TOL_FWD, "m")
+    assert_close(G.down(v), g["v_out"], TOL_FWD, "v")
+    G.free(p, gr, m, v)
+
+
+def test_parameter_grads_stored_as_bf16(golden):
+    """LayerNorm dgamma/dbeta and the projection's dw/db land in bf16 gradient storage as
+    bf16(stored + fp32 gradient): the kernels accumulate into zeroed fp32 staging, one rounding follows."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(3)
+    d, eps = _ln_case(golden("add_layernorm"), "c384")
+    x = G.up(np.add(d["x"], d["r"]), grad=0)
+    gamma, beta = G.up(d["gamma"]), G.up(d["beta"])
+    pre_g = O.f32_to_bf16_bits(rng.standard_normal(d["gamma"].shape).astype(np.float32))
+    pre_b = O.f32_to_bf16_bits(rng.standard_normal(d["beta"].shape).astype(np.float32))
+    G.bf16_grad(gamma, pre_g)
+    G.bf16_grad(beta, pre_b)
+    y = G.empty(d["x"].shape, grad=d["dy"])
+    ln = G.node("LayerNormOp", (x, gamma, beta), (y,), eps=eps, normalized_dim=-1)
+    G.run_forward(ln)
+    G.run_backward(ln)
+    _bits_close(G.down_bits(gamma.grad), O.f32_to_bf16_store(d["dgamma"], pre_g, True), "dgamma bits")
+    _bits_close(G.down_bits(beta.grad), O.f32_to_bf16_store(d["dbeta"], pre_b, True), "dbeta bits")
+    G.free(x, gamma, beta, y)
+
+    g = golden("linear_add")
+    case = "wide"
+    xw = G.up(g[f"{case}.x"], grad=g[f"{case}.pre_x"])
+    act = G.up(g[f"{case}.act"], grad=g[f"{case}.pre_act"])
+    w, b = G.up(g[f"{case}.w"]), G.up(g[f"{case}.b"])
+    pre_w, pre_bb = O.f32_to_bf16_bits(g[f"{case}.pre_w"]), O.f32_to_bf16_bits(g[f"{case}.pre_b"])
+    G.bf16_grad(w, pre_w)
+    G.bf16_grad(b, pre_bb)
+    out = G.empty(g[f"{case}.out"].shape, grad=g[f"{case}.dout"])
+    n = G.node("FusedLinearAddOp", (xw, act, w, b), (out,))
+    G.run_backward(n)
+    # the golden dw/db include the fp32 preload; take it out again, then add onto the bf16 preload
+    dw_only = np.subtract(g[f"{case}.dw"], g[f"{case}.pre_w"])
+    db_only = np.subtract(g[f"{case}.db"], g[f"{case}.pre_b"])
+    assert_close(G.down(w.grad), np.add(O.bf16_bits_to_f32(pre_w).reshape(dw_only.shape), dw_only), TOL_BF16, "dw")
+    assert_close(G.down(b.grad), np.add(O.bf16_bits_to_f32(pre_bb).reshape(db_only.shape), db_only), TOL_BF16, "db")
+    assert_close(G.down(xw.grad), g[f"{case}.dx"], TOL_BWD, "dx")
+    G.check_clean_status()
+    G.free(xw, act, w, b, out)
+
+
 def test_errors_are_exceptions_not_aborts():
     import autograd_b200 as ag
     ctx, alloc, be = G.env()

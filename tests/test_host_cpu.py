@@ -268,6 +268,13 @@ def _dp_worker(rank, world, port, out_q):
         assert red.world_size == world and abs(red.grad_scale - 1.0 / world) < 1e-12
         red.reduce()
         loss = red.mean_loss(torch.tensor([float(rank)]))
+        # the large bucket once more in its bf16 transport form: half the bytes, values rounded to bf16
+        big2 = torch.from_numpy(np.full(1000, 1.0 + 2.0 ** -10 + rank, np.float32))
+        red2 = dp.GradAllReducer([big2], wires=[dp.Bf16Wire.for_tensors(big2)])
+        assert red2.bytes_per_step == 2000
+        red2.reduce()
+        want = float(sum(float(torch.tensor(1.0 + 2.0 ** -10 + r).to(torch.bfloat16)) for r in range(world)))
+        assert np.all(big2.numpy() == np.float32(want)), (big2[:4], want)
         _, dg_full, db_full = O.layernorm_backward(full_x, gamma, full_dy, 1e-5, np.zeros((10, 8), np.float32), z, z)
         ok = (np.allclose(small.numpy(), np.concatenate([dg_full, db_full]), rtol=1e-5, atol=1e-5)
               and np.all(big.numpy() == sum(range(1, world + 1))) and abs(float(loss) - (world - 1) / 2) < 1e-6)

@@ -147,3 +147,18 @@ def test_adamw_and_bf16(golden):
     assert_close(m, g["m_out"], TIGHT, "m")
     assert_close(v, g["v_out"], TIGHT, "v")
     assert np.array_equal(O.f32_to_bf16_bits(g["bf16_in"]), g["bf16_bits"])
+
+
+def test_grad_bf16_storage(golden):
+    """Gradients kept as bf16 bit patterns: conversion with and without accumulate, the gather
+    backward that rounds once per table row, AdamW on bf16 gradients."""
+    g = golden("grad_bf16")
+    assert np.array_equal(O.f32_to_bf16_store(g["src"], g["dst0"], False), g["conv_plain"])
+    assert np.array_equal(O.f32_to_bf16_store(g["src"], g["dst0"], True), g["conv_acc"])
+    assert np.array_equal(O.gather_backward_bf16(g["ids"], g["dout"], g["table0"]), g["table1"])
+    lr, lr_t, b1, b2, eps, wd = (float(v) for v in g["hp"])
+    p, m, v = O.adamw_step_bf16grad(g["p"], g["g_bits"], g["m"], g["v"], lr, lr_t, b1, b2, eps, wd,
+                                    grad_scale=float(g["grad_scale"]))
+    assert_close(p, g["p_out"], TIGHT, "p")
+    assert_close(m, g["m_out"], TIGHT, "m")
+    assert_close(v, g["v_out"], TIGHT, "v")
