@@ -238,7 +238,7 @@ inline size_t al256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 FlcePlan flce_plan(const ag_flce_desc* d) {
   FlcePlan p;
-  p.rows_per_tile = d->N < 16384 ? d->N : 16384;
+  p.rows_per_tile = d->N < AG_FLCE_ROWS_TILE ? d->N : AG_FLCE_ROWS_TILE;
   const int vc = d->vocab_chunk < d->V ? d->vocab_chunk : d->V;
   size_t off = 0;
   p.off_panel = off; off += al256((size_t)p.rows_per_tile * vc * 4);

@@ -23,6 +23,12 @@ int ag_flce_tc_grads(ag_ctx* ctx, const ag_flce_desc* d, void* tc_scratch, int64
                      const int32_t* targets, const float* lse, const float* row_scale, const float* dloss,
                      const float* denom, float* dX, float* dW);
 
+// Token rows handled per pass over the vocabulary panels (the rows of the logits / dlogits panel held in
+// scratch).  148 SMs x 128-row tiles = 74 CTA pairs x 256-row tiles: every GEMM of a full row tile then
+// has a whole number of rounds over the SMs in the row direction (the dX panel, 1280 columns = 5 column
+// tiles, takes exactly 5 rounds; with 16384 rows its 320 tiles took 5 rounds for 4.3 rounds of work).
+constexpr int64_t AG_FLCE_ROWS_TILE = 148 * 128;
+
 // Operand modes of the tensor-core GEMM: tf32 (hi, lo) pairs (3 MMAs per k-step, fp32-grade), bf16
 // values (1 MMA), bf16 (hi, lo) pairs (3 MMAs at the bf16 rate).
 enum AgTcMode { AG_TC_TF32X3 = 0, AG_TC_BF16 = 1, AG_TC_BF16X3 = 2 };

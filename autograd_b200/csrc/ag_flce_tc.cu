@@ -1186,7 +1186,7 @@ TcPlan tc_plan(const ag_flce_desc* d) {
   const int mode = tc_mode_of(d->precision);
   const bool bf16 = mode == TC_BF16;  // one array per operand (no lo part)
   p.es = tc_mode_tf32(mode) ? 4 : 2;
-  p.rows_tile = d->N < 16384 ? d->N : 16384;
+  p.rows_tile = d->N < AG_FLCE_ROWS_TILE ? d->N : AG_FLCE_ROWS_TILE;
   p.vc = d->vocab_chunk < d->V ? d->vocab_chunk : d->V;
   const int64_t ldr = up8(p.rows_tile), ldc = up16(p.vc);
   size_t off = 0;

@@ -467,6 +467,27 @@ def test_flce_mid_size_vs_oracle(N, C, V, precision):
     G.check_clean_status()
 
 
+@pytest.mark.parametrize("precision", [0, 1, 2, 3])
+def test_flce_more_rows_than_one_row_tile(precision):
+    """Token rows are taken in tiles of 18944 (one 128-row GEMM tile per SM); 19244 rows = a full tile and
+    a ragged one of 300, with a ragged last vocabulary panel."""
+    ctx, alloc, be = G.env()
+    N, C, V = 18944 + 300, 64, 1000
+    rng = np.random.default_rng(1240)
+    X_ = (rng.standard_normal((1, N, C)) / np.sqrt(C)).astype(np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C))).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(1, N)).astype(np.int32)
+    Y_[rng.random((1, N)) < 0.05] = -1
+    Xo, Wo = (O.round_to_bf16(X_[0]), O.round_to_bf16(W_)) if precision == 2 else (X_[0], W_)
+    ref = O.flce_masked(Xo, Wo, Y_[0], dloss=1.0)
+    loss, dX, dW = _run_flce(be, X_, W_, Y_, precision, ignore_mode=0, chunk=512, dloss=1.0)
+    tol_f, tol_b = (TOL_BF16, TOL_BF16) if precision == 2 else (TOL_FWD, TOL_BWD)
+    assert abs(loss - float(ref["loss"])) <= tol_f * abs(loss)
+    assert_close(dX[0], ref["dX"], tol_b, "dX")
+    assert_close(dW, ref["dW"], tol_b, "dW")
+    G.check_clean_status()
+
+
 @pytest.mark.parametrize("precision", [1, 3])
 def test_flce_wide_vocab_panel(precision):
     """Vocabulary panels wider than 4096 columns: the dX contraction is taken in pieces of 4096."""
