@@ -50,6 +50,7 @@ class FakeContext:
 
     def __init__(self):
         self.calls = []
+        self.kwargs = []          # keyword arguments of the recorded calls, same order
         self._next = 0x10000000
         self.sm_count = 148
 
@@ -60,6 +61,7 @@ class FakeContext:
 
     def free(self, addr):
         self.calls.append(("free", addr))
+        self.kwargs.append({})
 
     def norm_partials_bytes(self, c):
         return 148 * 8 * 2 * c * 4
@@ -79,6 +81,7 @@ class FakeContext:
     def __getattr__(self, name):
         def rec(*args, **kw):
             self.calls.append((name,) + args)
+            self.kwargs.append(kw)
         return rec
 
 
@@ -170,6 +173,46 @@ def test_scratch_slots_are_preferred_over_the_workspace():
     be.get_backward_kernel(n.op)(n.inputs, n.outputs)            # no scratch: backend workspace
     call = [c for c in ctx.calls if c[0] == "gather_backward"][0]
     assert call[4] != address_of(slot) and call[5] >= ctx.scatter_add_scratch_bytes(32, 32, 50)
+
+
+def test_bf16_gradient_storage_goes_through_fp32_staging():
+    """A parameter whose gradient storage is uint16 (bf16 words, the reference's grad_dtype="bf16"): the
+    kernel accumulates into a zeroed fp32 staging area, then one f32_to_bf16(accumulate) adds it into the
+    stored gradient; the gather backward and AdamW switch to their bf16-gradient entry points."""
+    ctx, alloc, be = _fake_env()
+    x, g, b = _t(alloc, (2, 3, 8), grad=True), _t(alloc, (8,)), _t(alloc, (8,), grad=True)
+    g.grad = hg.HostTensor((8,), np.uint16, requires_grad=False)
+    g.grad.storage = alloc.alloc((8,), np.uint16)
+    y = _t(alloc, (2, 3, 8), grad=True)
+    n = hg.make_node(hg.make_op("LayerNormOp", eps=1e-5, normalized_dim=-1), (x, g, b), (y,))
+    be.get_backward_kernel(n.op)(n.inputs, n.outputs)
+    names = [c[0] for c in ctx.calls]
+    assert names.index("fill_f32") < names.index("layernorm_backward") < names.index("f32_to_bf16")
+    ln = [c for c in ctx.calls if c[0] == "layernorm_backward"][0]
+    conv = [c for c in ctx.calls if c[0] == "f32_to_bf16"]
+    assert len(conv) == 1                                         # beta keeps its fp32 storage
+    stage = ln[6]
+    assert stage not in (0, address_of(g.grad.storage)) and ln[7] == address_of(b.grad.storage)
+    assert conv[0][1:4] == (stage, address_of(g.grad.storage), 8)
+    assert ctx.kwargs[[c[0] for c in ctx.calls].index("f32_to_bf16")] == {"accumulate": True}
+    fill = [c for c in ctx.calls if c[0] == "fill_f32"][0]
+    assert fill[1] == stage and fill[2] == 0.0
+
+    ctx.calls.clear()
+    ctx.kwargs.clear()
+    ids, tab = _t(alloc, (2, 16), np.int32, requires_grad=False), _t(alloc, (50, 32))
+    tab.grad = hg.HostTensor((50, 32), np.uint16, requires_grad=False)
+    tab.grad.storage = alloc.alloc((50, 32), np.uint16)
+    out = _t(alloc, (2, 16, 32), grad=True)
+    gn = hg.make_node(hg.make_op("GatherOp"), (ids, tab), (out,))
+    be.get_backward_kernel(gn.op)(gn.inputs, gn.outputs)
+    assert [c[0] for c in ctx.calls if c[0].startswith("gather")] == ["gather_backward_bf16"]
+
+    ctx.calls.clear()
+    ctx.kwargs.clear()
+    p, m, v = _t(alloc, (64,)), _t(alloc, (64,)), _t(alloc, (64,))
+    be.adamw_step(p.storage, tab.grad.storage, m.storage, v.storage, None, 1e-3, 1e-3, 0.9, 0.95, 1e-8, 0.1)
+    assert ctx.calls[-1][0] == "adamw_step" and ctx.kwargs[-1] == {"grad_bf16": True}
 
 
 def test_bf16_host_conversion_matches_the_oracle(golden):
