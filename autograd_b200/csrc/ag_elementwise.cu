@@ -429,6 +429,15 @@ __device__ __forceinline__ uint32_t bf16_bits_rne(float value) {
 
 // dst = bf16(src), or bf16(src + float(dst)) when accumulate: 8 elements per packet (two 16-byte loads,
 // one 16-byte store)
+// 32 bytes of fp32 per lane in one store (a whole sector; two 16-byte stores of a lane each fill half a
+// sector per request): bf16 -> fp32 went from 47 to 41 us on 41.9 M elements.  The same width on the load
+// side of fp32 -> bf16 measured slower (47 against 43 us) and is not used.  Needs a 32-byte aligned pointer.
+__device__ __forceinline__ void st_v8_f32(float* p, const float (&v)[8]) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]),
+               "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
+}
+
 struct F32ToBf16 {
   const float* src;
   uint16_t* dst;
@@ -472,6 +481,7 @@ struct F32ToBf16 {
 
 __global__ void __launch_bounds__(EW_THREADS) f32_to_bf16_kernel(F32ToBf16 f, int64_t n, int early) { ew_drive<8>(n, f, early); }
 
+template <bool WIDE>
 struct Bf16ToF32 {
   const uint16_t* src;
   float* dst;
@@ -484,16 +494,25 @@ struct Bf16ToF32 {
     for (int u = 0; u < U; ++u) {
       const int64_t o = (i + u * stride) * 8;
       const uint32_t w[4] = {t[u].x, t[u].y, t[u].z, t[u].w};
-      *reinterpret_cast<float4*>(dst + o) = make_float4(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xffff0000u),
-                                                         __uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xffff0000u));
-      *reinterpret_cast<float4*>(dst + o + 4) = make_float4(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xffff0000u),
-                                                             __uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xffff0000u));
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[2 * e] = __uint_as_float(w[e] << 16);
+        v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+      }
+      if constexpr (WIDE) {
+        st_v8_f32(dst + o, v);
+      } else {
+        *reinterpret_cast<float4*>(dst + o) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(dst + o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
     }
   }
   __device__ __forceinline__ void scalar(int64_t j) { dst[j] = __uint_as_float((uint32_t)src[j] << 16); }
 };
 
-__global__ void __launch_bounds__(EW_THREADS) bf16_to_f32_kernel(Bf16ToF32 f, int64_t n, int early) { ew_drive<8>(n, f, early); }
+template <bool WIDE>
+__global__ void __launch_bounds__(EW_THREADS) bf16_to_f32_kernel(Bf16ToF32<WIDE> f, int64_t n, int early) { ew_drive<8>(n, f, early); }
 
 template <typename... P>
 bool all_aligned16(P... p) {
@@ -647,8 +666,8 @@ extern "C" int ag_f32_to_bf16(ag_ctx* ctx, const float* src, uint16_t* dst, int6
   if (n == 0) return AG_OK;
   AG_REQUIRE(ctx, src && dst && n > 0, "ag_f32_to_bf16: null pointer or negative n");
   AG_REQUIRE(ctx, all_aligned16(src, dst), "ag_f32_to_bf16: pointers must be 16-byte aligned");
-  F32ToBf16 f{src, dst, accumulate != 0};
   const int grid = ew_grid(ctx, n / 8, 0);
+  F32ToBf16 f{src, dst, accumulate != 0};
   AG_LAUNCH_PDL(ctx, "f32_to_bf16_kernel", f32_to_bf16_kernel, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
   return AG_OK;
 }
@@ -658,8 +677,13 @@ extern "C" int ag_bf16_to_f32(ag_ctx* ctx, const uint16_t* src, float* dst, int6
   if (n == 0) return AG_OK;
   AG_REQUIRE(ctx, src && dst && n > 0, "ag_bf16_to_f32: null pointer or negative n");
   AG_REQUIRE(ctx, all_aligned16(src, dst), "ag_bf16_to_f32: pointers must be 16-byte aligned");
-  Bf16ToF32 f{src, dst};
   const int grid = ew_grid(ctx, n / 8, 0);
-  AG_LAUNCH_PDL(ctx, "bf16_to_f32_kernel", bf16_to_f32_kernel, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
+  if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+    Bf16ToF32<true> f{src, dst};
+    AG_LAUNCH_PDL(ctx, "bf16_to_f32_kernel", bf16_to_f32_kernel<true>, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
+  } else {
+    Bf16ToF32<false> f{src, dst};
+    AG_LAUNCH_PDL(ctx, "bf16_to_f32_kernel", bf16_to_f32_kernel<false>, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
+  }
   return AG_OK;
 }
