@@ -404,7 +404,8 @@ def run_b200(a):
             # the dominant kernel is the tcgen05 panel GEMM of the CE head: every launch does the
             # same useful work, 2 * rows_tile * vocab_chunk * C (logits, dX and dW panels alike)
             t_flce = (fam.get("flce_fwd", (0, 0))[1] + fam.get("flce_bwd", (0, 0))[1]) / a.steps / 1e3
-            rows_tile = min(Nn, 16384)
+            n_row_tiles = -(-Nn // 18944)          # the head takes token rows in tiles of 148 x 128
+            rows_tile = Nn / n_row_tiles           # mean rows per launch
             vc = min(cfg.ce_vocab_chunk, cfg.vocab)
             fl_launch = 2.0 * rows_tile * vc * cfg.n_embd
             avg_ms = sum(tc_ms) / len(tc_ms)
@@ -417,6 +418,12 @@ def run_b200(a):
                         "traffic": None, "launches_per_step": len(tc_ms) // a.steps,
                         "avg_launch_ms": round(avg_ms, 4), "useful_flops_per_launch": fl_launch,
                         "issued_mma_tflops": round(ach * mma_per_kstep, 2),
+                        # MMA issue rate in bf16-equivalent terms (a TF32 MMA takes the tensor pipe twice as
+                        # long as a bf16 one) over the same peak: how busy the tensor pipe is kept
+                        "issued_frac_of_peak": round(ach * mma_per_kstep * (1 if "bf16" in a.ce_precision else 2) / peak, 4),
+                        # the same rate over the nominal dense figure of the part at its maximum clock
+                        # (2250 TFLOP/s bf16, 1125 TF32); the step runs below that clock, at the power cap
+                        "issued_frac_of_nominal": round(ach * mma_per_kstep / (2250.0 if "bf16" in a.ce_precision else 1125.0), 4),
                         "peak_source": peaks["source"] + " cuBLAS bf16, sustained; TF32 MMAs issue at half that "
                                        "rate and 3xTF32 issues three per k-step",
                         "flce_useful_tflops_whole_op": round(useful / t_flce / 1e12, 2),
