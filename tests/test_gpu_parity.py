@@ -766,6 +766,42 @@ def test_grad_bf16_conversion_bit_exact(golden):
     G.check_clean_status()
 
 
+def test_grad_bf16_edge_cases():
+    """Empty input is a no-op, fewer elements than one packet take the scalar tail, a pointer that is not
+    16-byte aligned is an error (never a fault); C not a multiple of 4 takes the scalar scatter-add."""
+    import autograd_b200 as ag
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(12)
+    src = rng.standard_normal(13).astype(np.float32)
+    old = O.f32_to_bf16_bits(rng.standard_normal(13).astype(np.float32))
+    s, d = G.up(src, requires_grad=False), G.up(old, requires_grad=False)
+    ctx.f32_to_bf16(s.storage.ptr.address, d.storage.ptr.address, 0)
+    assert np.array_equal(G.down_bits(d), old)
+    ctx.f32_to_bf16(s.storage.ptr.address, d.storage.ptr.address, 5, accumulate=True)
+    want = old.copy()
+    want[:5] = O.f32_to_bf16_store(src[:5], old[:5], True)
+    assert np.array_equal(G.down_bits(d), want)
+    ctx.f32_to_bf16(s.storage.ptr.address, d.storage.ptr.address, 13)
+    assert np.array_equal(G.down_bits(d), O.f32_to_bf16_bits(src))
+    with pytest.raises(ag.AgError):
+        ctx.f32_to_bf16(s.storage.ptr.address + 4, d.storage.ptr.address, 4)
+    with pytest.raises(ag.AgError):
+        ctx.bf16_to_f32(d.storage.ptr.address + 2, s.storage.ptr.address, 4)
+    G.free(s, d)
+    # ragged width: 30 columns
+    V, C, n = 40, 30, 200
+    ids_ = rng.integers(0, V // 2, size=(1, n)).astype(np.int32)
+    dout_ = rng.standard_normal((1, n, C), dtype=np.float32)
+    t0 = O.f32_to_bf16_bits(rng.standard_normal((V, C)).astype(np.float32))
+    ids, out = G.up(ids_, requires_grad=False), G.empty(dout_.shape, grad=dout_)
+    table = G.empty((V, C))
+    G.bf16_grad(table, t0)
+    G.run_backward(G.node("GatherOp", (ids, table), (out,)))
+    _bits_close(G.down_bits(table.grad), O.gather_backward_bf16(ids_, dout_, t0), "ragged dtable bits", max_off=0.02)
+    G.check_clean_status()
+    G.free(ids, out, table)
+
+
 def test_gather_backward_bf16_golden(golden):
     ctx, alloc, be = G.env()
     g = golden("grad_bf16")
