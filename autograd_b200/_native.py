@@ -63,6 +63,7 @@ SIGNATURES = {
     "ag_norm_partials_bytes": (_sz, [_ctx, _int]),
     "ag_layernorm_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _i64, _int, _f32]),
     "ag_layernorm_backward_noalloc": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _int, _f32]),
+    "ag_debug_expire_staging": (_int, [_ctx]),
     "ag_rmsnorm_forward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _i64, _int, _f32, _int]),
     "ag_rmsnorm_backward": (_int, [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _i64, _int, _f32, _int]),
     "ag_gelu_forward": (_int, [_ctx, _ptr, _ptr, _i64]),

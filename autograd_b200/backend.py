@@ -70,7 +70,7 @@ class CudaBackend:
         self.ce_ignore_mode = N.AG_CE_IGNORE_MASKED
         self._workspace = None       # grow-only scratch for calls that arrive without arena scratch
         self._grad_stage = None      # grow-only fp32 staging of gradients whose storage is bf16
-        self._side = {}              # id(loss tensor) -> Storage holding lse (forward -> backward)
+        self._side = {}              # id(loss tensor) -> (loss tensor, Storage holding lse), forward -> backward
         self._forward = {
             "LayerNormOp": self._layernorm_forward,
             "GELUOp": self._gelu_forward,
@@ -170,7 +170,13 @@ class CudaBackend:
         self._context.synchronize()
 
     def adamw_step(self, p_storage, g_storage, m_storage, v_storage, tmp_storage, lr, lr_t, b1, b2, eps,
-                   weight_decay, grad_scale=1.0, **_ignored):
+                   weight_decay, grad_scale=1.0, **extra):
+        # The packed-buffer form of the reference's Metal dispatch (optimizer.py:471-486) passes
+        # numel, decay_numel, lr_bc1 and inv_sqrt_bc2, which change both the extent and the maths of
+        # the step; that form is not implemented here, and dropping them would be a silently wrong step.
+        unsupported = sorted(k for k in extra if k in ("numel", "decay_numel", "lr_bc1", "inv_sqrt_bc2"))
+        if unsupported:
+            raise TypeError(f"adamw_step: the packed-buffer arguments {unsupported} are not supported by the cuda backend")
         n = int(prod(p_storage.shape))
         grad_bf16 = np.dtype(g_storage.dtype) == np.dtype(np.uint16)  # backend.py:5128, :5139
         self._context.adamw_step(address_of(p_storage), address_of(g_storage), address_of(m_storage),
@@ -351,14 +357,39 @@ class CudaBackend:
         return self._context.flce_desc(n, c, v, vocab_chunk=self.ce_vocab_chunk, precision=self.ce_precision,
                                        reduction=self.ce_reduction, ignore_mode=self.ce_ignore_mode)
 
-    def _lse_buffer(self, key, n):
-        st = self._side.get(key)
+    # The lse vector must survive from the head's forward to its backward, which the runtime's
+    # scratch (one execution step) cannot give; it lives in a side buffer per loss tensor.  The
+    # tensor classes have no weak references, so an entry holds its loss tensor (its id cannot be
+    # reused while the entry exists) and the table is bounded: beyond MAX_SIDE_BUFFERS graphs the
+    # least recently used entry is released.
+    MAX_SIDE_BUFFERS = 8
+
+    def _lse_buffer(self, out, n):
+        key = id(out)
+        ent = self._side.pop(key, None)
+        st = ent[1] if ent is not None else None
         if st is None or st.nbytes < n * 4:
             if st is not None:
+                self._context.synchronize()
                 self._allocator.free(st)
             st = self._allocator.alloc((n,), np.float32)
-            self._side[key] = st
+        self._side[key] = (out, st)          # most recently used last
+        while len(self._side) > self.MAX_SIDE_BUFFERS:
+            _, old = self._side.pop(next(iter(self._side)))
+            self._context.synchronize()
+            self._allocator.free(old)
         return st
+
+    def _lse_lookup(self, out):
+        ent = self._side.get(id(out))
+        return None if ent is None or ent[0] is not out else ent[1]
+
+    def release_side_buffers(self):
+        """Free every forward -> backward side buffer (call when the graphs that own them are dropped)."""
+        self._context.synchronize()
+        for _, st in self._side.values():
+            self._allocator.free(st)
+        self._side.clear()
 
     def _flce_forward(self, inputs, outputs, scratch=None):
         x, w, targets = inputs[0], inputs[1], inputs[2]
@@ -369,7 +400,7 @@ class CudaBackend:
         desc = self._flce_desc(n, c, v)
         need = self._context.flce_scratch_bytes(desc)
         sc, sc_bytes = self._slot(scratch, "flce", need)
-        lse = self._lse_buffer(id(out), n)
+        lse = self._lse_buffer(out, n)
         self._context.flce_forward(desc, _addr(x), _addr(w), _addr(targets), _addr(row_scale), _addr(out),
                                    address_of(lse), sc, sc_bytes)
 
@@ -384,7 +415,7 @@ class CudaBackend:
         desc = self._flce_desc(n, c, v)
         need = self._context.flce_scratch_bytes(desc)
         sc, sc_bytes = self._slot(scratch, "flce", need)
-        lse = self._side.get(id(out))
+        lse = self._lse_lookup(out)
         if lse is None:
             raise RuntimeError("FusedLinearCrossEntropy backward called before forward")
         dx = _addr(x.grad) if x.requires_grad else 0
@@ -438,6 +469,22 @@ class CudaBackend:
         flce_bytes = self._context.flce_scratch_bytes(desc)
         return desc, z_bytes, part_bytes, flce_bytes
 
+    def _rms_flce_slot(self, scratch, n, c, v):
+        """(desc, base, z_bytes, part_bytes, bytes left for the CE head) of the "rms_flce" slot.
+
+        The slot was sized when the graph was planned, from ce_precision / ce_vocab_chunk as they
+        were then; the head's need depends on both.  The size that is handed on is what really
+        remains in the slot after z, dz and the partial rows, so that a setting changed after
+        planning is caught here or by the C side's own size check instead of overrunning the arena."""
+        desc, z_bytes, part_bytes, flce_bytes = self._rms_flce_layout(n, c, v)
+        need = 2 * z_bytes + part_bytes + flce_bytes
+        base, slot_bytes = self._slot(scratch, "rms_flce", need)
+        if slot_bytes < need:
+            raise RuntimeError(
+                f"FusedRMSNormLinearCrossEntropy: the scratch slot has {slot_bytes} bytes but the current "
+                f"ce_precision / ce_vocab_chunk need {need}; they were changed after the graph was planned")
+        return desc, base, z_bytes, part_bytes, slot_bytes - (2 * z_bytes + part_bytes)
+
     def _rms_flce_forward(self, inputs, outputs, scratch=None):
         """backend.py:716-797: z = RMSNorm(x)*gamma, then the linear + CE head on z."""
         x, w, gamma, targets = inputs[:4]
@@ -445,11 +492,10 @@ class CudaBackend:
         out = outputs[0]
         n, c = self._rows_cols(x)
         v = w.shape[0]
-        desc, z_bytes, part_bytes, flce_bytes = self._rms_flce_layout(n, c, v)
-        base, _ = self._slot(scratch, "rms_flce", 2 * z_bytes + part_bytes + flce_bytes)
+        desc, base, z_bytes, part_bytes, flce_bytes = self._rms_flce_slot(scratch, n, c, v)
         z = base
         self._context.rmsnorm_forward(_addr(x), _addr(gamma), z, 0, n, c, out.op.op.eps)
-        lse = self._lse_buffer(id(out), n)
+        lse = self._lse_buffer(out, n)
         self._context.flce_forward(desc, z, _addr(w), _addr(targets), _addr(row_scale), _addr(out), address_of(lse),
                                    base + 2 * z_bytes + part_bytes, flce_bytes)
 
@@ -463,10 +509,9 @@ class CudaBackend:
         n, c = self._rows_cols(x)
         v = w.shape[0]
         eps = out.op.op.eps
-        desc, z_bytes, part_bytes, flce_bytes = self._rms_flce_layout(n, c, v)
-        base, _ = self._slot(scratch, "rms_flce", 2 * z_bytes + part_bytes + flce_bytes)
+        desc, base, z_bytes, part_bytes, flce_bytes = self._rms_flce_slot(scratch, n, c, v)
         z, dz, part = base, base + z_bytes, base + 2 * z_bytes
-        lse = self._side.get(id(out))
+        lse = self._lse_lookup(out)
         if lse is None:
             raise RuntimeError("FusedRMSNormLinearCrossEntropy backward called before forward")
         self._context.rmsnorm_forward(_addr(x), _addr(gamma), z, 0, n, c, eps)

@@ -152,6 +152,10 @@ class CudaContext:
         self._check(lib.ag_layernorm_backward_noalloc(self._h, _p(dy), _p(x), _p(gamma), _p(dres), _p(dx),
                                                       _p(dgamma), _p(dbeta), int(N_), int(C_), float(eps)))
 
+    def debug_expire_staging(self):
+        """Test hook: the next norm kernel gives up its staging wait at once (see the header)."""
+        self._check(lib.ag_debug_expire_staging(self._h))
+
     def rmsnorm_forward(self, x, gamma, y, inv_rms, N_, C_, eps, dtype=N.AG_F32):
         self._check(lib.ag_rmsnorm_forward(self._h, _p(x), _p(gamma), _p(y), _p(inv_rms), int(N_), int(C_), float(eps),
                                            int(dtype)))

@@ -25,6 +25,8 @@ struct ag_ctx {
   int64_t launches;
   int pdl;              // 1: kernels are launched with programmatic stream serialization
   int tc_pair;          // 1: the split-operand tensor-core GEMMs run on CTA pairs (cta_group::2)
+  int norm_ring;        // 1: norm kernels stream rows through a shared-memory ring fed by bulk copies
+  int debug_stage_expire;  // ag_debug_expire_staging: the next staging wait gives up at once (tests)
   int tc_timing;        // ag_tc_timing: bracket tensor-core GEMM launches with pool events
   int tc_timing_base;
   int tc_timing_count;
@@ -242,8 +244,12 @@ __device__ __forceinline__ void ag_prefetch_l2_bulk(const void* src, uint32_t by
 // through the bulk-copy engine when alignment allows, else with plain loads.  Called by all
 // threads of the CTA; returns after a __syncthreads() with the data visible.
 // `bar` must point to an 8-byte aligned uint64_t in shared memory used for nothing else.
+// `poll_limit` bounds the wait for the copy; when it runs out the CTA records
+// AG_STATUS_STAGE_FALLBACK, gives the copy that is still in flight a second bounded wait to
+// land (nothing may write this CTA's shared memory behind its back) and fills the vectors with
+// plain loads.  A limit of 0 takes that path at once (used by the tests).
 __device__ __forceinline__ void ag_stage_vectors(float* dst0, const float* src0, float* dst1, const float* src1,
-                                                 int n, uint64_t* bar, int* status) {
+                                                 int n, uint64_t* bar, int* status, uint32_t poll_limit = 1u << 20) {
   const uint32_t bytes = (uint32_t)n * 4u;
   const bool bulk_ok = (bytes % 16u == 0) && ((reinterpret_cast<uintptr_t>(src0) & 15u) == 0) &&
                        (src1 == nullptr || (reinterpret_cast<uintptr_t>(src1) & 15u) == 0) &&
@@ -260,10 +266,16 @@ __device__ __forceinline__ void ag_stage_vectors(float* dst0, const float* src0,
       ag_bulk_g2s(dst0, src0, bytes, bar);
       if (src1) ag_bulk_g2s(dst1, src1, bytes, bar);
     }
-    done = ag_mbar_wait_bounded(bar, 0, 1u << 20);
+    done = ag_mbar_wait_bounded(bar, 0, poll_limit);
     // all threads agree on the outcome
     done = __syncthreads_and(done ? 1 : 0) != 0;
-    if (!done && threadIdx.x == 0) atomicOr(status, AG_STATUS_STAGE_FALLBACK);
+    if (!done) {
+      if (threadIdx.x == 0) {
+        atomicOr(status, AG_STATUS_STAGE_FALLBACK);
+        if (!ag_mbar_wait_bounded(bar, 0, 1u << 20)) atomicOr(status, AG_STATUS_WAIT_EXPIRED);
+      }
+      __syncthreads();
+    }
   }
   if (!done) {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {

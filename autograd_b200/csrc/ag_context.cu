@@ -64,6 +64,9 @@ extern "C" int ag_ctx_create(int device, void* stream, ag_ctx** out) {
     // AG_B200_TC_PAIR=0 runs the tensor-core GEMMs on single CTAs (diagnostics)
     e = getenv("AG_B200_TC_PAIR");
     c->tc_pair = (e && e[0] == '0') ? 0 : 1;
+    e = getenv("AG_B200_NORM_RING");
+    c->norm_ring = (e && e[0] == '0') ? 0 : 1;
+    c->debug_stage_expire = 0;
   }
   CREATE_CUDA(cudaMalloc(&c->d_status, sizeof(int)));
   CREATE_CUDA(cudaMemset(c->d_status, 0, sizeof(int)));

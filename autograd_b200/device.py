@@ -71,11 +71,12 @@ def cuda_scratch_layouts(node, backend, pack_slots):
     return None, None
 
 
-def register(device: int = 0, stream: int | None = None, reference=None):
-    """Create the cuda device and, when the reference's modules are importable (or passed as
-    `reference`, an object with attributes `device`, `runtime`, `scratch`), hook it into them.
+def register(device: int = 0, stream: int | None = None, reference=None, existing=None):
+    """Create the cuda device (or take `existing`, a (context, allocator, backend) triple from
+    `create`) and, when the reference's modules are importable (or passed as `reference`, an object
+    with attributes `device`, `runtime`, `scratch`), hook it into them.
     Returns (context, allocator, backend)."""
-    ctx, allocator, backend = create(device, stream)
+    ctx, allocator, backend = existing if existing is not None else create(device, stream)
     mods = reference
     if mods is None:
         mods = _find_reference_modules()

@@ -137,6 +137,12 @@ int ag_layernorm_backward_noalloc(ag_ctx* ctx, const float* dy, const float* x, 
                                   const float* dres, float* dx, float* dgamma, float* dbeta,
                                   int64_t N, int C, float eps);
 
+/* Test hook (no counterpart in the reference): the next LayerNorm / RMSNorm kernel launched through
+ * ctx gives up its bounded wait for the staged gamma/beta vectors at once, so that the unwind path
+ * runs: AG_STATUS_STAGE_FALLBACK is set, the copy in flight is given time to land, the vectors
+ * are filled with plain loads and the results are still correct.  One-shot. */
+int ag_debug_expire_staging(ag_ctx* ctx);
+
 /* ---- a4 RMSNorm -----------------------------------------------------------------------
  * Replaces: the RMSNorm stage of backend.py:1097-1108 / :1228-1251 (also :741-749,
  * :862-886, :1737-1745, :1990-2011); metal_ops.metal:3412-3537, :8107-8240, :14542.

@@ -120,9 +120,11 @@ def _cfg1_inputs(N=16384, C=384, seed=1234):
     return x, r, gamma, beta, dy
 
 
-@pytest.mark.parametrize("N,C", [(16384, 384), (4096, 1280), (1000, 1536), (777, 2048), (300, 4100)])
+@pytest.mark.parametrize("N,C", [(16384, 384), (4096, 1280), (1000, 1536), (777, 2048), (300, 4100), (32768, 1280),
+                                 (8192, 1536), (1, 384), (9, 1280)])
 def test_add_layernorm_full_size_vs_oracle(N, C):
-    """Config 1 (16384 x 384, eps 1e-5) and the other row widths of the path."""
+    """Config 1 (16384 x 384, eps 1e-5), the benchmark step's shape (32768 x 1280: every CTA walks
+    many rows, the grid is one resident wave) and the other row widths of the path."""
     ctx, alloc, be = G.env()
     eps = 1e-5
     x_, r_, g_, b_, dy_ = _cfg1_inputs(N, C)
@@ -169,9 +171,11 @@ def test_gelu_golden(golden, case):
     G.free(x, y)
 
 
-def test_gelu_full_size_vs_oracle():
+@pytest.mark.parametrize("rows,cols", [(16384, 1536), (32768, 5120)])
+def test_gelu_full_size_vs_oracle(rows, cols):
+    """16384 x 1536, and the MLP activation of the benchmark step (32768 x 5120)."""
     rng = np.random.default_rng(1239)
-    x_ = (2.0 * rng.standard_normal((16384, 1536), dtype=np.float32)).astype(np.float32)
+    x_ = (2.0 * rng.standard_normal((rows, cols), dtype=np.float32)).astype(np.float32)
     x_[0, :8] = [0.0, -0.0, 30.0, -30.0, 1e-20, -1e-20, 9.0, -9.0]
     dy_ = rng.standard_normal(x_.shape, dtype=np.float32)
     x = G.up(x_, grad=0)
@@ -222,8 +226,18 @@ def _bf16(a):
 def test_qwen_path_config3_reduced(dtype):
     """Config 3 shapes (C 1536, 12/2 heads x 128, I 8960, eps 1e-6, theta 1e6) at a reduced
     token count, fp32 and bf16 storage, against the fp32 oracle."""
+    _qwen_path(dtype, 2, 192)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_qwen_path_config3_full_size(dtype):
+    """Config 3 at its stated size: batch 4 x seq 2048 = 8192 token rows, positions 0..2047."""
+    _qwen_path(dtype, 4, 2048)
+
+
+def _qwen_path(dtype, B, T):
     ctx, alloc, be = G.env()
-    B, T, C, H, HKV, D, I, eps = 2, 192, 1536, 12, 2, 128, 8960, 1e-6
+    C, H, HKV, D, I, eps = 1536, 12, 2, 128, 8960, 1e-6
     N = B * T
     rng = np.random.default_rng(1236)
     bf = dtype == "bf16"
@@ -921,9 +935,21 @@ def test_fused_layer_step_matches_oracle():
     their backward passes with the fused residual-gradient add, scatter-add into the tied table), at a
     small size, replayed with the oracle on the same buffers: loss, every dgamma/dbeta, the tied
     table gradient, the residual-stream gradient and the in-place rotated q/k must agree."""
-    from autograd_b200.step import FusedLayerStep, StepConfig
+    from autograd_b200.step import StepConfig
+    _step_vs_oracle(StepConfig(n_layer=2, n_embd=128, n_head=1, head_dim=128, seq_len=64, batch=3, vocab=640))
+
+
+def test_fused_layer_step_bench_width_matches_oracle():
+    """The same replay at the width bench.py runs: n_embd 1280, 10 heads x 128, seq 2048, vocab 32768,
+    MLP 5120, two layers, 10 sequences = 20480 token rows (more than one 18944-row tile of the CE head,
+    so both row tiles occur; every norm / RoPE / GELU kernel takes its persistent multi-row path)."""
+    from autograd_b200.step import StepConfig
+    _step_vs_oracle(StepConfig(n_layer=2, n_embd=1280, n_head=10, head_dim=128, seq_len=2048, batch=10, vocab=32768))
+
+
+def _step_vs_oracle(cfg):
+    from autograd_b200.step import FusedLayerStep
     ctx, alloc, be = G.env()
-    cfg = StepConfig(n_layer=2, n_embd=128, n_head=1, head_dim=128, seq_len=64, batch=3, vocab=640)
     st = FusedLayerStep(ctx, alloc, be, cfg, seed=77)
     Nn, C, V, L, I = st.N, st.C, st.V, st.L, st.I
     B, T, H, D = cfg.batch, cfg.seq_len, cfg.n_head, cfg.head_dim
@@ -986,3 +1012,98 @@ def test_fused_layer_step_matches_oracle():
     assert_close(get(st.q, (B, T, H, D)), q, TOL_FWD * 4, "q after the step")
     assert_close(get(st.h_final, (Nn, C)), hf, TOL_FWD, "final residual stream")
     st.close()
+
+
+# ------------------------------------------------------------------------------ shapes of the benchmark step
+def test_rope_step_shape_vs_oracle():
+    """RoPE as the benchmark step runs it: 16 sequences x 2048 positions, q and k with 10 heads x 128,
+    theta 1e5, the nanochat sign forward and its transpose backward (flat work distribution, several
+    packet pairs per thread)."""
+    ctx, alloc, be = G.env()
+    B, T, H, D = 16, 2048, 10, 128
+    rng = np.random.default_rng(1243)
+    q_ = rng.standard_normal((B, T, H, D), dtype=np.float32)
+    k_ = rng.standard_normal((B, T, H, D), dtype=np.float32)
+    cos_, sin_ = O.rope_tables(T, D, 1e5)
+    q, k, cos, sin = G.up(q_), G.up(k_), G.up(cos_), G.up(sin_)
+    be.rope_qk(q, k, cos, sin, sin_sign=-1)
+    q1, k1 = O.rope_apply(q_, cos_, sin_, -1), O.rope_apply(k_, cos_, sin_, -1)
+    assert_close(G.down(q), q1, TOL_FWD, "q forward")
+    assert_close(G.down(k), k1, TOL_FWD, "k forward")
+    be.rope_qk(q, k, cos, sin, sin_sign=+1)
+    assert_close(G.down(q), O.rope_apply(q1, cos_, sin_, +1), TOL_FWD, "q backward")
+    assert_close(G.down(k), O.rope_apply(k1, cos_, sin_, +1), TOL_FWD, "k backward")
+    G.check_clean_status()
+    G.free(q, k, cos, sin)
+
+
+def test_rmsnorm_flce_qwen_shape_tensor_core():
+    """FusedRMSNormLinearCrossEntropyOp (backend.py:716-886) on the tensor-core path (3xTF32) at the
+    Qwen shape - hidden 1536, vocabulary 151936 (38 panels of 4096), eps 1e-6 - with row_scale
+    (rl_autograd.py:518-524), targets of -1 and targets >= V (both ignored, backend.py:768;
+    debug/check_qwen_kernel.py:872-874), on 2048 token rows."""
+    ctx, alloc, be = G.env()
+    rng = np.random.default_rng(1244)
+    B, T, C, V, eps = 1, 2048, 1536, 151936, 1e-6
+    N = B * T
+    X_ = rng.standard_normal((B, T, C), dtype=np.float32)
+    W_ = (0.02 * rng.standard_normal((V, C), dtype=np.float32)).astype(np.float32)
+    G_ = (1 + 0.02 * rng.standard_normal(C)).astype(np.float32)
+    Y_ = rng.integers(0, V, size=(B, T)).astype(np.int32)
+    Y_[0, ::19] = -1
+    Y_[0, 5::23] = V
+    Y_[0, 7] = V + 1000
+    rs_ = (rng.random((B, T)).astype(np.float32) * (2.0 / N)).astype(np.float32)
+    assert be.ce_precision == 1 and be.ce_vocab_chunk == 4096
+    x, w, gam = G.up(X_, grad=0), G.up(W_, grad=0), G.up(G_, grad=0)
+    y, rs = G.up(Y_, requires_grad=False), G.up(rs_, requires_grad=False)
+    loss = G.empty((1,), grad=np.array([1.0], np.float32))
+    n = G.node("FusedRMSNormLinearCrossEntropyOp", [x, w, gam, y, rs], (loss,), eps=eps)
+    G.run_forward(n)
+    G.run_backward(n)
+    ref = O.rmsnorm_flce(X_[0], W_, G_, Y_[0], eps, row_scale=rs_[0])
+    got = float(G.down(loss)[0])
+    assert abs(got - float(ref["loss"])) <= TOL_FWD * abs(got), (got, float(ref["loss"]))
+    dX = G.down(x.grad)[0]
+    assert_close(dX, ref["dX"], TOL_BWD, "dX")
+    assert_close(G.down(w.grad), ref["dW"], TOL_BWD, "dW")
+    assert_close(G.down(gam.grad), ref["dG"], TOL_BWD, "dG")
+    ignored = (Y_[0] < 0) | (Y_[0] >= V)
+    assert ignored.sum() > 150 and not dX[ignored].any()          # ignored rows: exactly zero gradient
+    # out-of-range targets are reported through the status word and are otherwise treated as ignored
+    ctx.synchronize()
+    flags = ctx.status()
+    assert flags in (0, 1), flags
+    G.free(x, w, gam, y, rs, loss)
+
+
+def test_staging_wait_that_gives_up_takes_the_plain_load_path():
+    """A bounded wait run to expiry, safely: with the test hook the next norm kernel treats its wait for
+    the bulk-copied gamma/beta as expired at once.  The kernel must set AG_STATUS_STAGE_FALLBACK, let the
+    copy land, fill the vectors with plain loads, return by itself and still produce correct results."""
+    import autograd_b200 as ag
+    ctx, alloc, be = G.env()
+    N, C, eps = 3000, 1280, 1e-5
+    x_, r_, g_, b_, dy_ = _cfg1_inputs(N, C, seed=1245)
+    x, r, gamma, beta = G.up(x_), G.up(r_), G.up(g_, grad=0), G.up(b_, grad=0)
+    h, y = G.empty((N, C), grad=0), G.empty((N, C), grad=dy_)
+    assert ctx.status() == 0
+    ctx.debug_expire_staging()
+    be.fused_add_layernorm_forward(x, r, gamma, beta, h, y, eps)
+    ctx.synchronize()
+    assert ctx.status() == ag.AG_STATUS_STAGE_FALLBACK
+    h_ref, y_ref, _, _ = O.add_layernorm_forward(x_, r_, g_, b_, eps)
+    assert_close(G.down(y), y_ref, TOL_FWD, "y after the fallback")
+    ctx.debug_expire_staging()
+    ln = G.node("LayerNormOp", (h, gamma, beta), (y,), eps=eps, normalized_dim=-1)
+    G.run_backward(ln)
+    ctx.synchronize()
+    assert ctx.status() == ag.AG_STATUS_STAGE_FALLBACK
+    dh_ref, dg_ref, db_ref = O.layernorm_backward(h_ref, g_, dy_, eps, np.zeros_like(x_), np.zeros_like(g_), np.zeros_like(b_))
+    assert_close(G.down(h.grad), dh_ref, TOL_BWD, "dh after the fallback")
+    assert_close(G.down(gamma.grad), dg_ref, TOL_BWD, "dgamma after the fallback")
+    # the hook is one-shot: the next launch stages normally
+    be.fused_add_layernorm_forward(x, r, gamma, beta, h, y, eps)
+    ctx.synchronize()
+    assert ctx.status() == 0
+    G.free(x, r, gamma, beta, h, y)
