@@ -64,8 +64,10 @@ extern "C" int ag_ctx_create(int device, void* stream, ag_ctx** out) {
     // AG_B200_TC_PAIR=0 runs the tensor-core GEMMs on single CTAs (diagnostics)
     e = getenv("AG_B200_TC_PAIR");
     c->tc_pair = (e && e[0] == '0') ? 0 : 1;
+    // AG_B200_NORM_RING: 0 = rows in registers everywhere, 1 = the shared-memory row ring wherever the
+    // shape fits, unset = the measured choice per shape (diagnostics, A/B measurements)
     e = getenv("AG_B200_NORM_RING");
-    c->norm_ring = (e && e[0] == '0') ? 0 : 1;
+    c->norm_ring = !e ? 2 : (e[0] == '0' ? 0 : 1);
     c->debug_stage_expire = 0;
   }
   CREATE_CUDA(cudaMalloc(&c->d_status, sizeof(int)));

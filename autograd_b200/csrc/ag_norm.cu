@@ -505,16 +505,18 @@ norm_partials_reduce_kernel(const float* __restrict__ partials, int P, int C, fl
   if (!out) return;  // uniform per block
   float t = 0.0f;
   if (c < C) {
-    // eight loads in flight per thread, added in row order
-    int p = threadIdx.y;
-    for (; p + 7 * 32 < P; p += 8 * 32) {
+    // eight loads in flight per thread, added in row order; rows past the end contribute +0, which
+    // leaves the sum's bits as they are
+    for (int p = threadIdx.y; p < P; p += 8 * 32) {
       float v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = partials[((int64_t)(p + j * 32) * 2 + slot) * C + c];
+      for (int j = 0; j < 8; ++j) {
+        const int q = p + j * 32;
+        v[j] = q < P ? partials[((int64_t)q * 2 + slot) * C + c] : 0.0f;
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) t += v[j];
     }
-    for (; p < P; p += 32) t += partials[((int64_t)p * 2 + slot) * C + c];
   }
   s[threadIdx.y][threadIdx.x] = t;
   __syncthreads();
@@ -533,18 +535,19 @@ norm_partials_reduce_kernel(const float* __restrict__ partials, int P, int C, fl
 // warp has in flight and the bytes it computes on compete for the same registers, and with wide
 // rows only one CTA fits an SM.  Here the rows in flight live in shared memory instead: one
 // producer lane per CTA issues a 1-D bulk copy per operand row into a ring of R slots
-// (mbarrier complete_tx), eight consumer warps take the rows in turn, and a slot goes back to
-// the producer (a second mbarrier) as soon as its row has been read.  Registers then hold only
+// (mbarrier complete_tx), the consumer warps (eight, fewer for wide rows) take the rows in turn,
+// two slots each, and a slot goes back to the producer (a second mbarrier) as soon as its row has
+// been read.  Registers then hold only
 // the row being computed and the dgamma/dbeta column sums.  Every CTA owns whole rows: CTA b
 // takes rows b, b + grid, b + 2*grid, ...; local row j sits in slot j % R.
 //
 // Every wait is bounded.  When one runs out the CTA sets AG_STATUS_WAIT_EXPIRED, all roles leave
 // their loops, the producer gives the copies it has issued a last bounded wait to land, and the
 // kernel returns.
-constexpr int RING_CONSUMERS = 8;
-constexpr int RING_THREADS = (RING_CONSUMERS + 1) * 32;  // + the producer warp
-constexpr int RING_MAX_SLOTS = 16;
-constexpr uint32_t RING_POLL_LIMIT = 1u << 20;
+constexpr int RING_MAX_CONSUMERS = 8;                        // consumer warps per CTA (fewer for wide rows)
+constexpr int RING_MAX_THREADS = (RING_MAX_CONSUMERS + 1) * 32;  // + the producer warp
+constexpr int RING_MAX_SLOTS = 16;                           // two slots per consumer warp
+constexpr uint32_t RING_POLL_LIMIT = 1u << 18;  // polls with back-off: tens of milliseconds
 constexpr int RING_MAX_PER_LANE = 48;  // row elements per lane (C <= 1536)
 
 struct __align__(16) RingHeader {
@@ -557,7 +560,8 @@ struct __align__(16) RingHeader {
 constexpr size_t kRingHeaderBytes = (sizeof(RingHeader) + 127) / 128 * 128;
 
 struct RingPlan {
-  int slots;            // R
+  int slots;            // R = 2 * consumers
+  int consumers;        // consumer warps; the CTA has one more warp, the producer
   uint32_t row_bytes;   // bytes of one operand row
   uint32_t slot_bytes;  // operand rows per slot * row_bytes
   size_t vec_bytes;     // staged fp32 vectors (gamma, beta)
@@ -565,17 +569,24 @@ struct RingPlan {
   size_t smem;          // total dynamic shared memory
 };
 
-// Ring of up to 16 slots.  Narrow rows get a small ring so that several CTAs share an SM (more
-// warps to hide the row reductions behind); wide rows get as many slots as one CTA per SM can hold.
-inline RingPlan ring_plan(int C, size_t elem_bytes, int rows_per_slot, int n_vectors, size_t fold_bytes) {
+// Two slots per consumer warp: while a warp computes on one row its next row is in flight.  A slot
+// is always consumed by the same warp (slot s belongs to warp s % consumers), see ring_wait_full.
+// Narrow rows: 8 consumer warps, 16 slots, small enough that several CTAs share an SM.  Wide rows:
+// one CTA per SM and as many consumer warps (at most 8) as 200 KB of slots allow.
+inline RingPlan ring_plan(int C, size_t elem_bytes, int rows_per_slot, int n_vectors, int fold_slots) {
   RingPlan p;
   p.row_bytes = (uint32_t)((size_t)C * elem_bytes);
   p.slot_bytes = p.row_bytes * (uint32_t)rows_per_slot;
   p.vec_bytes = ((size_t)n_vectors * C * sizeof(float) + 127) / 128 * 128;
-  const size_t budget = p.slot_bytes >= 8192 ? (size_t)168 * 1024 : (size_t)64 * 1024;
-  int r = (int)(budget / p.slot_bytes);
-  if (r > RING_MAX_SLOTS) r = RING_MAX_SLOTS;
-  if (r < RING_CONSUMERS) r = 0;  // too wide for this scheme (see ring_wait_full): the caller falls back
+  int cw = RING_MAX_CONSUMERS;
+  if (p.slot_bytes >= 8192) {
+    const size_t fit = ((size_t)200 * 1024) / ((size_t)2 * p.slot_bytes);
+    if (fit < (size_t)cw) cw = (int)fit;
+  }
+  if (cw < 3) cw = 0;  // too wide for this scheme: the caller falls back
+  const int r = 2 * cw;
+  p.consumers = cw;
+  const size_t fold_bytes = (size_t)cw * fold_slots * C * sizeof(float);
   p.slots = r;
   p.ring_bytes = (size_t)r * p.slot_bytes;
   if (p.ring_bytes < fold_bytes) p.ring_bytes = fold_bytes;
@@ -630,16 +641,11 @@ __device__ __forceinline__ void ring_produce(RingHeader* hd, unsigned char* ring
 }
 
 // Consumer side of a slot: every lane polls, the warp takes one decision.
-// A parity wait only tells "the phase with this parity is over" if the barrier is at most one phase
-// behind.  Slot s is filled for round k only after the row of round k-1 was consumed, possibly by
-// another warp, and bulk copies may land out of order, so a warp can get here while round k-1 of
-// this slot is still in flight: it first waits for that phase (normally over long ago), then for
-// its own.  With at least RING_CONSUMERS slots round k-2 is always over by then (the producer
-// waited for its consumer before issuing round k-1, and this warp's previous row was issued later).
+// A parity wait can only tell the current phase of a barrier from the one just before it, so a slot
+// must always be consumed by the same warp, which then meets its phases strictly in order: the ring
+// has two slots per consumer warp and rows go to the warps round-robin.
 __device__ __forceinline__ bool ring_wait_full(RingHeader* hd, uint32_t slot, uint32_t round) {
-  bool ok = true;
-  if (round > 0) ok = ag_mbar_wait_bounded(&hd->full[slot], (round - 1) & 1u, RING_POLL_LIMIT);
-  ok = ok && ag_mbar_wait_bounded(&hd->full[slot], round & 1u, RING_POLL_LIMIT);
+  const bool ok = ag_mbar_wait_bounded(&hd->full[slot], round & 1u, RING_POLL_LIMIT);
   return __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
 }
 
@@ -657,10 +663,10 @@ __device__ __forceinline__ void ring_drain(RingHeader* hd, int R, int* status) {
 
 // ---- forward --------------------------------------------------------------------------
 template <typename T, int KP, int KIND>
-__global__ void __launch_bounds__(RING_THREADS, 1)
+__global__ void __launch_bounds__(RING_MAX_THREADS, 1)
 norm_forward_ring_kernel(const T* x, const T* r, const float* __restrict__ gamma, const float* __restrict__ beta, T* h,
                          T* __restrict__ y, float* __restrict__ stat0, float* __restrict__ stat1, int64_t N, int C,
-                         float eps, int R, uint32_t slot_bytes, uint32_t stage_poll_limit, int* status, int pdl_early) {
+                         float eps, int R, int CW, uint32_t slot_bytes, uint32_t stage_poll_limit, int* status, int pdl_early) {
   ag_pdl_wait();
   if (pdl_early) ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
@@ -682,7 +688,7 @@ norm_forward_ring_kernel(const T* x, const T* r, const float* __restrict__ gamma
   const unsigned char* gx = reinterpret_cast<const unsigned char*>(x);
   const unsigned char* gr = reinterpret_cast<const unsigned char*>(r);
   // the first rows are requested before gamma/beta are staged, so both transfers overlap
-  if (warp == RING_CONSUMERS) {
+  if (warp == CW) {
     if (lane == 0)
       ring_produce(hd, ring, R, slot_bytes, row_bytes, gx, gr, nullptr, first_row, gridDim.x, 0u, n_first, status);
     __syncwarp();
@@ -692,12 +698,12 @@ norm_forward_ring_kernel(const T* x, const T* r, const float* __restrict__ gamma
                      stage_poll_limit);
   volatile int* abort_flag = &hd->abort;
 
-  if (warp == RING_CONSUMERS) {
+  if (warp == CW) {
     if (lane == 0)
       ring_produce(hd, ring, R, slot_bytes, row_bytes, gx, gr, nullptr, first_row, gridDim.x, n_first, n_local, status);
     __syncwarp();
   } else {
-    for (uint32_t j = (uint32_t)warp; j < n_local; j += RING_CONSUMERS) {
+    for (uint32_t j = (uint32_t)warp; j < n_local; j += (uint32_t)CW) {
       if (__any_sync(0xffffffffu, *abort_flag)) break;
       const uint32_t slot = j % (uint32_t)R;
       if (!ring_wait_full(hd, slot, j / (uint32_t)R)) {
@@ -800,7 +806,7 @@ norm_forward_ring_kernel(const T* x, const T* r, const float* __restrict__ gamma
     }
   }
   __syncthreads();
-  if (*abort_flag && warp == RING_CONSUMERS && lane == 0) ring_drain(hd, R, status);
+  if (*abort_flag && warp == CW && lane == 0) ring_drain(hd, R, status);
 }
 
 // ---- backward -------------------------------------------------------------------------
@@ -808,11 +814,11 @@ norm_forward_ring_kernel(const T* x, const T* r, const float* __restrict__ gamma
 // registers (C/32 values per lane and sum), x-hat of the current row too; dy is read from the slot
 // twice (column/row sums, then dx) rather than kept.
 template <typename T, int KP, int KIND>
-__global__ void __launch_bounds__(RING_THREADS, 1)
+__global__ void __launch_bounds__(RING_MAX_THREADS, 1)
 norm_backward_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
                           const T* dres, T* dx, float* __restrict__ partials, int want_dgamma, int want_dbeta,
-                          int64_t N, int C, float eps, int R, uint32_t slot_bytes, uint32_t stage_poll_limit,
-                          int* status, int pdl_early) {
+                          int64_t N, int C, float eps, int R, int CW, uint32_t slot_bytes,
+                          uint32_t stage_poll_limit, int* status, int pdl_early) {
   ag_pdl_wait();
   if (pdl_early) ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
@@ -835,7 +841,7 @@ norm_backward_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
   const unsigned char* gx = reinterpret_cast<const unsigned char*>(x);
   const unsigned char* gdy = reinterpret_cast<const unsigned char*>(dy);
   const unsigned char* gres = with_res ? reinterpret_cast<const unsigned char*>(dres) : nullptr;
-  if (warp == RING_CONSUMERS) {
+  if (warp == CW) {
     if (lane == 0)
       ring_produce(hd, ring, R, slot_bytes, row_bytes, gx, gdy, gres, first_row, gridDim.x, 0u, n_first, status);
     __syncwarp();
@@ -852,12 +858,12 @@ norm_backward_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
       if constexpr (KIND == kLayerNorm) acc_b[p][e] = 0.0f;
     }
 
-  if (warp == RING_CONSUMERS) {
+  if (warp == CW) {
     if (lane == 0)
       ring_produce(hd, ring, R, slot_bytes, row_bytes, gx, gdy, gres, first_row, gridDim.x, n_first, n_local, status);
     __syncwarp();
   } else {
-    for (uint32_t j = (uint32_t)warp; j < n_local; j += RING_CONSUMERS) {
+    for (uint32_t j = (uint32_t)warp; j < n_local; j += (uint32_t)CW) {
       if (__any_sync(0xffffffffu, *abort_flag)) break;
       const uint32_t slot = j % (uint32_t)R;
       if (!ring_wait_full(hd, slot, j / (uint32_t)R)) {
@@ -981,12 +987,12 @@ norm_backward_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
   // the ring is reused for the fold
   __syncthreads();
   if (*abort_flag) {
-    if (warp == RING_CONSUMERS && lane == 0) ring_drain(hd, R, status);
+    if (warp == CW && lane == 0) ring_drain(hd, R, status);
     __syncthreads();
   }
   // fold the warps' column sums in warp order: [warp][slot][C] floats in the ring's memory
   float* s_fold = reinterpret_cast<float*>(ring);
-  if (warp < RING_CONSUMERS) {
+  if (warp < CW) {
     float* my_g = s_fold + (size_t)warp * SLOTS * C;
     float* my_b = my_g + C;
 #pragma unroll
@@ -1006,10 +1012,9 @@ norm_backward_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
     const bool wanted = slot == 0 ? (want_dgamma != 0) : (want_dbeta != 0);
     if (!wanted) continue;  // uniform across the CTA
     float* out = partials + ((int64_t)blockIdx.x * 2 + slot) * C;
-    for (int c = threadIdx.x; c < C; c += RING_THREADS) {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
       float t = 0.0f;
-#pragma unroll
-      for (int w = 0; w < RING_CONSUMERS; ++w) t += s_fold[((size_t)w * SLOTS + slot) * C + c];
+      for (int w = 0; w < CW; ++w) t += s_fold[((size_t)w * SLOTS + slot) * C + c];
       out[c] = t;
     }
   }
@@ -1080,8 +1085,18 @@ inline uint32_t take_stage_poll_limit(ag_ctx* ctx) {
   return limit;
 }
 
-inline bool ring_applies(const ag_ctx* ctx, int kp, int nv, int64_t N) {
-  return ctx->norm_ring && kp > 0 && kp * nv <= RING_MAX_PER_LANE && N < (1ll << 31);
+// Which shapes take the row ring.  Measured on B200 (back-to-back launches, operands rotated through
+// more buffers than fit in L2): with fp32 storage both designs reach the same HBM rate on long
+// inputs (32768 x 1280: 0.92 / 0.91 of the copy rate forward / backward with rows in registers, 0.86 /
+// 0.92 through the ring) and the register kernels win on short ones (16384 x 384 backward 0.68 vs
+// 0.60), so fp32 keeps them except for the widest rows in backward (C 1536: 0.71 vs 0.69).  With bf16
+// storage a lane's 16-byte packet holds half as many bytes per element in flight; there the ring wins
+// (8192 x 1536: forward 0.57 vs 0.53, backward 0.48 vs 0.38).  ctx->norm_ring: 0 never, 1 always where
+// the shape fits, 2 (default) this policy.
+inline bool ring_applies(const ag_ctx* ctx, int kp, int nv, int64_t N, bool backward) {
+  if (!ctx->norm_ring || kp <= 0 || kp * nv > RING_MAX_PER_LANE || N >= (1ll << 31)) return false;
+  if (ctx->norm_ring == 1) return true;
+  return nv == 8 || (backward && kp * nv >= 48);
 }
 
 template <typename T, int KIND, int KP>
@@ -1092,18 +1107,19 @@ int launch_fwd_ring_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, 
   } else {
     const RingPlan plan = ring_plan(C, sizeof(T), r ? 2 : 1, KIND == kLayerNorm ? 2 : 1, 0);
     if (plan.slots == 0) return -1;
+    const int threads = (plan.consumers + 1) * 32;
     auto kern = norm_forward_ring_kernel<T, KP, KIND>;
     static int occ_cache[AG_MAX_DEVICES] = {};
     static size_t occ_smem[AG_MAX_DEVICES] = {};
     const int occ = resident_ctas(ctx, kern, plan.smem, &occ_cache[ag_dev_slot(ctx)], &occ_smem[ag_dev_slot(ctx)],
-                                  RING_THREADS);
+                                  threads);
     if (occ < 0)
       AG_FAIL(ctx, AG_ERR_CUDA, "norm_forward_ring_kernel: occupancy query failed: %s",
               cudaGetErrorString(cudaGetLastError()));
     const int64_t cap = (int64_t)ctx->sm_count * (occ > 8 ? 8 : occ);
     const int grid = (int)(N < cap ? N : cap);
-    AG_LAUNCH_PDL(ctx, "norm_forward_ring_kernel", kern, grid, RING_THREADS, plan.smem, x, r, gamma, beta, h, y, s0, s1,
-                  N, C, eps, plan.slots, plan.slot_bytes, take_stage_poll_limit(ctx), ctx->d_status, 1);
+    AG_LAUNCH_PDL(ctx, "norm_forward_ring_kernel", kern, grid, threads, plan.smem, x, r, gamma, beta, h, y, s0, s1,
+                  N, C, eps, plan.slots, plan.consumers, plan.slot_bytes, take_stage_poll_limit(ctx), ctx->d_status, 1);
     return AG_OK;
   }
 }
@@ -1114,7 +1130,7 @@ int launch_fwd(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const fl
   constexpr int NV = Pack<T>::N;
   const bool vec_ok = (C % NV == 0) && ag_aligned16(x) && ag_aligned16(r) && ag_aligned16(h) && ag_aligned16(y);
   const int kp = vec_ok ? pick_kp(C / NV) : 0;
-  if (ring_applies(ctx, kp, NV, N)) {
+  if (ring_applies(ctx, kp, NV, N, false)) {
     int rc = -1;
 #define AG_FWD_RING_CASE(K)                                                                   \
   case K:                                                                                     \
@@ -1176,22 +1192,22 @@ int launch_bwd_ring_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma,
   if constexpr (KP * Pack<T>::N > RING_MAX_PER_LANE) {
     AG_FAIL(ctx, AG_ERR_INVALID, "norm_backward_ring_kernel: row too wide");
   } else {
-    const size_t fold_bytes = (size_t)RING_CONSUMERS * norm_bwd_slots<KIND>() * C * sizeof(float);
-    const RingPlan plan = ring_plan(C, sizeof(T), (dres && dx) ? 3 : 2, 1, fold_bytes);
+    const RingPlan plan = ring_plan(C, sizeof(T), (dres && dx) ? 3 : 2, 1, norm_bwd_slots<KIND>());
     if (plan.slots == 0) return -1;
+    const int threads = (plan.consumers + 1) * 32;
     auto kern = norm_backward_ring_kernel<T, KP, KIND>;
     static int occ_cache[AG_MAX_DEVICES] = {};
     static size_t occ_smem[AG_MAX_DEVICES] = {};
     const int occ = resident_ctas(ctx, kern, plan.smem, &occ_cache[ag_dev_slot(ctx)], &occ_smem[ag_dev_slot(ctx)],
-                                  RING_THREADS);
+                                  threads);
     if (occ < 0)
       AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_ring_kernel: occupancy query failed: %s",
               cudaGetErrorString(cudaGetLastError()));
     int64_t cap = (int64_t)ctx->sm_count * (occ > 8 ? 8 : occ);
     if (cap > max_grid) cap = max_grid;
     const int grid = (int)(N < cap ? N : cap);
-    AG_LAUNCH_PDL(ctx, "norm_backward_ring_kernel", kern, grid, RING_THREADS, plan.smem, dy, x, gamma, dres, dx, partials,
-                  wg, wb, N, C, eps, plan.slots, plan.slot_bytes, take_stage_poll_limit(ctx), ctx->d_status, 1);
+    AG_LAUNCH_PDL(ctx, "norm_backward_ring_kernel", kern, grid, threads, plan.smem, dy, x, gamma, dres, dx, partials,
+                  wg, wb, N, C, eps, plan.slots, plan.consumers, plan.slot_bytes, take_stage_poll_limit(ctx), ctx->d_status, 1);
     *grid_out = grid;
     return AG_OK;
   }
@@ -1221,7 +1237,7 @@ int launch_bwd(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T
   const int kp = vec_ok ? pick_kp(C / NV) : 0;
   int grid = 0;
   int rc = -1;
-  if (ring_applies(ctx, kp, NV, N)) {
+  if (ring_applies(ctx, kp, NV, N, true)) {
 #define AG_BWD_RING_CASE(K)                                                                                          \
   case K:                                                                                                            \
     rc = launch_bwd_ring_kp<T, KIND, K>(ctx, dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, max_grid, &grid);  \

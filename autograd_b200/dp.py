@@ -59,24 +59,63 @@ class GradAllReducer:
         gradients are those of the mean over the global batch."""
         return 1.0 / self.world_size
 
-    def reduce(self):
+    def reduce(self, timer=None):
+        """One allreduce(sum) per bucket.  `timer`: an optional `CommTimer`; each collective (with the
+        pack / unpack of its wire form, if any) is then bracketed by a device-side event pair."""
         if self.world_size == 1:
             return
-        for b, w in zip(self.buckets, self.wires):
+        for i, (b, w) in enumerate(zip(self.buckets, self.wires)):
+            if timer is not None:
+                timer.begin(f"bucket{i}")
             if w is None:
                 self._dist.all_reduce(b, op=self._dist.ReduceOp.SUM, group=self.group)
             else:
                 w.pack()
                 self._dist.all_reduce(w.tensor, op=self._dist.ReduceOp.SUM, group=self.group)
                 w.unpack()
+            if timer is not None:
+                timer.end()
 
     def mean_loss(self, loss_tensor):
-        """Global mean of the per-rank mean losses (equal token counts per rank)."""
+        """Global mean of the per-rank mean losses (equal token counts per rank) by an allreduce of its
+        own.  A caller that keeps the loss scalar inside one of the gradient buckets gets its sum from
+        `reduce()` already and only divides by `world_size`."""
         if self.world_size == 1:
             return loss_tensor
         self._dist.all_reduce(loss_tensor, op=self._dist.ReduceOp.SUM, group=self.group)
         loss_tensor /= self.world_size
         return loss_tensor
+
+
+class CommTimer:
+    """Device-side timing of collectives: an event pair on the current CUDA stream around each one
+    (the process group's own stream is ordered against it on both sides), summed per name."""
+
+    def __init__(self):
+        import torch
+        self._torch = torch
+        self._open = None
+        self._pairs = []
+
+    def begin(self, name):
+        e0 = self._torch.cuda.Event(enable_timing=True)
+        e0.record()
+        self._open = (name, e0)
+
+    def end(self):
+        name, e0 = self._open
+        e1 = self._torch.cuda.Event(enable_timing=True)
+        e1.record()
+        self._pairs.append((name, e0, e1))
+        self._open = None
+
+    def totals_ms(self):
+        """name -> milliseconds summed over every bracketed collective; synchronises the device."""
+        self._torch.cuda.synchronize()
+        out = {}
+        for name, e0, e1 in self._pairs:
+            out[name] = out.get(name, 0.0) + float(e0.elapsed_time(e1))
+        return out
 
 
 class Bf16Wire:

@@ -103,9 +103,11 @@ class FusedLayerStep:
         self.gamma = self._dev((self.n_norms, C), f32, host=gam)
         self.beta = self._dev((self.n_norms, C), f32, host=bet)
         # gradient buckets (contiguous, so that one allreduce covers each)
-        self.small_bucket = self._dev((self.n_norms * 2 * C,), f32)    # [dgamma | dbeta] per norm
+        # [dgamma | dbeta] per norm, then the loss scalar: one small allreduce carries all of them
+        self.n_small = self.n_norms * 2 * C
+        self.small_bucket = self._dev((self.n_small + 4,), f32)
+        self.loss = self.small_bucket + self.n_small * 4
         self.dtable = self._dev((V, C), f32)                           # dW_vocab == embedding grad (tied)
-        self.loss = self._dev((1,), f32)
         self.dloss = self._dev((1,), f32)
         # RoPE tables (module.py:146-156)
         pos = np.arange(c.seq_len, dtype=f32)[:, None]
@@ -217,7 +219,7 @@ class FusedLayerStep:
         ctx, t, c = self.ctx, self.timer, self.cfg
         Nn, C, V, L, I = self.N, self.C, self.V, self.L, self.I
         k = t.begin("zero_grads")
-        ctx.fill_f32(self.small_bucket, 0.0, self.n_norms * 2 * C)
+        ctx.fill_f32(self.small_bucket, 0.0, self.n_small)       # not the loss word behind the gradients
         ctx.fill_f32(self.dtable, 0.0, V * C)
         ctx.fill_f32(self.dy[0], 0.0, Nn * C)      # gradient of the final norm's output: written by the head
         t.end(k)
@@ -254,13 +256,16 @@ class FusedLayerStep:
         self.forward()
         self.backward()
 
-    def read_loss(self) -> float:
-        return float(self.ctx.copy_to_host(self.loss, (1,), np.float32)[0])
+    def read_loss(self, world: int = 1) -> float:
+        """Device -> host read of the loss; after a data-parallel reduce the word holds the sum of the
+        ranks' mean losses, `world` turns it into the global mean."""
+        return float(self.ctx.copy_to_host(self.loss, (1,), np.float32)[0]) / world
 
     def grad_buckets(self):
-        """(address, n_floats) of the two contiguous gradient buckets a data-parallel
-        allreduce covers: all dgamma/dbeta, and the tied dW_vocab / embedding gradient."""
-        return [(self.small_bucket, self.n_norms * 2 * self.C), (self.dtable, self.V * self.C)]
+        """(address, n_floats) of the two contiguous buckets a data-parallel allreduce covers: all
+        dgamma/dbeta followed by the loss scalar (the sum of the ranks' mean losses; divide by the
+        world size), and the tied dW_vocab / embedding gradient."""
+        return [(self.small_bucket, self.n_small + 1), (self.dtable, self.V * self.C)]
 
     # ------------------------------------------------------------------ accounting
     def algorithmic_bytes(self):

@@ -53,9 +53,12 @@ def parse_args():
                     help="step: the fused-layer step (the benchmark); kernels: one JSON line per fused layer "
                          "kernel at the shapes of BASELINE configs 1-4, each against its own roofline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-config-kernels", action="store_true",
+                    help="step workload: skip the per-kernel timings at the shapes of configs 1-4 (`configs` key)")
     ap.add_argument("--only", default="", help="--workload kernels: comma-separated sections (cfg1,gelu,cfg3,cfg4,cfg2,next)")
-    ap.add_argument("--cpu-sample-tokens", type=int, default=2048)
-    ap.add_argument("--cpu-sample-layers", type=int, default=2)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=0,
+                    help="token rows of the CPU sample (0: sized so that the CPU run stays within a few minutes)")
+    ap.add_argument("--cpu-sample-layers", type=int, default=2, help="numpy-port fallback only")
     return ap.parse_args()
 
 
@@ -72,6 +75,13 @@ def load_peaks():
 def workload_name(a):
     return (f"gpt_fused_layer_step depth{a.layers} n_embd{a.n_embd} heads{a.n_embd // 128}x128 seq{a.seq_len} "
             f"vocab{a.vocab} batch{a.batch}/gpu")
+
+
+def bench_config(a, world):
+    """The `config` object of the JSON line; both arms (this backend and the CPU reference) print the same one."""
+    return {"workload": workload_name(a), "tokens_per_gpu": a.batch * a.seq_len, "ce_precision": a.ce_precision,
+            "vocab_chunk": 4096, "parallelism": f"dp{world} token-row sharded",
+            "l2": "every streamed buffer is larger than the L2 cache; no flush needed"}
 
 
 # --------------------------------------------------------------------------------------
@@ -136,28 +146,56 @@ def cpu_sample_step(a, tokens, layers, seed=1238):
     return n, total, desc
 
 
+def cpu_reference_sample(a, tokens, warmup, steps):
+    """The fused-layer step on the host with the reference's own CPU backend (`oracle/_ref`, through
+    oracle/ref_timing.py) on a sample of `tokens` token rows at full depth and vocabulary.  Returns
+    (tokens, mean seconds per step, cpu_baseline dict without "value") or None when oracle/_ref is absent."""
+    from oracle import ref_loader
+    if not ref_loader.available():
+        return None
+    from oracle import ref_timing as RT
+    S = RT.FusedLayerStepSample(a.layers, a.n_embd, a.n_embd // 128, 128, a.seq_len, a.vocab, tokens)
+    for _ in range(warmup):
+        S.step()
+    t = [S.step() for _ in range(max(steps, 1))]
+    return S.tokens, sum(t) / len(t), {"unit": UNIT, "cores": S.threads, "kind": "reference", "sample": S.description}
+
+
+def cpu_port_sample(a, tokens):
+    """Fallback when oracle/_ref does not exist: the numpy restatement (oracle/fused_layers.py)."""
+    n, t, desc = cpu_sample_step(a, tokens, a.cpu_sample_layers)
+    return n, t, {"unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                  "sample": desc + f"; numpy restatement of the reference CPU backend (oracle/fused_layers.py), numpy {np.__version__}"}
+
+
 def run_reference(a):
+    """`--impl reference`: the reference's CPU implementation of the path on this host's cores.  Each
+    step is a bounded sample of the workload (fewer token rows; full depth, full vocabulary); `value`
+    is tokens/s of that sample, `ms_per_step` its measured wall time - nothing is extrapolated."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
-    for _ in range(a.warmup):
-        cpu_sample_step(a, a.cpu_sample_tokens, a.cpu_sample_layers)
-    times = []
-    n = a.cpu_sample_tokens
-    for _ in range(a.steps):
-        n, t, desc = cpu_sample_step(a, a.cpu_sample_tokens, a.cpu_sample_layers)
-        times.append(t)
-    ms = 1e3 * sum(times) / len(times)
-    value = n / (ms / 1e3)
+    world = int(os.environ.get("WORLD_SIZE", str(a.gpus)))
+    tokens = a.cpu_sample_tokens
+    if tokens <= 0:
+        # about 3.3 ms per token row and step on 8-16 cores: keep (warmup + steps) steps near two minutes
+        tokens = int(36000 / max(a.steps + a.warmup, 1)) // 256 * 256
+        tokens = min(max(tokens, 256), 2048)
+    res = cpu_reference_sample(a, tokens, a.warmup, a.steps)
+    if res is None:
+        for _ in range(a.warmup):
+            cpu_port_sample(a, tokens)
+        runs = [cpu_port_sample(a, tokens) for _ in range(a.steps)]
+        res = (runs[0][0], sum(r[1] for r in runs) / len(runs), runs[0][2])
+    n, sec, cpu = res
+    value = n / sec
+    cpu["value"] = value
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
-        "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": a.warmup, "ms_per_step": 1e3 * sec, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(a), "sample": desc},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": desc + "; numpy restatement of the reference CPU backend (oracle/), numpy "
-                                   f"{np.__version__}, BLAS threads unrestricted"},
+        "config": bench_config(a, world),
+        "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -256,8 +294,9 @@ def run_b200(a):
     wires = None
     if world > 1 and a.grad_wire == "bf16":  # the small dgamma/dbeta bucket stays fp32
         wires = [None, dp.Bf16Wire.for_device(ctx, alloc, *step.grad_buckets()[1], local)]
+    # two allreduces per step: [all dgamma/dbeta | loss scalar] and the tied table gradient
     reducer = dp.GradAllReducer(buckets, wires=wires) if world > 1 else None
-    loss_t = dp.as_torch(step.loss, 1, local)
+    comm_timer = [None]
     if reducer is not None:
         ctx.fill_f32(step.dloss, reducer.grad_scale, 1)
 
@@ -277,10 +316,9 @@ def run_b200(a):
             load(i)
         step.step()
         if reducer is not None:
-            reducer.reduce()
-            reducer.mean_loss(loss_t)
+            reducer.reduce(comm_timer[0])
         if e2e:
-            return step.read_loss()
+            return step.read_loss(world)
         return None
 
     def barrier():
@@ -323,6 +361,8 @@ def run_b200(a):
     # kernels from overlapping their launch, so this pass is a little slower than the one above.
     step.timer.reset()
     step.timer.enabled = True
+    if reducer is not None:
+        comm_timer[0] = dp.CommTimer()      # an event pair around each allreduce of this pass
     barrier()
     ctx.tc_timing(True, TC_BASE)
     ctx.event_record(EV0)
@@ -333,6 +373,8 @@ def run_b200(a):
     ctx.tc_timing(False)
     ms_breakdown = ctx.event_elapsed_ms(EV0, EV1)
     step.timer.enabled = False
+    comm_ms = comm_timer[0].totals_ms() if comm_timer[0] is not None else {}
+    comm_timer[0] = None
     fam = step.timer.totals_ms()
     tc_n = ctx.tc_timing_count()
     tc_ms = [ctx.event_elapsed_ms(TC_BASE + 2 * i, TC_BASE + 2 * i + 1) for i in range(tc_n)]
@@ -371,20 +413,50 @@ def run_b200(a):
     ms_bf16 = alt_ms.get("bf16")
     ms_x3 = alt_ms.get("bf16x3")
 
+    comm = None
     if world > 1:
+        # per-rank figures: device time of the timed steps, time inside the collectives, time of the
+        # step's own kernels in the breakdown pass
+        fam_ms = sum(v[1] for v in fam.values())
+        mine = torch.tensor([ms_dev, comm_ms.get("bucket0", 0.0), comm_ms.get("bucket1", 0.0), fam_ms],
+                            device=f"cuda:{local}", dtype=torch.float64)
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        per = torch.stack(allr).cpu().numpy() / a.steps
+        comm = {"small_bucket_and_loss_ms": round(float(per[:, 1].max()), 4),
+                "table_gradient_bucket_ms": round(float(per[:, 2].max()), 4),
+                "rank_skew_ms": round(float(per[:, 0].max() - per[:, 0].min()), 4),
+                "per_rank_step_ms": [round(float(v), 3) for v in per[:, 0]],
+                "per_rank_kernel_ms": [round(float(v), 3) for v in per[:, 3]],
+                "note": "CUDA-event pairs around each allreduce in the breakdown pass, max over ranks, per step; the time "
+                        "inside a collective includes waiting for the slowest rank to arrive (the ranks' steps run at "
+                        "the power cap and differ, see per_rank_kernel_ms); rank_skew_ms = max - min over ranks of the "
+                        "device time of the timed steps"}
         t = torch.tensor([ms_dev, ms_e2e, ms_bf16 or 0.0, ms_x3 or 0.0], device=f"cuda:{local}", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e = float(t[0]), float(t[1])
         ms_bf16 = float(t[2]) if ms_bf16 is not None else None
         ms_x3 = float(t[3]) if ms_x3 is not None else None
 
+    # ---- the kernels of BASELINE configs 1-4, each alone at its stated shape (rank 0 of a 1-GPU run):
+    # compact per-kernel figures in the same line, so that they come from the same run as the headline
+    device_bytes = step.device_bytes
+    alg = step.algorithmic_bytes()
+    useful, executed = step.flce_flops()
+    step.close()
+    config_lines = None
+    if world == 1 and not a.no_config_kernels:
+        config_lines = []
+        a_k = argparse.Namespace(**vars(a))
+        a_k.only = "cfg1,cfg3,cfg4,cfg2"
+        run_kernels(a_k, env=(ctx, alloc, be), dev_index=local, collect=config_lines, steps=10, warmup=3,
+                    cfg2_modes=("3xtf32",))
+
     if rank == 0:
         tokens = Nn * world
         ms_step = ms_dev / a.steps
         value = tokens / (ms_step / 1e3)
         e2e_value = tokens / (ms_e2e / a.steps / 1e3)
-        alg = step.algorithmic_bytes()
-        useful, executed = step.flce_flops()
         kernels = {}
         for name, (count, total_ms) in sorted(fam.items()):
             per_step_ms = total_ms / a.steps
@@ -412,18 +484,20 @@ def run_b200(a):
             ach = fl_launch / (avg_ms / 1e3) / 1e12
             mma_per_kstep = 1 if a.ce_precision == "bf16" else 3
             peak = peaks["bf16_tflops_sustained"]
+            nominal = 2250.0 if "bf16" in a.ce_precision else 1125.0
             roofline = {"bound": "tensor", "kernel": "tc_gemm_kernel",
                         "what": "tcgen05 panel GEMM of the fused linear+CE (logits+stats, logits+dlogits, dX, dW)",
                         "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
                         "traffic": None, "launches_per_step": len(tc_ms) // a.steps,
                         "avg_launch_ms": round(avg_ms, 4), "useful_flops_per_launch": fl_launch,
                         "issued_mma_tflops": round(ach * mma_per_kstep, 2),
-                        # MMA issue rate in bf16-equivalent terms (a TF32 MMA takes the tensor pipe twice as
-                        # long as a bf16 one) over the same peak: how busy the tensor pipe is kept
-                        "issued_frac_of_peak": round(ach * mma_per_kstep * (1 if "bf16" in a.ce_precision else 2) / peak, 4),
-                        # the same rate over the nominal dense figure of the part at its maximum clock
-                        # (2250 TFLOP/s bf16, 1125 TF32); the step runs below that clock, at the power cap
-                        "issued_frac_of_nominal": round(ach * mma_per_kstep / (2250.0 if "bf16" in a.ce_precision else 1125.0), 4),
+                        # the issued MMA rate over the nominal dense rate of the part (2250 TFLOP/s bf16, 1125 TF32
+                        # at the maximum SM clock), and over that rate scaled to the SM clock sampled during the
+                        # step (the step runs below the maximum clock, at the power cap): a true ceiling, <= 1
+                        "issued_frac_of_nominal": round(ach * mma_per_kstep / nominal, 4),
+                        "issued_frac_of_nominal_at_sampled_clock": (
+                            round(ach * mma_per_kstep / (nominal * clocks["sm_mhz"] / clocks["sm_max_mhz"]), 4)
+                            if clocks.get("sm_mhz") and clocks.get("sm_max_mhz") else None),
                         "peak_source": peaks["source"] + " cuBLAS bf16, sustained; TF32 MMAs issue at half that "
                                        "rate and 3xTF32 issues three per k-step",
                         "flce_useful_tflops_whole_op": round(useful / t_flce / 1e12, 2),
@@ -451,20 +525,23 @@ def run_b200(a):
 
         cpu = None
         if world == 1 and not a.no_cpu_baseline:
-            n, t, desc = cpu_sample_step(a, a.cpu_sample_tokens, a.cpu_sample_layers)
-            cpu = {"value": n / t, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
-                   "sample": desc + f"; numpy {np.__version__}, one run"}
+            # the reference's own CPU backend on a bounded sample: one warm-up step, one timed step
+            res = cpu_reference_sample(a, a.cpu_sample_tokens or 1024, 1, 1) or cpu_port_sample(a, a.cpu_sample_tokens or 1024)
+            n, sec, cpu = res
+            cpu["value"] = n / sec
+        configs = None
+        if config_lines:
+            configs = [{"config": ln["config"], "kernel": ln["kernel"], "dtype": ln["dtype"], "ms": ln["ms"],
+                        "achieved": ln["roofline"]["achieved"], "unit": ln["roofline"]["unit"], "frac": ln["roofline"]["frac"],
+                        **({"unique_rows": ln["unique_rows"]} if "unique_rows" in ln else {})} for ln in config_lines]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32" if a.ce_precision in ("fp32", "3xtf32") else f"f32 ({a.ce_precision} tensor-core operands in the CE GEMMs)",
             "data": "synthetic",
-            "config": {"workload": workload_name(a), "tokens_per_gpu": Nn, "ce_precision": a.ce_precision,
-                       "vocab_chunk": cfg.ce_vocab_chunk, "parallelism": f"dp{world} token-row sharded",
-                       "l2": "every streamed buffer is larger than the L2 cache; no flush needed",
-                       "device_bytes": step.device_bytes,
-                       "allreduce_bytes_per_step": reducer.bytes_per_step if reducer else 0,
-                       "grad_wire": a.grad_wire if reducer else None},
+            "config": bench_config(a, world),
+            "setup": {"device_bytes": device_bytes, "allreduce_bytes_per_step": reducer.bytes_per_step if reducer else 0,
+                      "allreduces_per_step": 2 if reducer else 0, "grad_wire": a.grad_wire if reducer else None},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * Nn * 4, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / a.steps},
             "gpu_launches": int(launches),
@@ -475,6 +552,12 @@ def run_b200(a):
             "cpu_baseline": cpu,
             "loss": last_loss,
         }
+        if comm is not None:
+            line["comm"] = comm
+        if configs is not None:
+            # frac = achieved / peak of MEASURED_PEAKS.json (HBM copy rate; bf16 burst rate for the CE head); gather
+            # bytes are the unique-row bound
+            line["configs"] = configs
         if ms_bf16 is not None:
             line["ce_bf16_mode"] = {"ms_per_step": ms_bf16 / a.steps, "value": tokens / (ms_bf16 / a.steps / 1e3),
                                     "unit": UNIT, "note": "same step with the CE head's GEMM operands rounded to bf16 "
@@ -485,7 +568,6 @@ def run_b200(a):
                                                             "pairs, three MMAs per k-step at the bf16 rate (measured inside the fp32 bounds "
                                                             "of the path: loss 1e-5, dX and dW 1e-4); not the headline"}
         print(json.dumps(line), flush=True)
-    step.close()
     ctx.free_host(host)
     if world > 1:
         dist.destroy_process_group()
@@ -494,21 +576,42 @@ def run_b200(a):
 # --------------------------------------------------------------------------------------
 # per-kernel measurements at the shapes of BASELINE configs 1-4
 # --------------------------------------------------------------------------------------
-def run_kernels(a):
+def run_kernels(a, env=None, dev_index=0, collect=None, steps=None, warmup=None, cfg2_modes=None, with_cpu=False):
     """Each kernel alone, CUDA events around `steps` launches after `warmup`, operands rotated
-    through enough copies that consecutive launches never find their inputs in L2."""
+    through enough copies that consecutive launches never find their inputs in L2.
+
+    Stand-alone (`--workload kernels`) it creates its own context and prints one JSON line per
+    kernel; from the step benchmark it runs on that benchmark's context (`env`) and appends the lines
+    to `collect`.  `with_cpu`: each line also carries the reference's CPU time for the same shape
+    (`cpu_baseline`; a bounded sample where the full shape would take minutes)."""
     import torch
 
     import autograd_b200 as ag
     from autograd_b200 import dp
 
-    torch.cuda.set_device(0)
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    ctx, alloc, be = ag.create(0, stream.cuda_stream)
+    steps = steps or a.steps
+    warmup = warmup or a.warmup
+    if env is None:
+        torch.cuda.set_device(dev_index)
+        stream = torch.cuda.Stream()
+        torch.cuda.set_stream(stream)
+        ctx, alloc, be = ag.create(dev_index, stream.cuda_stream)
+    else:
+        ctx, alloc, be = env
     peaks = load_peaks()
     L2 = ctx.l2_bytes
     bufs = []
+    cpu_ref = None
+    if with_cpu:
+        from oracle import ref_loader
+        if ref_loader.available():
+            from oracle import ref_timing as RT
+            cpu_ref = (ref_loader.load(), RT, RT.use_all_cores())
+
+    def cpu_entry(seconds, tokens, sample, kind="reference"):
+        """`cpu_baseline` of one kernel line: the same operation on the host."""
+        return {"cpu_baseline": {"value": tokens / seconds, "unit": UNIT, "ms": round(1e3 * seconds, 3),
+                                 "cores": cpu_ref[2][0], "kind": kind, "sample": sample + "; " + cpu_ref[2][1]}}
 
     def dev(n_elems, dtype=np.float32, std=1.0, ints=None):
         st = alloc.alloc((int(n_elems),), dtype)
@@ -517,10 +620,10 @@ def run_kernels(a):
         if ints is not None:
             ctx.copy_from_host(addr, ints.astype(np.int32))
         elif np.dtype(dtype) == np.dtype(np.float32):
-            dp.as_torch(addr, n_elems, 0).normal_(0.0, std)
+            dp.as_torch(addr, n_elems, dev_index).normal_(0.0, std)
         else:  # bf16 bit patterns of N(0, std), written through an int16 alias of the buffer
-            t = torch.empty(int(n_elems), device="cuda", dtype=torch.bfloat16).normal_(0.0, std)
-            dst = torch.as_tensor(dp.DeviceArrayView(addr, n_elems, "<i2"), device="cuda")
+            t = torch.empty(int(n_elems), device=f"cuda:{dev_index}", dtype=torch.bfloat16).normal_(0.0, std)
+            dst = torch.as_tensor(dp.DeviceArrayView(addr, n_elems, "<i2"), device=f"cuda:{dev_index}")
             dst.copy_(t.view(torch.int16))
         return addr
 
@@ -534,19 +637,19 @@ def run_kernels(a):
         return max(2, int(2.5 * L2 // max(bytes_per_set, 1)) + 1)
 
     def time_it(fn, n_sets):
-        for i in range(a.warmup):
+        for i in range(warmup):
             fn(i % n_sets)
         ctx.synchronize()
         E0, E1 = 2, 3
         ctx.event_record(E0)
-        for i in range(a.steps):
+        for i in range(steps):
             fn(i % n_sets)
         ctx.event_record(E1)
-        return ctx.event_elapsed_ms(E0, E1) / a.steps
+        return ctx.event_elapsed_ms(E0, E1) / steps
 
     def emit(cfg, kernel, ms, tokens, alg_bytes=None, useful_flops=None, dtype="f32", extra=None):
         line = {"workload": "kernels", "config": cfg, "kernel": kernel, "dtype": dtype, "ms": round(ms, 5),
-                "tokens_per_s": tokens / (ms / 1e3), "steps": a.steps, "warmup": a.warmup}
+                "tokens_per_s": tokens / (ms / 1e3), "steps": steps, "warmup": warmup}
         if alg_bytes is not None:
             gbs = alg_bytes / (ms / 1e3) / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -559,7 +662,10 @@ def run_kernels(a):
                                 "useful_flops": useful_flops, "peak_source": peaks["source"] + " bf16 burst"}
         if extra:
             line.update(extra)
-        print(json.dumps(line), flush=True)
+        if collect is not None:
+            collect.append(line)
+        else:
+            print(json.dumps(line), flush=True)
 
     f4 = 4
     def sec_cfg1():
@@ -571,12 +677,18 @@ def run_kernels(a):
             h = [dev(N * C) for _ in range(n_sets)]; y = [dev(N * C) for _ in range(n_sets)]
             gam, bet, dg, db = dev(C), dev(C), dev(C), dev(C)
             pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
+            cf = cb = None
+            if cpu_ref is not None:       # the reference's Add + LayerNorm graph at the same shape
+                tf, tb = cpu_ref[1].OpGraph(cpu_ref[0], cpu_ref[1].add_layernorm(N // 512, 512, C)).time_pair(1, 2)
+                what = f"AddOp + LayerNormOp graph, {N} x {C}, Runtime(device='cpu')"
+                cf, cb = cpu_entry(tf, N, what + " forward()"), cpu_entry(tb, N, what + " backward_graph()")
             ms = time_it(lambda i: ctx.add_layernorm_forward(x[i], r[i], gam, bet, h[i], y[i], 0, 0, N, C, 1e-5), n_sets)
-            emit("cfg1" if C == 384 else "cfg5-width", f"add_layernorm_forward {N}x{C}", ms, N, alg_bytes=4 * nb)
+            emit("cfg1" if C == 384 else "cfg5-width", f"add_layernorm_forward {N}x{C}", ms, N, alg_bytes=4 * nb, extra=cf)
             # backward: dy = y[i], saved input = h[i], residual gradient accumulated in place in x[i]
             ms = time_it(lambda i: ctx.layernorm_backward(y[i], h[i], gam, x[i], x[i], dg, db, part.ptr.address, pb, N, C,
                                                           1e-5), n_sets)
-            emit("cfg1" if C == 384 else "cfg5-width", f"layernorm_backward(+residual grad) {N}x{C}", ms, N, alg_bytes=4 * nb)
+            emit("cfg1" if C == 384 else "cfg5-width", f"layernorm_backward(+residual grad) {N}x{C}", ms, N, alg_bytes=4 * nb,
+                 extra=cb)
             free_all()
 
     def sec_gelu():
@@ -584,15 +696,51 @@ def run_kernels(a):
         n = 16384 * 1536
         n_sets = sets_for(3 * n * f4)
         x = [dev(n) for _ in range(n_sets)]; y = [dev(n) for _ in range(n_sets)]; g = [dev(n) for _ in range(n_sets)]
+        cf = cb = None
+        if cpu_ref is not None:
+            tf, tb = cpu_ref[1].OpGraph(cpu_ref[0], cpu_ref[1].gelu(16384, 1536)).time_pair(1, 2)
+            cf = cpu_entry(tf, 16384, "GELUOp graph, 16384 x 1536, Runtime(device='cpu') forward()")
+            cb = cpu_entry(tb, 16384, "GELUOp graph, 16384 x 1536, Runtime(device='cpu') backward_graph()")
         ms = time_it(lambda i: ctx.gelu_forward(x[i], y[i], n), n_sets)
-        emit("gelu", "gelu_forward 16384x1536", ms, 16384, alg_bytes=2 * n * f4)
+        emit("gelu", "gelu_forward 16384x1536", ms, 16384, alg_bytes=2 * n * f4, extra=cf)
         ms = time_it(lambda i: ctx.gelu_backward(x[i], y[i], 0, g[i], n), n_sets)
-        emit("gelu", "gelu_backward 16384x1536", ms, 16384, alg_bytes=3 * n * f4)
+        emit("gelu", "gelu_backward 16384x1536", ms, 16384, alg_bytes=3 * n * f4, extra=cb)
         free_all()
 
     def sec_cfg3():
         # ---- config 3: RMSNorm, RoPE, SwiGLU at the Qwen shapes, fp32 and bf16 storage
         N, C, H, HKV, D, I, B, T = 8192, 1536, 12, 2, 128, 8960, 4, 2048
+        # RoPE tables, positions 0..T-1 (module.py:247-250)
+        freqs = np.arange(T, dtype=np.float32)[:, None] * (np.float32(1e6) ** (-np.arange(0, D, 2, dtype=np.float32)[None, :]
+                                                                              / np.float32(D)))
+        cos_, sin_ = np.cos(freqs).astype(np.float32), np.sin(freqs).astype(np.float32)
+        cpu = {}
+        if cpu_ref is not None:
+            # The reference has no standalone op for these stages.  Two CPU figures per stage: the carrier op
+            # end to end (FusedRMSNormMLPOp: RMSNorm + two GEMMs + SwiGLU, mostly GEMM time), and the stage alone
+            # = the numpy statements of that stage (backend.py:1097-1108, :1113-1126, :1202-1251, restated in
+            # oracle/fused_layers.py; RoPE: the reference's own apply_rope_np / apply_rope_backward_np).
+            ref, RT, _ = cpu_ref
+            from oracle import fused_layers as O
+            rng = np.random.default_rng(1236)
+            cx = rng.standard_normal((N, C), dtype=np.float32); cg = np.ones(C, np.float32)
+            t0 = time.perf_counter(); O.rmsnorm_forward(cx, cg, 1e-6); t1 = time.perf_counter()
+            O.rmsnorm_backward(cx, cg, cx, 1e-6, cx, cg); t2 = time.perf_counter()
+            cgu = rng.standard_normal((N, 2 * I), dtype=np.float32); chd = rng.standard_normal((N, I), dtype=np.float32)
+            t3 = time.perf_counter(); O.swiglu_forward(cgu); t4 = time.perf_counter()
+            O.swiglu_backward(cgu, chd); t5 = time.perf_counter()
+            rp = RT.RopeBuffers(ref, B, T, H, HKV, D, 1e6)
+            rf, rb = rp.time_pair(1)
+            ctf, ctb = RT.OpGraph(ref, RT.rmsnorm_mlp(B, T, C, I)).time_pair(0, 1)
+            carrier = {"cpu_carrier_op": {"op": "FusedRMSNormMLPOp 4x2048x1536, I 8960, Runtime(device='cpu')",
+                                          "forward_ms": round(1e3 * ctf, 1), "backward_ms": round(1e3 * ctb, 1)}}
+            stage = "stage alone, numpy statements of the reference's CPU kernel"
+            cpu = {"rms_f": {**cpu_entry(t1 - t0, N, stage, "port"), **carrier},
+                   "rms_b": {**cpu_entry(t2 - t1, N, stage, "port"), **carrier},
+                   "rope": cpu_entry(rf, N, "apply_rope_np on q (12 heads) and k (2 heads), 4 x 2048 x 128"),
+                   "swi_f": {**cpu_entry(t4 - t3, N, stage, "port"), **carrier},
+                   "swi_b": {**cpu_entry(t5 - t4, N, stage, "port"), **carrier}}
+            del cx, cgu, chd, rp
         for dt_name, dt, es in (("f32", np.float32, 4), ("bf16", np.uint16, 2)):
             agdt = ag.AG_F32 if es == 4 else ag.AG_BF16
             n_sets = sets_for(3 * N * C * es)
@@ -601,27 +749,27 @@ def run_kernels(a):
             gam, dg = dev(C), dev(C)
             pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
             ms = time_it(lambda i: ctx.rmsnorm_forward(x[i], gam, y[i], 0, N, C, 1e-6, agdt), n_sets)
-            emit("cfg3", "rmsnorm_forward 8192x1536", ms, N, alg_bytes=2 * N * C * es, dtype=dt_name)
+            emit("cfg3", "rmsnorm_forward 8192x1536", ms, N, alg_bytes=2 * N * C * es, dtype=dt_name, extra=cpu.get("rms_f"))
             ms = time_it(lambda i: ctx.rmsnorm_backward(y[i], x[i], gam, d[i], d[i], dg, part.ptr.address, pb, N, C, 1e-6,
                                                         agdt), n_sets)
-            emit("cfg3", "rmsnorm_backward(+residual grad) 8192x1536", ms, N, alg_bytes=4 * N * C * es, dtype=dt_name)
+            emit("cfg3", "rmsnorm_backward(+residual grad) 8192x1536", ms, N, alg_bytes=4 * N * C * es, dtype=dt_name,
+                 extra=cpu.get("rms_b"))
             free_all()
             nq, nk = N * H * D, N * HKV * D
             n_sets = sets_for((nq + nk) * es)
             q = [dev(nq, dt) for _ in range(n_sets)]; k = [dev(nk, dt) for _ in range(n_sets)]
-            from oracle import fused_layers as O   # table formula only (module.py:247-250); not the thing measured
-            cos_, sin_ = O.rope_tables(T, D, 1e6)
             cos = dev(cos_.size); sin = dev(sin_.size)
             ctx.copy_from_host(cos, cos_); ctx.copy_from_host(sin, sin_)
             ms = time_it(lambda i: ctx.rope_qk(q[i], k[i], cos, sin, B, T, H, HKV, D, sin_sign=1, dtype=agdt), n_sets)
-            emit("cfg3", "rope_qk 4x2048 q12 k2 d128", ms, N, alg_bytes=2 * (nq + nk) * es, dtype=dt_name)
+            emit("cfg3", "rope_qk 4x2048 q12 k2 d128", ms, N, alg_bytes=2 * (nq + nk) * es, dtype=dt_name, extra=cpu.get("rope"))
             free_all()
             n_sets = sets_for(4 * N * I * es)
             gu = [dev(N * 2 * I, dt) for _ in range(n_sets)]; hid = [dev(N * I, dt) for _ in range(n_sets)]
             ms = time_it(lambda i: ctx.swiglu_forward(gu[i], hid[i], N, I, agdt), n_sets)
-            emit("cfg3", "swiglu_forward 8192x8960", ms, N, alg_bytes=3 * N * I * es, dtype=dt_name)
+            emit("cfg3", "swiglu_forward 8192x8960", ms, N, alg_bytes=3 * N * I * es, dtype=dt_name, extra=cpu.get("swi_f"))
             ms = time_it(lambda i: ctx.swiglu_backward(gu[i], hid[i], N, I, agdt), n_sets)
-            emit("cfg3", "swiglu_backward_inplace 8192x8960", ms, N, alg_bytes=5 * N * I * es, dtype=dt_name)
+            emit("cfg3", "swiglu_backward_inplace 8192x8960", ms, N, alg_bytes=5 * N * I * es, dtype=dt_name,
+                 extra=cpu.get("swi_b"))
             free_all()
 
     def sec_cfg4():
@@ -637,13 +785,21 @@ def run_kernels(a):
         n_sets = 2
         out = [dev(n * C) for _ in range(n_sets)]
         sb = ctx.scatter_add_scratch_bytes(n, C, V); sc = alloc.alloc((sb,), np.uint8); bufs.append(sc)
+        cf, cb = {}, {}
+        if cpu_ref is not None:
+            tf, tb = cpu_ref[1].OpGraph(cpu_ref[0], cpu_ref[1].gather(32, 2048, V, C, ids=ids_)).time_pair(0, 1)
+            what = "GatherOp graph, 65536 Zipf ids, table 151936 x 1536, Runtime(device='cpu')"
+            cf = cpu_entry(tf, n, what + " forward()")
+            cb = cpu_entry(tb, n, what + " backward_graph() (np.add.at, plus the zero-fill of the output gradient)")
         ms = time_it(lambda i: ctx.gather_forward(ids, table, out[i], n, C, V), n_sets)
-        emit("cfg4", "gather_forward 65536 ids x 1536", ms, n, alg_bytes=2 * n * C * f4,
-             extra={"unique_rows": uniq, "unique_row_lower_bound_bytes": (n + uniq) * C * f4})
+        # DRAM sees every distinct table row once (the hot Zipf rows stay in L2) plus the output: the
+        # roofline numerator is that bound, not 2 x n x C
+        emit("cfg4", "gather_forward 65536 ids x 1536", ms, n, alg_bytes=(n + uniq) * C * f4,
+             extra={"unique_rows": uniq, "bytes_if_every_row_were_distinct": 2 * n * C * f4, **cf})
         ctx.fill_f32(dtable, 0.0, V * C)
         ms = time_it(lambda i: ctx.gather_backward(ids, out[i], dtable, sc.ptr.address, sb, n, C, V), n_sets)
         emit("cfg4", "scatter_add (sort + segmented sum) 65536 ids x 1536", ms, n, alg_bytes=(n + 2 * uniq) * C * f4,
-             extra={"unique_rows": uniq, "note": "without the dense zero-fill of dTable"})
+             extra={"unique_rows": uniq, "note": "without the dense zero-fill of dTable", **cb})
         ms0 = time_it(lambda i: ctx.fill_f32(dtable, 0.0, V * C), 1)
         emit("cfg4", "zero-fill of dTable 151936x1536", ms0, n, alg_bytes=V * C * f4)
         free_all()
@@ -654,8 +810,15 @@ def run_kernels(a):
         rng = np.random.default_rng(1238)
         tg_ = rng.integers(0, V, size=N).astype(np.int32)
         tg_[rng.random(N) < 0.05] = -1
+        modes = {"3xtf32": ag.AG_CE_3XTF32, "bf16": ag.AG_CE_BF16, "bf16x3": ag.AG_CE_BF16X3}
         for C in (384, 1280):
-            for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16", ag.AG_CE_BF16), ("bf16x3", ag.AG_CE_BF16X3)):
+            cf = cb = None
+            if cpu_ref is not None:     # a 2048-row sample of the 16384 rows: the cost is linear in the rows
+                tf, tb = cpu_ref[1].OpGraph(cpu_ref[0], cpu_ref[1].fused_linear_ce(1, 2048, C, V)).time_pair(0, 1)
+                what = f"FusedLinearCrossEntropyOp graph, 2048 of 16384 rows, C {C}, V 32768, Runtime(device='cpu')"
+                cf, cb = cpu_entry(tf, 2048, what + " forward()"), cpu_entry(tb, 2048, what + " backward_graph()")
+            for pname in (cfg2_modes or modes):
+                prec = modes[pname]
                 X = dev(N * C, std=1.0 / np.sqrt(C)); W = dev(V * C, std=0.02)
                 dX, dW = dev(N * C), dev(V * C)
                 tg = dev(N, np.int32, ints=tg_)
@@ -666,9 +829,9 @@ def run_kernels(a):
                 ms_f = time_it(lambda i: ctx.flce_forward(desc, X, W, tg, 0, loss, lse, scr.ptr.address, sbytes), 1)
                 ms_b = time_it(lambda i: ctx.flce_backward(desc, X, W, tg, 0, dloss, lse, dX, dW, scr.ptr.address, sbytes), 1)
                 fl = 2.0 * N * C * V
-                emit("cfg2", f"fused_linear_ce forward N16384 C{C} V32768", ms_f, N, useful_flops=fl, dtype=pname)
+                emit("cfg2", f"fused_linear_ce forward N16384 C{C} V32768", ms_f, N, useful_flops=fl, dtype=pname, extra=cf)
                 emit("cfg2", f"fused_linear_ce backward N16384 C{C} V32768", ms_b, N, useful_flops=2 * fl, dtype=pname,
-                     extra={"executed_flops": 3 * fl})
+                     extra={"executed_flops": 3 * fl, **(cb or {})})
                 emit("cfg2", f"fused_linear_ce fwd+bwd N16384 C{C} V32768", ms_f + ms_b, N, useful_flops=3 * fl, dtype=pname,
                      extra={"scratch_bytes": sbytes})
                 free_all()
@@ -737,6 +900,7 @@ def run_kernels(a):
             raise SystemExit(f"--only: unknown section {name!r}; choose from {sorted(sections)}")
         sections[name]()
     ctx.check_status()
+    return collect
 
 
 def main():
@@ -744,7 +908,7 @@ def main():
     if a.impl == "reference":
         run_reference(a)
     elif a.workload == "kernels":
-        run_kernels(a)
+        run_kernels(a, with_cpu=not a.no_cpu_baseline)
     else:
         run_b200(a)
 

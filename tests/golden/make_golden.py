@@ -460,9 +460,12 @@ def gen_grad_bf16(ref, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("AUTOGRAD_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("AUTOGRAD_REFERENCE"),
+                    help="path of the reference checkout (or set AUTOGRAD_REFERENCE)")
     ap.add_argument("--out", default=HERE)
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("give --reference or set AUTOGRAD_REFERENCE")
     ref = load_reference(args.reference)
     for fn in (gen_add_layernorm, gen_gelu, gen_gather, gen_flce, gen_rmsnorm_swiglu, gen_rope,
                gen_rmsnorm_flce, gen_linear_add, gen_adamw_bf16, gen_grad_bf16):

@@ -223,12 +223,13 @@ def test_bf16_host_conversion_matches_the_oracle(golden):
 
 
 # ---------------------------------------------------------------------------------------
-# registration into the real reference (only where a checkout exists; never on the GPU box)
+# registration into the real reference: its modules as copied to oracle/_ref by oracle/make_ref.py,
+# or a checkout named by AUTOGRAD_REFERENCE
 # ---------------------------------------------------------------------------------------
-REFERENCE = os.environ.get("AUTOGRAD_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("AUTOGRAD_REFERENCE") or os.path.join(ROOT, "oracle", "_ref")
 
 
-@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE, "runtime.py")), reason="no reference checkout")
+@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE, "runtime.py")), reason="no reference modules")
 def test_registers_behind_the_reference_runtime_and_plans_scratch():
     import subprocess
     code = r'''
@@ -340,3 +341,68 @@ def test_grad_allreduce_two_gloo_ranks():
     for p in procs:
         p.join(timeout=60)
     assert res == [(0, True, 0, 5), (1, True, 5, 10)], res
+
+
+def test_rmsnorm_ce_scratch_slot_too_small_for_the_current_precision_is_an_error():
+    """The arena slot of FusedRMSNormLinearCrossEntropyOp is sized at planning time from ce_precision /
+    ce_vocab_chunk; a setting changed afterwards must not overrun it: the backend compares the real slot
+    size with its current need, and hands the C side the bytes that are really left for the head."""
+    class Ctx(FakeContext):
+        @staticmethod
+        def flce_scratch_bytes(desc):
+            return (1 << 20) if desc.precision == _native.AG_CE_FP32 else (4 << 20)
+
+    ctx = Ctx()
+    alloc = CudaAllocator(ctx)
+    be = CudaBackend(ctx, alloc)
+    alloc.backend = be
+    x, w, g = _t(alloc, (2, 8, 64), grad=True), _t(alloc, (100, 64), grad=True), _t(alloc, (64,), grad=True)
+    y = _t(alloc, (2, 8), np.int32, requires_grad=False)
+    loss = _t(alloc, (1,), grad=True)
+    n = hg.make_node(hg.make_op("FusedRMSNormLinearCrossEntropyOp", eps=1e-6), (x, w, g, y), (loss,))
+    be.ce_precision = _native.AG_CE_FP32
+    _, z_bytes, part_bytes, flce_bytes = be._rms_flce_layout(16, 64, 100)
+    planned = 2 * z_bytes + part_bytes + flce_bytes
+    slot = alloc.alloc((planned,), np.uint8)
+    be.get_forward_kernel(n.op)(n.inputs, n.outputs, scratch={"rms_flce": slot})          # as planned: fine
+    call = [c for c in ctx.calls if c[0] == "flce_forward"][-1]
+    assert call[-1] == flce_bytes and call[-2] == address_of(slot) + 2 * z_bytes + part_bytes
+    be.ce_precision = _native.AG_CE_3XTF32                                                  # needs 4 MiB now
+    with pytest.raises(RuntimeError, match="changed after the graph was planned"):
+        be.get_forward_kernel(n.op)(n.inputs, n.outputs, scratch={"rms_flce": slot})
+    with pytest.raises(RuntimeError, match="changed after the graph was planned"):
+        be.get_backward_kernel(n.op)(n.inputs, n.outputs, scratch={"rms_flce": slot})
+    # a larger slot than needed: the head is told what is really left, not the computed minimum
+    be.ce_precision = _native.AG_CE_FP32
+    big = alloc.alloc((planned + 4096,), np.uint8)
+    be.get_forward_kernel(n.op)(n.inputs, n.outputs, scratch={"rms_flce": big})
+    assert [c for c in ctx.calls if c[0] == "flce_forward"][-1][-1] == flce_bytes + 4096
+
+
+def test_adamw_rejects_the_packed_buffer_arguments():
+    ctx, alloc, be = _fake_env()
+    p, g, m, v = (_t(alloc, (64,)) for _ in range(4))
+    with pytest.raises(TypeError, match="packed-buffer"):
+        be.adamw_step(p.storage, g.storage, m.storage, v.storage, None, 1e-3, 1e-3, 0.9, 0.95, 1e-8, 0.1,
+                      numel=64, decay_numel=32, lr_bc1=1e-3, inv_sqrt_bc2=1.0)
+    be.adamw_step(p.storage, g.storage, m.storage, v.storage, None, 1e-3, 1e-3, 0.9, 0.95, 1e-8, 0.1, grad_scale=0.5)
+    assert ctx.calls[-1][0] == "adamw_step"
+
+
+def test_lse_side_buffers_are_bounded_and_released():
+    ctx, alloc, be = _fake_env()
+    x, w = _t(alloc, (1, 8, 32), grad=True), _t(alloc, (50, 32), grad=True)
+    y = _t(alloc, (1, 8), np.int32, requires_grad=False)
+    losses = []
+    for _ in range(be.MAX_SIDE_BUFFERS + 3):
+        loss = _t(alloc, (1,), grad=True)
+        n = hg.make_node(hg.make_op("FusedLinearCrossEntropyOp", ignore_index=-1), (x, w, y), (loss,))
+        be.get_forward_kernel(n.op)(n.inputs, n.outputs)
+        losses.append((loss, n))
+    assert len(be._side) == be.MAX_SIDE_BUFFERS
+    loss, n = losses[-1]
+    be.get_backward_kernel(n.op)(n.inputs, n.outputs)                     # the newest graph still finds its lse
+    with pytest.raises(RuntimeError, match="before forward"):            # the oldest was evicted
+        be.get_backward_kernel(losses[0][1].op)(losses[0][1].inputs, losses[0][1].outputs)
+    be.release_side_buffers()
+    assert not be._side
