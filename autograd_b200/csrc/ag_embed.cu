@@ -6,14 +6,15 @@
 // Backward: dtable[ids[i],:] += dout[i,:] with a summation order that does not depend on
 // scheduling.  No float atomics are used anywhere:
 //   1. stable LSD radix sort of (id, position) pairs, 9 bits per pass, so that equal ids end
-//      up adjacent and in ascending position order;
+//      up adjacent and in ascending position order (up to 262144 ids: one histogram launch and
+//      one launch per pass; beyond that a histogram, a scan and a scatter launch per pass);
 //   2. the sorted list is cut into groups of SEG_GROUP consecutive entries.  A CTA walks one
 //      group (for one 512-column slice), summing each run of equal ids in list order.  A run
 //      that is a complete segment (its id neither continues from the previous group nor
 //      into the next one) starts from the current dtable row and is written back directly:
 //      for such rows the result is bit-identical to numpy's sequential np.add.at.  A run cut
 //      by a group boundary is written to a per-group partial slot instead;
-//   3. a combine kernel adds, for every segment that spans several groups, its partial slots
+//   3. a combine kernel finds the segments that span several groups and adds their partial slots
 //      in group order onto the dtable row.
 // Ids outside [0,V) are dropped and flagged in the status word.
 #include "ag_common.cuh"
@@ -189,6 +190,138 @@ sort_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __rest
   }
 }
 
+// ------------------------------------------------------------------------------ radix sort, few launches
+// For up to SORT_FUSED_MAX_TILES tiles (262144 ids) a pass needs no scan launch and no separate
+// histogram launch after the first one:
+//   * sort_hist_ids_kernel reads the ids themselves (key = id, or V for an id outside the table;
+//     value = position), writes the per-tile histogram of the first digit and zeroes the
+//     histograms of the later passes;
+//   * sort_scatter_fused_kernel derives its tile's digit offsets from the whole histogram
+//     (n_tiles x SORT_DIGITS counters, tile-major, a few hundred KB in L2: thread d walks digit d
+//     down the tiles with coalesced loads, then the CTA scans the 512 digit totals), places its
+//     keys stably, and counts the next pass's per-tile histogram as it goes - integer atomics on
+//     counters, aggregated per warp, whose final values do not depend on the order of the additions.
+// The order of the sorted list is the one the unfused kernels produce: stable by digit, tile, rank.
+constexpr int SORT_FUSED_MAX_TILES = 256;
+constexpr int SORT_MAX_PASSES = 4;
+
+__device__ __forceinline__ uint32_t sort_key_of(int id, int V) { return (id >= 0 && id < V) ? (uint32_t)id : (uint32_t)V; }
+
+// hist0 and hist_later are tile-major: counter of (tile, digit) at [tile * SORT_DIGITS + digit].
+__global__ void __launch_bounds__(SORT_TILE)
+sort_hist_ids_kernel(const int32_t* __restrict__ ids, uint32_t* __restrict__ hist0, uint32_t* __restrict__ hist_later,
+                     int64_t later_entries, int64_t n, int V, int* status) {
+  ag_pdl_wait();
+  if (gridDim.x <= 148) ag_pdl_trigger();
+  __shared__ uint32_t s_cnt[SORT_DIGITS];
+  for (int d = threadIdx.x; d < SORT_DIGITS; d += SORT_TILE) s_cnt[d] = 0;
+  // the histograms of the later passes start at zero: this CTA clears its share
+  for (int64_t e = (int64_t)blockIdx.x * SORT_TILE + threadIdx.x; e < later_entries; e += (int64_t)gridDim.x * SORT_TILE)
+    hist_later[e] = 0u;
+  __syncthreads();
+  const int64_t i = (int64_t)blockIdx.x * SORT_TILE + threadIdx.x;
+  if (i < n) {
+    const int id = ids[i];
+    if (id < 0 || id >= V) atomicOr(status, AG_STATUS_BAD_INDEX);
+    atomicAdd(&s_cnt[sort_key_of(id, V) & (SORT_DIGITS - 1)], 1u);  // integer: order-free
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < SORT_DIGITS; d += SORT_TILE) hist0[(int64_t)blockIdx.x * SORT_DIGITS + d] = s_cnt[d];
+}
+
+// FIRST: keys and values come from the ids (pass 0); otherwise from keys_in / vals_in.
+// hist: this pass's per-tile histogram; hist_next: the next pass's (NULL on the last pass), counted
+// per tile of the OUTPUT positions.  Both tile-major.
+template <bool FIRST>
+__global__ void __launch_bounds__(SORT_TILE)
+sort_scatter_fused_kernel(const int32_t* __restrict__ ids, const uint32_t* __restrict__ keys_in,
+                          const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out,
+                          uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ hist,
+                          uint32_t* __restrict__ hist_next, int64_t n, int V, int shift, int n_tiles) {
+  ag_pdl_wait();
+  if (gridDim.x <= 148) ag_pdl_trigger();
+  __shared__ uint16_t s_cnt[SORT_WARPS][SORT_DIGITS];  // 32 KB
+  __shared__ uint32_t s_tot[2][SORT_DIGITS], s_bef[2][SORT_DIGITS];
+  __shared__ uint32_t s_base[SORT_DIGITS];             // first output position of (digit, this tile)
+  __shared__ uint32_t s_wsum[SORT_DIGITS / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int d = lane; d < SORT_DIGITS; d += 32) s_cnt[warp][d] = 0;
+
+  // ---- offsets: total[d] = count of digit d over all tiles, before[d] = over the tiles before this one.
+  // Thread (half, d) walks digit d down one half of the tiles; a warp's loads are 32 consecutive counters.
+  {
+    const int d = threadIdx.x & (SORT_DIGITS - 1), half = threadIdx.x >> 9;
+    const int t0 = half ? (n_tiles + 1) / 2 : 0, t1 = half ? n_tiles : (n_tiles + 1) / 2;
+    uint32_t total = 0, before = 0;
+    for (int t = t0; t < t1; t += 8) {
+      uint32_t v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (t + u < t1) ? hist[(int64_t)(t + u) * SORT_DIGITS + d] : 0u;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        total += v[u];
+        if (t + u < (int)blockIdx.x) before += v[u];
+      }
+    }
+    s_tot[half][d] = total;
+    s_bef[half][d] = before;
+  }
+  __syncthreads();
+  if (threadIdx.x < SORT_DIGITS) {
+    // exclusive scan of the 512 digit totals: 16 warps of 32 digits
+    const int d = threadIdx.x;
+    const uint32_t total = s_tot[0][d] + s_tot[1][d];
+    uint32_t inc = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_wsum[warp] = inc;
+    s_base[d] = inc - total + s_bef[0][d] + s_bef[1][d];  // the warps' offsets are added below
+  }
+  __syncthreads();
+  if (threadIdx.x < SORT_DIGITS) {
+    uint32_t wbase = 0;
+    for (int w = 0; w < warp; ++w) wbase += s_wsum[w];
+    s_base[threadIdx.x] += wbase;
+  }
+
+  const int64_t i = (int64_t)blockIdx.x * SORT_TILE + threadIdx.x;
+  const bool live = i < n;
+  uint32_t key = 0, val = 0;
+  int digit = 0;
+  if (live) {
+    if (FIRST) {
+      key = sort_key_of(ids[i], V);
+      val = (uint32_t)i;
+    } else {
+      key = keys_in[i];
+      val = vals_in[i];
+    }
+    digit = (key >> shift) & (SORT_DIGITS - 1);
+  }
+  const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
+  uint32_t peers = 0;
+  if (live) peers = __match_any_sync(live_mask, digit);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (live && rank_in_warp == 0) s_cnt[warp][digit] = (uint16_t)__popc(peers);
+  __syncthreads();
+  if (live) {
+    uint32_t before = 0;
+    for (int w = 0; w < warp; ++w) before += s_cnt[w][digit];
+    const uint32_t dst = s_base[digit] + before + rank_in_warp;
+    keys_out[dst] = key;
+    vals_out[dst] = val;
+    if (hist_next) {
+      // one atomic per distinct counter and warp (a hot id fills whole warps with the same counter)
+      const uint32_t counter = (dst >> 10) * SORT_DIGITS + ((key >> (shift + SORT_BITS)) & (SORT_DIGITS - 1));
+      const uint32_t same = __match_any_sync(live_mask, counter);
+      if ((same & ((1u << lane) - 1u)) == 0) atomicAdd(&hist_next[counter], (uint32_t)__popc(same));  // order-free
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ scatter-add
 constexpr int SEG_GROUP = 32;       // sorted entries per group
 constexpr int SEG_THREADS = 128;    // one float4 per thread: 512 columns per CTA
@@ -234,8 +367,8 @@ constexpr int SEG_BATCH = 8;  // sorted entries whose rows are requested togethe
 template <bool VEC, typename TT>
 __global__ void __launch_bounds__(SEG_THREADS)
 scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ pos,
-                      const float* __restrict__ dout, TT* dtable, float* __restrict__ partials, int64_t n, int C,
-                      int V) {
+                      const float* __restrict__ dout, TT* dtable, float* __restrict__ partials,
+                      long long* __restrict__ heads, int n_groups, int64_t n, int C, int V) {
   constexpr bool BF = sizeof(TT) == 2;  // rounded storage: sum from zero, add the old row last
   ag_pdl_wait();
   __shared__ uint32_t s_key[SEG_GROUP + 2];  // [0] = key before the group, [1..G] group, [G+1] = key after
@@ -272,7 +405,7 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
 
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
   if (VEC) {
-    if (col >= C) return;
+    if (col < C) {
     // Rows of SEG_BATCH entries, and the dtable rows of the complete runs that begin among them, are
     // requested together; the adds then run in sorted (= position) order, each complete run starting
     // from its dtable row: the same sequence of additions as an unbuffered add-at.
@@ -314,6 +447,7 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
         }
       }
     }
+    }
   } else {
     // scalar mode: a thread covers columns col, col+128, col+256, col+384
     for (int j = 0; j < cnt; ++j) {
@@ -332,111 +466,115 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
       }
     }
   }
-}
 
-// One warp per group: if the group's LAST run opens a segment that continues into following groups
-// and starts in this group (the head of the segment), heads[group] = 2 * (last group holding entries
-// of the segment) + (partial slot of the head run); otherwise -1.  Coalesced loads and ballots only:
-// no chain of dependent loads.
-constexpr int SEG_SPLIT = 4;  // sub-ranges of a segment's groups summed side by side in the combine kernel
-
-__global__ void __launch_bounds__(128)
-segment_heads_kernel(const uint32_t* __restrict__ keys, long long* __restrict__ heads, int64_t n, int n_groups, int V) {
-  ag_pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const long long grp = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (grp >= n_groups) return;  // warp-uniform
-  const int64_t g0 = grp * SEG_GROUP;
-  const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
-  const int64_t last = g0 + cnt - 1;
-  long long rec = -1;
-  if (last + 1 < n) {  // warp-uniform
-    const uint32_t kj = lane < cnt ? keys[g0 + lane] : 0xffffffffu;
-    const uint32_t k_last = __shfl_sync(0xffffffffu, kj, cnt - 1);
-    const uint32_t k_next = keys[last + 1];
-    const uint32_t k_prev = g0 > 0 ? keys[g0 - 1] : 0xffffffffu;
-    bool go = (k_next == k_last) && (k_last < (uint32_t)V);
-    // sorted keys: the entries equal to the last key are the tail of the group
-    const int start = cnt - __popc(__ballot_sync(0xffffffffu, lane < cnt && kj == k_last));
-    if (start == 0 && k_prev == k_last) go = false;  // a continuation: an earlier group is the head
-    if (go) {
-      // first keys of the following groups, 32 groups per probe; equal ones form a prefix
-      long long g_end = grp;
-      for (long long gb = grp + 1;; gb += 32) {
-        const long long gq = gb + lane;
-        const bool same = gq < n_groups && keys[gq * SEG_GROUP] == k_last;
-        const int m = __popc(__ballot_sync(0xffffffffu, same));
-        g_end = gb + m - 1;
-        if (m < 32) break;
+  // The first warp of the group's first column slice leaves the group's head record for the combine
+  // kernel: 2 * (last group holding entries of the segment) + (partial slot of the head run) when the
+  // group's LAST run opens a segment that continues into following groups and starts in this group,
+  // else -1.  The decision comes from the keys already in shared memory; only a head group (rare)
+  // probes the first keys of the following groups, 32 per ballot.
+  if (blockIdx.y == 0 && threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    long long rec = -1;
+    if (cnt > 0 && g0 + cnt < n) {
+      const uint32_t k_last = s_key[cnt];
+      int rb = cnt - 1;
+      while (rb > 0 && s_key[rb] == k_last) --rb;
+      const bool from_prev = rb == 0 && s_key[0] == k_last;
+      if (s_key[cnt + 1] == k_last && k_last < (uint32_t)V && !from_prev) {  // warp-uniform
+        long long g_end = blockIdx.x;
+        for (long long gb = (long long)blockIdx.x + 1;; gb += 32) {
+          const long long gq = gb + lane;
+          const bool same = gq < n_groups && keys[gq * SEG_GROUP] == k_last;
+          const int m = __popc(__ballot_sync(0xffffffffu, same));
+          g_end = gb + m - 1;
+          if (m < 32) break;
+        }
+        rec = g_end * 2 + (rb == 0 ? 0 : 1);
       }
-      rec = g_end * 2 + (start == 0 ? 0 : 1);
     }
+    if (lane == 0) heads[blockIdx.x] = rec;
   }
-  if (lane == 0) heads[grp] = rec;
 }
 
-// One CTA per (group, column slice), block (SEG_THREADS, SEG_SPLIT): for a head group, the partial
-// slots of the segment's following groups are split into SEG_SPLIT consecutive sub-ranges; thread row
-// y adds its sub-range in group order (8 loads in flight), then row 0 adds
-// dtable row + head partial + sub-sum 0 + ... + sub-sum 3 and writes the dtable row.  Fixed order.
+constexpr int SEG_SPLIT = 8;  // sub-ranges of a segment's groups summed side by side in the combine kernel
+
+// Block (SEG_THREADS, SEG_SPLIT), grid (about one resident wave, column slices): a CTA walks the groups
+// g = blockIdx.x, blockIdx.x + gridDim.x, ... of its column slice, eight head records per look, and works
+// only on the heads of segments that span several groups (heads[g] >= 0, few).  For a head group, the
+// partial slots of the segment's following groups are split into SEG_SPLIT consecutive sub-ranges; thread
+// row y adds its sub-range in group order (8 loads in flight), then row 0 adds
+// dtable row + head partial + sub-sum 0 + ... + sub-sum 7 and writes the dtable row.  Fixed order; a
+// table row is written by exactly one CTA.
 template <bool VEC, typename TT>
 __global__ void __launch_bounds__(SEG_THREADS * SEG_SPLIT)
 scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __restrict__ heads, TT* dtable,
-                       const float* __restrict__ partials, int64_t n, int C) {
+                       const float* __restrict__ partials, int64_t n, int64_t n_groups, int C) {
   constexpr bool BF = sizeof(TT) == 2;
   ag_pdl_wait();
-  const int64_t grp = blockIdx.x;
-  const long long rec = heads[grp];
-  if (rec < 0) return;  // uniform
-  const int64_t g_end = rec >> 1;
-  const int head_slot = (int)(rec & 1);
-  const int64_t g0 = grp * SEG_GROUP;
-  const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
-  const uint32_t key = keys[g0 + cnt - 1];
+  __shared__ float4 s_sub[SEG_SPLIT][SEG_THREADS];
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
-  TT* drow = dtable + (int64_t)key * C;
-  if (VEC) {
-    __shared__ float4 s_sub[SEG_SPLIT][SEG_THREADS];
-    const int y = threadIdx.y;
-    const int64_t chunk = (g_end - grp + SEG_SPLIT - 1) / SEG_SPLIT;
-    float4 sub = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (col < C) {
-      int64_t g = grp + 1 + y * chunk;
-      int64_t ge = g + chunk;
-      if (ge > g_end + 1) ge = g_end + 1;
-      for (; g + 8 <= ge; g += 8) {
-        float4 v[8];
+  const int y = threadIdx.y;
+  for (int64_t gb = blockIdx.x; gb < n_groups; gb += (int64_t)8 * gridDim.x) {
+    long long recs[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(partials + ((g + u) * 2 + 0) * C + col));
+    for (int u = 0; u < 8; ++u) {
+      const int64_t gq = gb + (int64_t)u * gridDim.x;
+      recs[u] = gq < n_groups ? heads[gq] : -1;
+    }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) sub = f4_add(sub, v[u]);
+    for (int u = 0; u < 8; ++u) {
+      const long long rec = recs[u];
+      if (rec < 0) continue;  // uniform across the CTA
+      const int64_t grp = gb + (int64_t)u * gridDim.x;
+      const int64_t g_end = rec >> 1;
+      const int head_slot = (int)(rec & 1);
+      const int64_t g0 = grp * SEG_GROUP;
+      const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
+      const uint32_t key = keys[g0 + cnt - 1];
+      TT* drow = dtable + (int64_t)key * C;
+      if (VEC) {
+        const int64_t chunk = (g_end - grp + SEG_SPLIT - 1) / SEG_SPLIT;
+        float4 sub = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (col < C) {
+          int64_t g = grp + 1 + y * chunk;
+          int64_t ge = g + chunk;
+          if (ge > g_end + 1) ge = g_end + 1;
+          for (; g + 8 <= ge; g += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              v[k] = __ldcs(reinterpret_cast<const float4*>(partials + ((g + k) * 2 + 0) * C + col));
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sub = f4_add(sub, v[k]);
+          }
+          for (; g < ge; ++g) sub = f4_add(sub, *reinterpret_cast<const float4*>(partials + (g * 2 + 0) * C + col));
+        }
+        __syncthreads();  // the previous head's sub-sums have been read
+        s_sub[y][threadIdx.x] = sub;
+        __syncthreads();
+        if (y == 0 && col < C) {
+          const float4 old = seg_load4(drow + col);
+          const float4 head = *reinterpret_cast<const float4*>(partials + (grp * 2 + head_slot) * C + col);
+          float4 acc = BF ? head : f4_add(old, head);
+#pragma unroll
+          for (int q = 0; q < SEG_SPLIT; ++q) acc = f4_add(acc, s_sub[q][threadIdx.x]);
+          seg_store4(drow + col, BF ? f4_add(old, acc) : acc);
+        }
+      } else if (y == 0) {
+        for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
+          const float old = seg_load1(drow + c);
+          float acc = BF ? partials[(grp * 2 + head_slot) * C + c] : old + partials[(grp * 2 + head_slot) * C + c];
+          for (int64_t g = grp + 1; g <= g_end; ++g) acc += partials[(g * 2 + 0) * C + c];
+          seg_store1(drow + c, BF ? old + acc : acc);
+        }
       }
-      for (; g < ge; ++g) sub = f4_add(sub, *reinterpret_cast<const float4*>(partials + (g * 2 + 0) * C + col));
-    }
-    s_sub[y][threadIdx.x] = sub;
-    __syncthreads();
-    if (y == 0 && col < C) {
-      const float4 old = seg_load4(drow + col);
-      const float4 head = *reinterpret_cast<const float4*>(partials + (grp * 2 + head_slot) * C + col);
-      float4 acc = BF ? head : f4_add(old, head);
-#pragma unroll
-      for (int q = 0; q < SEG_SPLIT; ++q) acc = f4_add(acc, s_sub[q][threadIdx.x]);
-      seg_store4(drow + col, BF ? f4_add(old, acc) : acc);
-    }
-  } else {
-    if (threadIdx.y != 0) return;
-    for (int c = col; c < C && c < (int)(blockIdx.y + 1) * SEG_COLS; c += SEG_THREADS) {
-      const float old = seg_load1(drow + c);
-      float acc = BF ? partials[(grp * 2 + head_slot) * C + c] : old + partials[(grp * 2 + head_slot) * C + c];
-      for (int64_t g = grp + 1; g <= g_end; ++g) acc += partials[(g * 2 + 0) * C + c];
-      seg_store1(drow + c, BF ? old + acc : acc);
     }
   }
 }
 
 struct ScatterPlan {
   int64_t n_tiles, n_groups;
-  size_t off_keys[2], off_vals[2], off_hist, off_partials, total;
+  size_t off_keys[2], off_vals[2], off_hist, off_heads, off_partials, total;
 };
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -450,11 +588,9 @@ inline ScatterPlan scatter_plan(int64_t n, int C) {
     p.off_keys[b] = off; off += align256((size_t)n * 4);
     p.off_vals[b] = off; off += align256((size_t)n * 4);
   }
-  p.off_hist = off;  // also the per-group head records of the combine step (8 bytes per group)
-  {
-    const size_t hist_bytes = (size_t)SORT_DIGITS * p.n_tiles * 4, head_bytes = (size_t)p.n_groups * 8;
-    off += align256(hist_bytes > head_bytes ? hist_bytes : head_bytes);
-  }
+  p.off_hist = off;  // one histogram per pass when the passes are fused (few tiles), else one in all
+  off += align256((size_t)SORT_DIGITS * p.n_tiles * 4 * (p.n_tiles <= SORT_FUSED_MAX_TILES ? SORT_MAX_PASSES : 1));
+  p.off_heads = off; off += align256((size_t)p.n_groups * 8);   // head record of every group
   p.off_partials = off; off += align256((size_t)p.n_groups * 2 * C * 4);
   p.total = off;
   return p;
@@ -511,48 +647,69 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
   uint32_t* vals[2] = {reinterpret_cast<uint32_t*>(base + p.off_vals[0]), reinterpret_cast<uint32_t*>(base + p.off_vals[1])};
   uint32_t* hist = reinterpret_cast<uint32_t*>(base + p.off_hist);
   float* partials = reinterpret_cast<float*>(base + p.off_partials);
-  // the histogram area is free once the keys are sorted: it holds the per-group head records
-  // (8 bytes per group of 32 ids, the histogram has 2 KB per 1024 ids)
-  long long* heads = reinterpret_cast<long long*>(base + p.off_hist);
+  long long* heads = reinterpret_cast<long long*>(base + p.off_heads);
   const int n_tiles = (int)p.n_tiles;
-
-  AG_LAUNCH_PDL(ctx, "sort_init_kernel", sort_init_kernel, n_tiles, SORT_TILE, 0, ids, keys[0], vals[0], n_ids, V,
-                ctx->d_status);
   // keys are in [0, V]: sort just enough 9-bit digits to cover V
   int bits = 1;
   while (((int64_t)1 << bits) <= (int64_t)V) ++bits;
+  const int passes = (bits + SORT_BITS - 1) / SORT_BITS;
   int cur = 0;
-  for (int shift = 0; shift < bits; shift += SORT_BITS) {
-    AG_LAUNCH_PDL(ctx, "sort_hist_kernel", sort_hist_kernel, n_tiles, SORT_TILE, 0, (const uint32_t*)keys[cur], hist, n_ids,
-                  shift, n_tiles);
-    AG_LAUNCH_PDL(ctx, "sort_scan_kernel", sort_scan_kernel, 1, 1024, 0, hist, (int64_t)SORT_DIGITS * n_tiles);
-    AG_LAUNCH_PDL(ctx, "sort_scatter_kernel", sort_scatter_kernel, n_tiles, SORT_TILE, 0, (const uint32_t*)keys[cur],
-                  (const uint32_t*)vals[cur], keys[cur ^ 1], vals[cur ^ 1], (const uint32_t*)hist, n_ids, shift, n_tiles);
-    cur ^= 1;
+  if (n_tiles <= SORT_FUSED_MAX_TILES) {
+    // passes + 1 launches: no key/position initialisation, no scan, no histogram launch after the first
+    const int64_t hist_entries = (int64_t)SORT_DIGITS * n_tiles;
+    AG_LAUNCH_PDL(ctx, "sort_hist_ids_kernel", sort_hist_ids_kernel, n_tiles, SORT_TILE, 0, ids, hist, hist + hist_entries,
+                  hist_entries * (passes - 1), n_ids, V, ctx->d_status);
+    for (int pass = 0; pass < passes; ++pass) {
+      uint32_t* h = hist + hist_entries * pass;
+      uint32_t* h_next = pass + 1 < passes ? h + hist_entries : nullptr;
+      if (pass == 0) {
+        AG_LAUNCH_PDL(ctx, "sort_scatter_fused_kernel", sort_scatter_fused_kernel<true>, n_tiles, SORT_TILE, 0, ids,
+                      (const uint32_t*)nullptr, (const uint32_t*)nullptr, keys[1], vals[1], (const uint32_t*)h, h_next,
+                      n_ids, V, 0, n_tiles);
+        cur = 1;
+      } else {
+        AG_LAUNCH_PDL(ctx, "sort_scatter_fused_kernel", sort_scatter_fused_kernel<false>, n_tiles, SORT_TILE, 0,
+                      (const int32_t*)nullptr, (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], keys[cur ^ 1],
+                      vals[cur ^ 1], (const uint32_t*)h, h_next, n_ids, V, pass * SORT_BITS, n_tiles);
+        cur ^= 1;
+      }
+    }
+  } else {
+    AG_LAUNCH_PDL(ctx, "sort_init_kernel", sort_init_kernel, n_tiles, SORT_TILE, 0, ids, keys[0], vals[0], n_ids, V,
+                  ctx->d_status);
+    for (int shift = 0; shift < bits; shift += SORT_BITS) {
+      AG_LAUNCH_PDL(ctx, "sort_hist_kernel", sort_hist_kernel, n_tiles, SORT_TILE, 0, (const uint32_t*)keys[cur], hist,
+                    n_ids, shift, n_tiles);
+      AG_LAUNCH_PDL(ctx, "sort_scan_kernel", sort_scan_kernel, 1, 1024, 0, hist, (int64_t)SORT_DIGITS * n_tiles);
+      AG_LAUNCH_PDL(ctx, "sort_scatter_kernel", sort_scatter_kernel, n_tiles, SORT_TILE, 0, (const uint32_t*)keys[cur],
+                    (const uint32_t*)vals[cur], keys[cur ^ 1], vals[cur ^ 1], (const uint32_t*)hist, n_ids, shift, n_tiles);
+      cur ^= 1;
+    }
   }
   // 4-element packets of a table row: 16 bytes in fp32, 8 bytes in bf16 storage
   const bool vec = (C % 4 == 0) && ag_aligned16(dout) && ag_aligned16(dtable);
   dim3 grid((unsigned)p.n_groups, (unsigned)((C + SEG_COLS - 1) / SEG_COLS));
+  // combine: about one resident wave of 1024-thread CTAs (two per SM) over all column slices
+  int64_t cx = (int64_t)ctx->sm_count * 2 / grid.y;
+  cx = cx < 1 ? 1 : (cx > p.n_groups ? p.n_groups : cx);
+  dim3 cgrid((unsigned)cx, grid.y);
   auto groups_vec = scatter_groups_kernel<true, TT>;
   auto combine_vec = scatter_combine_kernel<true, TT>;
   auto groups_scalar = scatter_groups_kernel<false, TT>;
   auto combine_scalar = scatter_combine_kernel<false, TT>;
   if (vec) {
     AG_LAUNCH_PDL(ctx, "scatter_groups_kernel", groups_vec, grid, SEG_THREADS, 0,
-                  (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], dout, dtable, partials, n_ids, C, V);
-    AG_LAUNCH_PDL(ctx, "segment_heads_kernel", segment_heads_kernel, (unsigned)((p.n_groups + 3) / 4), 128, 0,
-                  (const uint32_t*)keys[cur], heads, n_ids, (int)p.n_groups, V);
-    AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", combine_vec, grid, dim3(SEG_THREADS, SEG_SPLIT), 0,
-                  (const uint32_t*)keys[cur], (const long long*)heads, dtable, (const float*)partials, n_ids, C);
+                  (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], dout, dtable, partials, heads, (int)p.n_groups,
+                  n_ids, C, V);
+    AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", combine_vec, cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0,
+                  (const uint32_t*)keys[cur], (const long long*)heads, dtable, (const float*)partials, n_ids,
+                  (int64_t)p.n_groups, C);
   } else {
-    groups_scalar<<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials,
-                                                                         n_ids, C, V);
+    groups_scalar<<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials, heads,
+                                                         (int)p.n_groups, n_ids, C, V);
     AG_LAUNCHED(ctx, "scatter_groups_kernel");
-    segment_heads_kernel<<<(unsigned)((p.n_groups + 3) / 4), 128, 0, ctx->stream>>>(keys[cur], heads, n_ids,
-                                                                                     (int)p.n_groups, V);
-    AG_LAUNCHED(ctx, "segment_heads_kernel");
-    combine_scalar<<<grid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, dtable,
-                                                                                           partials, n_ids, C);
+    combine_scalar<<<cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, dtable, partials, n_ids,
+                                                                            (int64_t)p.n_groups, C);
     AG_LAUNCHED(ctx, "scatter_combine_kernel");
   }
   return AG_OK;

@@ -30,7 +30,8 @@ template <typename T, int KP, int KIND>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_forward_kernel(const T* x, const T* r, const float* __restrict__ gamma,
                     const float* __restrict__ beta, T* h, T* __restrict__ y, float* __restrict__ stat0,
-                    float* __restrict__ stat1, int64_t N, int C, float eps, int* status, int pdl_early) {
+                    float* __restrict__ stat1, int64_t N, int C, float eps, uint32_t stage_poll_limit, int* status,
+                    int pdl_early) {
   ag_pdl_wait();
   // Early trigger only when the whole grid is resident at once: otherwise the next kernel's CTAs,
   // which only wait, would take SM slots from this grid's later waves.
@@ -58,7 +59,7 @@ norm_forward_kernel(const T* x, const T* r, const float* __restrict__ gamma,
       }
     }
   } else if (gamma) {
-    ag_stage_vectors(s_gamma, gamma, s_beta, (KIND == kLayerNorm) ? beta : nullptr, C, &s_bar, status);
+    ag_stage_vectors(s_gamma, gamma, s_beta, (KIND == kLayerNorm) ? beta : nullptr, C, &s_bar, status, stage_poll_limit);
   }
 
   for (int64_t row = (int64_t)blockIdx.x * NORM_WARPS + warp; row < N; row += (int64_t)gridDim.x * NORM_WARPS) {
@@ -241,7 +242,7 @@ template <typename T, int KP, int KIND>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
                      const T* dres, T* dx, float* __restrict__ partials, int want_dgamma, int want_dbeta, int64_t N,
-                     int C, float eps, int* status, int pdl_early) {
+                     int C, float eps, uint32_t stage_poll_limit, int* status, int pdl_early) {
   ag_pdl_wait();
   if (pdl_early) ag_pdl_trigger();  // see norm_forward_kernel
   constexpr int NV = Pack<T>::N;
@@ -263,7 +264,7 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       for (int e = 0; e < NV; ++e) rg[p][e] = (gamma && col < C) ? __ldg(gamma + col + e) : 1.0f;
     }
   } else if (gamma) {
-    ag_stage_vectors(s_gamma, gamma, nullptr, nullptr, C, &s_bar, status);
+    ag_stage_vectors(s_gamma, gamma, nullptr, nullptr, C, &s_bar, status, stage_poll_limit);
   }
   float* my_g = s_acc + (size_t)warp * SLOTS * C;
   float* my_b = my_g + C;  // LayerNorm only
@@ -1023,6 +1024,13 @@ norm_backward_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
 // ---------------------------------------------------------------------------------------
 // host-side dispatch
 // ---------------------------------------------------------------------------------------
+// One-shot test hook: the next norm kernel that stages gamma/beta gives up its staging wait at once.
+inline uint32_t take_stage_poll_limit(ag_ctx* ctx) {
+  const uint32_t limit = ctx->debug_stage_expire ? 0u : (1u << 20);
+  ctx->debug_stage_expire = 0;
+  return limit;
+}
+
 inline int pick_kp(int packets_per_row) {
   const int need = (packets_per_row + 31) / 32;
   static const int kChoices[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
@@ -1074,15 +1082,8 @@ int launch_fwd_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const
   if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_forward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
   const int grid = persistent_grid(ctx, N, occ);
   AG_LAUNCH_PDL(ctx, "norm_forward_kernel", kern, grid, NORM_THREADS, smem, x, r, gamma, beta, h, y, s0, s1, N, C, eps,
-                ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
+                take_stage_poll_limit(ctx), ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
   return AG_OK;
-}
-
-// One-shot test hook: the next ring kernel gives up its staging wait at once.
-inline uint32_t take_stage_poll_limit(ag_ctx* ctx) {
-  const uint32_t limit = ctx->debug_stage_expire ? 0u : (1u << 20);
-  ctx->debug_stage_expire = 0;
-  return limit;
 }
 
 // Which shapes take the row ring.  Measured on B200 (back-to-back launches, operands rotated through
@@ -1181,7 +1182,7 @@ int launch_bwd_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, cons
   if (occ < 0) AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
   const int grid = persistent_grid(ctx, N, occ, max_grid);
   AG_LAUNCH_PDL(ctx, "norm_backward_kernel", kern, grid, NORM_THREADS, smem, dy, x, gamma, dres, dx, partials, wg, wb, N, C,
-                eps, ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
+                eps, take_stage_poll_limit(ctx), ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
   *grid_out = grid;
   return AG_OK;
 }
@@ -1417,8 +1418,9 @@ extern "C" int ag_layernorm_backward_noalloc(ag_ctx* ctx, const float* dy, const
                                        eps, /*small_workspace=*/true);
 }
 
-// Test hook for the unwind path of the gamma/beta staging (a wait that gives up): the next
-// row-ring norm kernel launched through ctx treats its staging wait as expired at once, records
+// Test hook for the unwind path of the gamma/beta staging (a wait that gives up): the next norm
+// kernel launched through ctx that stages these vectors in shared memory (rows of more than 512 fp32
+// columns, and every row-ring kernel) treats its staging wait as expired at once, records
 // AG_STATUS_STAGE_FALLBACK, lets the copy land and fills the vectors with plain loads.
 extern "C" int ag_debug_expire_staging(ag_ctx* ctx) {
   if (!ctx) return AG_ERR_INVALID;

@@ -356,11 +356,14 @@ def _zipf_ids(rng, V, n, s=1.1):
     return rng.choice(V, size=n, p=p).astype(np.int32)
 
 
-@pytest.mark.parametrize("V,C,n", [(151936, 1536, 65536), (5000, 100, 4099), (32768, 1280, 32768)])
+@pytest.mark.parametrize("V,C,n", [(151936, 1536, 65536), (5000, 100, 4099), (32768, 1280, 32768), (300, 64, 5000),
+                                   (700000, 8, 3000), (20000, 64, 300000)])
 def test_gather_scatter_full_size(V, C, n):
     """Config 4: 65536 Zipf(1.1) ids over a 151936 x 1536 table; forward bit-exact, backward
     within tolerance of np.add.at, bit-reproducible, and bit-exact for rows whose occurrences
-    fall inside one summation group."""
+    fall inside one summation group.  The other shapes cover the sort's pass counts (a table of 300
+    rows sorts in one 9-bit pass, 700000 rows need three) and the unfused sort that takes over
+    beyond 262144 ids."""
     ctx, alloc, be = G.env()
     rng = np.random.default_rng(1237)
     ids_ = _zipf_ids(rng, V, n).reshape(1, n) if V != 32768 else rng.integers(0, V, size=(1, n)).astype(np.int32)
