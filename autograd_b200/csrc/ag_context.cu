@@ -69,6 +69,14 @@ extern "C" int ag_ctx_create(int device, void* stream, ag_ctx** out) {
     e = getenv("AG_B200_NORM_RING");
     c->norm_ring = !e ? 2 : (e[0] == '0' ? 0 : 1);
     c->debug_stage_expire = 0;
+    // AG_B200_LINEAR_K_CHUNK: longest tensor-core accumulation chain (contraction elements) in the forward
+    // of the linear + bias + residual op; shorter chains = smaller error, more launches.  A multiple of 32.
+    e = getenv("AG_B200_LINEAR_K_CHUNK");
+    c->linear_k_chunk = 384;
+    if (e) {
+      const int v = atoi(e);
+      if (v >= 64 && v % 32 == 0) c->linear_k_chunk = v;
+    }
   }
   CREATE_CUDA(cudaMalloc(&c->d_status, sizeof(int)));
   CREATE_CUDA(cudaMemset(c->d_status, 0, sizeof(int)));

@@ -73,10 +73,11 @@ constexpr int SORT_WARPS = SORT_TILE / 32;
 
 // Out-of-range ids get the key V (sorted behind every valid id, dropped later).
 __global__ void __launch_bounds__(SORT_TILE)
-sort_init_kernel(const int32_t* __restrict__ ids, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals, int64_t n,
-                 int V, int* status) {
+sort_init_kernel(const int32_t* __restrict__ ids, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals,
+                 uint32_t* __restrict__ head_count, int64_t n, int V, int* status) {
   ag_pdl_wait();
   if (gridDim.x * gridDim.y <= 148) ag_pdl_trigger();  // single-wave grids let the next kernel be scheduled early
+  if (blockIdx.x == 0 && threadIdx.x == 0) *head_count = 0u;  // the list of head groups starts empty
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int id = ids[i];
@@ -210,9 +211,10 @@ __device__ __forceinline__ uint32_t sort_key_of(int id, int V) { return (id >= 0
 // hist0 and hist_later are tile-major: counter of (tile, digit) at [tile * SORT_DIGITS + digit].
 __global__ void __launch_bounds__(SORT_TILE)
 sort_hist_ids_kernel(const int32_t* __restrict__ ids, uint32_t* __restrict__ hist0, uint32_t* __restrict__ hist_later,
-                     int64_t later_entries, int64_t n, int V, int* status) {
+                     int64_t later_entries, uint32_t* __restrict__ head_count, int64_t n, int V, int* status) {
   ag_pdl_wait();
   if (gridDim.x <= 148) ag_pdl_trigger();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *head_count = 0u;  // the list of head groups starts empty
   __shared__ uint32_t s_cnt[SORT_DIGITS];
   for (int d = threadIdx.x; d < SORT_DIGITS; d += SORT_TILE) s_cnt[d] = 0;
   // the histograms of the later passes start at zero: this CTA clears its share
@@ -368,7 +370,8 @@ template <bool VEC, typename TT>
 __global__ void __launch_bounds__(SEG_THREADS)
 scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ pos,
                       const float* __restrict__ dout, TT* dtable, float* __restrict__ partials,
-                      long long* __restrict__ heads, int n_groups, int64_t n, int C, int V) {
+                      long long* __restrict__ heads, uint32_t* __restrict__ head_count,
+                      uint32_t* __restrict__ head_list, int n_groups, int64_t n, int C, int V) {
   constexpr bool BF = sizeof(TT) == 2;  // rounded storage: sum from zero, add the old row last
   ag_pdl_wait();
   __shared__ uint32_t s_key[SEG_GROUP + 2];  // [0] = key before the group, [1..G] group, [G+1] = key after
@@ -468,7 +471,7 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
   }
 
   // The first warp of the group's first column slice leaves the group's head record for the combine
-  // kernel: 2 * (last group holding entries of the segment) + (partial slot of the head run) when the
+  // kernel (after its own share of the sums, so that it costs the CTA nothing): 2 * (last group holding entries of the segment) + (partial slot of the head run) when the
   // group's LAST run opens a segment that continues into following groups and starts in this group,
   // else -1.  The decision comes from the keys already in shared memory; only a head group (rare)
   // probes the first keys of the following groups, 32 per ballot.
@@ -492,40 +495,39 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
         rec = g_end * 2 + (rb == 0 ? 0 : 1);
       }
     }
-    if (lane == 0) heads[blockIdx.x] = rec;
+    if (lane == 0) {
+      heads[blockIdx.x] = rec;
+      // head groups are also listed, so that the combine kernel visits nothing else; the order of the
+      // list varies from run to run, the work done per entry and its result do not
+      if (rec >= 0) head_list[atomicAdd(head_count, 1u)] = blockIdx.x;
+    }
   }
 }
 
-constexpr int SEG_SPLIT = 8;  // sub-ranges of a segment's groups summed side by side in the combine kernel
+constexpr int SEG_SPLIT = 4;  // sub-ranges of a segment's groups summed side by side in the combine kernel
 
-// Block (SEG_THREADS, SEG_SPLIT), grid (about one resident wave, column slices): a CTA walks the groups
-// g = blockIdx.x, blockIdx.x + gridDim.x, ... of its column slice, eight head records per look, and works
-// only on the heads of segments that span several groups (heads[g] >= 0, few).  For a head group, the
+// Block (SEG_THREADS, SEG_SPLIT), grid (about one resident wave, column slices): a CTA takes entries
+// blockIdx.x, blockIdx.x + gridDim.x, ... of the list of head groups (the heads of segments that span
+// several groups; few) for its column slice.  For a head group, the
 // partial slots of the segment's following groups are split into SEG_SPLIT consecutive sub-ranges; thread
 // row y adds its sub-range in group order (8 loads in flight), then row 0 adds
-// dtable row + head partial + sub-sum 0 + ... + sub-sum 7 and writes the dtable row.  Fixed order; a
+// dtable row + head partial + sub-sum 0 + ... + sub-sum 3 and writes the dtable row.  Fixed order; a
 // table row is written by exactly one CTA.
 template <bool VEC, typename TT>
 __global__ void __launch_bounds__(SEG_THREADS * SEG_SPLIT)
-scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __restrict__ heads, TT* dtable,
-                       const float* __restrict__ partials, int64_t n, int64_t n_groups, int C) {
+scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __restrict__ heads,
+                       const uint32_t* __restrict__ head_count, const uint32_t* __restrict__ head_list, TT* dtable,
+                       const float* __restrict__ partials, int64_t n, int C) {
   constexpr bool BF = sizeof(TT) == 2;
   ag_pdl_wait();
   __shared__ float4 s_sub[SEG_SPLIT][SEG_THREADS];
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
   const int y = threadIdx.y;
-  for (int64_t gb = blockIdx.x; gb < n_groups; gb += (int64_t)8 * gridDim.x) {
-    long long recs[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int64_t gq = gb + (int64_t)u * gridDim.x;
-      recs[u] = gq < n_groups ? heads[gq] : -1;
-    }
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const long long rec = recs[u];
-      if (rec < 0) continue;  // uniform across the CTA
-      const int64_t grp = gb + (int64_t)u * gridDim.x;
+  const uint32_t n_heads = *head_count;
+  {
+    for (uint32_t hi = blockIdx.x; hi < n_heads; hi += gridDim.x) {
+      const int64_t grp = head_list[hi];
+      const long long rec = heads[grp];
       const int64_t g_end = rec >> 1;
       const int head_slot = (int)(rec & 1);
       const int64_t g0 = grp * SEG_GROUP;
@@ -590,7 +592,8 @@ inline ScatterPlan scatter_plan(int64_t n, int C) {
   }
   p.off_hist = off;  // one histogram per pass when the passes are fused (few tiles), else one in all
   off += align256((size_t)SORT_DIGITS * p.n_tiles * 4 * (p.n_tiles <= SORT_FUSED_MAX_TILES ? SORT_MAX_PASSES : 1));
-  p.off_heads = off; off += align256((size_t)p.n_groups * 8);   // head record of every group
+  // head records: a counter (256 bytes), the record of every group, the list of head groups
+  p.off_heads = off; off += 256 + align256((size_t)p.n_groups * 8) + align256((size_t)p.n_groups * 4);
   p.off_partials = off; off += align256((size_t)p.n_groups * 2 * C * 4);
   p.total = off;
   return p;
@@ -647,7 +650,9 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
   uint32_t* vals[2] = {reinterpret_cast<uint32_t*>(base + p.off_vals[0]), reinterpret_cast<uint32_t*>(base + p.off_vals[1])};
   uint32_t* hist = reinterpret_cast<uint32_t*>(base + p.off_hist);
   float* partials = reinterpret_cast<float*>(base + p.off_partials);
-  long long* heads = reinterpret_cast<long long*>(base + p.off_heads);
+  uint32_t* head_count = reinterpret_cast<uint32_t*>(base + p.off_heads);
+  long long* heads = reinterpret_cast<long long*>(base + p.off_heads + 256);
+  uint32_t* head_list = reinterpret_cast<uint32_t*>(base + p.off_heads + 256 + align256((size_t)p.n_groups * 8));
   const int n_tiles = (int)p.n_tiles;
   // keys are in [0, V]: sort just enough 9-bit digits to cover V
   int bits = 1;
@@ -658,7 +663,7 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
     // passes + 1 launches: no key/position initialisation, no scan, no histogram launch after the first
     const int64_t hist_entries = (int64_t)SORT_DIGITS * n_tiles;
     AG_LAUNCH_PDL(ctx, "sort_hist_ids_kernel", sort_hist_ids_kernel, n_tiles, SORT_TILE, 0, ids, hist, hist + hist_entries,
-                  hist_entries * (passes - 1), n_ids, V, ctx->d_status);
+                  hist_entries * (passes - 1), head_count, n_ids, V, ctx->d_status);
     for (int pass = 0; pass < passes; ++pass) {
       uint32_t* h = hist + hist_entries * pass;
       uint32_t* h_next = pass + 1 < passes ? h + hist_entries : nullptr;
@@ -675,8 +680,8 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
       }
     }
   } else {
-    AG_LAUNCH_PDL(ctx, "sort_init_kernel", sort_init_kernel, n_tiles, SORT_TILE, 0, ids, keys[0], vals[0], n_ids, V,
-                  ctx->d_status);
+    AG_LAUNCH_PDL(ctx, "sort_init_kernel", sort_init_kernel, n_tiles, SORT_TILE, 0, ids, keys[0], vals[0], head_count,
+                  n_ids, V, ctx->d_status);
     for (int shift = 0; shift < bits; shift += SORT_BITS) {
       AG_LAUNCH_PDL(ctx, "sort_hist_kernel", sort_hist_kernel, n_tiles, SORT_TILE, 0, (const uint32_t*)keys[cur], hist,
                     n_ids, shift, n_tiles);
@@ -689,8 +694,8 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
   // 4-element packets of a table row: 16 bytes in fp32, 8 bytes in bf16 storage
   const bool vec = (C % 4 == 0) && ag_aligned16(dout) && ag_aligned16(dtable);
   dim3 grid((unsigned)p.n_groups, (unsigned)((C + SEG_COLS - 1) / SEG_COLS));
-  // combine: about one resident wave of 1024-thread CTAs (two per SM) over all column slices
-  int64_t cx = (int64_t)ctx->sm_count * 2 / grid.y;
+  // combine: about one resident wave of 512-thread CTAs (four per SM) over all column slices
+  int64_t cx = (int64_t)ctx->sm_count * 4 / grid.y;
   cx = cx < 1 ? 1 : (cx > p.n_groups ? p.n_groups : cx);
   dim3 cgrid((unsigned)cx, grid.y);
   auto groups_vec = scatter_groups_kernel<true, TT>;
@@ -699,17 +704,17 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
   auto combine_scalar = scatter_combine_kernel<false, TT>;
   if (vec) {
     AG_LAUNCH_PDL(ctx, "scatter_groups_kernel", groups_vec, grid, SEG_THREADS, 0,
-                  (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], dout, dtable, partials, heads, (int)p.n_groups,
-                  n_ids, C, V);
+                  (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], dout, dtable, partials, heads, head_count,
+                  head_list, (int)p.n_groups, n_ids, C, V);
     AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", combine_vec, cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0,
-                  (const uint32_t*)keys[cur], (const long long*)heads, dtable, (const float*)partials, n_ids,
-                  (int64_t)p.n_groups, C);
+                  (const uint32_t*)keys[cur], (const long long*)heads, (const uint32_t*)head_count,
+                  (const uint32_t*)head_list, dtable, (const float*)partials, n_ids, C);
   } else {
-    groups_scalar<<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials, heads,
-                                                         (int)p.n_groups, n_ids, C, V);
+    groups_scalar<<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials, heads, head_count,
+                                                         head_list, (int)p.n_groups, n_ids, C, V);
     AG_LAUNCHED(ctx, "scatter_groups_kernel");
-    combine_scalar<<<cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, dtable, partials, n_ids,
-                                                                            (int64_t)p.n_groups, C);
+    combine_scalar<<<cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, head_count, head_list, dtable,
+                                                                            partials, n_ids, C);
     AG_LAUNCHED(ctx, "scatter_combine_kernel");
   }
   return AG_OK;

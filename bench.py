@@ -425,13 +425,21 @@ def run_b200(a):
         per = torch.stack(allr).cpu().numpy() / a.steps
         comm = {"small_bucket_and_loss_ms": round(float(per[:, 1].max()), 4),
                 "table_gradient_bucket_ms": round(float(per[:, 2].max()), 4),
+                # the first collective of a step is where a rank waits for the slowest one: its shortest time
+                # over the ranks is what the exchange itself costs, the rest is waiting
+                "small_bucket_and_loss_ms_min_over_ranks": round(float(per[:, 1].min()), 4),
+                "table_gradient_bucket_ms_min_over_ranks": round(float(per[:, 2].min()), 4),
+                "kernel_skew_ms": round(float(per[:, 3].max() - per[:, 3].min()), 4),
                 "rank_skew_ms": round(float(per[:, 0].max() - per[:, 0].min()), 4),
                 "per_rank_step_ms": [round(float(v), 3) for v in per[:, 0]],
                 "per_rank_kernel_ms": [round(float(v), 3) for v in per[:, 3]],
-                "note": "CUDA-event pairs around each allreduce in the breakdown pass, max over ranks, per step; the time "
-                        "inside a collective includes waiting for the slowest rank to arrive (the ranks' steps run at "
-                        "the power cap and differ, see per_rank_kernel_ms); rank_skew_ms = max - min over ranks of the "
-                        "device time of the timed steps"}
+                "per_rank_small_bucket_ms": [round(float(v), 3) for v in per[:, 1]],
+                "per_rank_table_bucket_ms": [round(float(v), 3) for v in per[:, 2]],
+                "note": "CUDA-event pairs around each allreduce in the breakdown pass, per step; max over ranks unless "
+                        "named otherwise.  The time inside a collective includes waiting for the slowest rank to arrive: "
+                        "the ranks' steps run at the power cap and differ (per_rank_kernel_ms = sum of the step's own "
+                        "kernel families, kernel_skew_ms its spread).  rank_skew_ms = max - min over ranks of the device "
+                        "time of the timed steps (small, since every step ends in a collective)"}
         t = torch.tensor([ms_dev, ms_e2e, ms_bf16 or 0.0, ms_x3 or 0.0], device=f"cuda:{local}", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e = float(t[0]), float(t[1])
