@@ -25,7 +25,7 @@ struct LinPlan {
   size_t total_fwd, total_bwd;
 };
 
-constexpr int COLSUM_ROWS = 64;  // partial rows of the bias-gradient reduction
+constexpr int COLSUM_ROWS = 256;  // partial rows of the bias-gradient reduction
 
 LinPlan lin_plan(int64_t N, int K, int C, int precision) {
   LinPlan p;
@@ -59,9 +59,12 @@ colsum_partial_kernel(const float* __restrict__ g, int64_t N, int C, float* __re
   const int64_t r1 = r0 + per < N ? r0 + per : N;
   float acc = 0.0f;
   int64_t r = r0;
-  for (; r + 4 <= r1; r += 4) {
-    const float a0 = g[r * C + c], a1 = g[(r + 1) * C + c], a2 = g[(r + 2) * C + c], a3 = g[(r + 3) * C + c];
-    acc += a0; acc += a1; acc += a2; acc += a3;
+  for (; r + 8 <= r1; r += 8) {  // eight rows in flight, added in row order
+    float a[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a[u] = __ldcs(g + (r + u) * C + c);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc += a[u];
   }
   for (; r < r1; ++r) acc += g[r * C + c];
   partial[(int64_t)blockIdx.y * C + c] = acc;
@@ -72,7 +75,15 @@ colsum_final_kernel(const float* __restrict__ partial, int P, int C, float* __re
   const int c = blockIdx.x * 256 + threadIdx.x;
   if (c >= C) return;
   float acc = out[c];
-  for (int p = 0; p < P; ++p) acc += partial[(int64_t)p * C + c];
+  int p = 0;
+  for (; p + 8 <= P; p += 8) {
+    float a[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a[u] = partial[(int64_t)(p + u) * C + c];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc += a[u];
+  }
+  for (; p < P; ++p) acc += partial[(int64_t)p * C + c];
   out[c] = acc;
 }
 
