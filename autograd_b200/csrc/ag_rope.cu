@@ -1,17 +1,19 @@
 // Rotate-half RoPE applied in place to q (B,T,H,D) and k (B,T,HKV,D).
 //
-// The (token, head, packet) space is flattened and dealt out to CTAs in contiguous slabs.  A
-// thread owns one 16-byte packet of the low half of a head together with the matching packet of
-// the high half, so both halves are read once and written once; its cos/sin entries come
-// straight from the (L2-resident) tables.  All loads of a thread (four packet pairs) are issued
-// in one burst before the first store: there is no shared-memory stage and no barrier.  Shapes where D/2 is not a multiple of the packet width use a scalar
-// kernel.
+// Work item = (token, group of four heads, 16-byte packet of the low half).  A thread loads the cos/sin
+// entries of its packet once and applies them to the matching packets of up to four heads (q heads
+// first, then k heads): the table traffic per data byte is a quarter of one lookup per head, which
+// matters for bf16 storage, where a 16-byte data packet needs 64 bytes of fp32 table entries.  Both
+// halves of a head are read once and written once; all loads of a thread (eight packets and the
+// table entries) are issued in one burst before the first store: there is no shared-memory stage and
+// no barrier.  Consecutive threads take consecutive packets of one head half (256 / 128 contiguous
+// bytes at head_dim 128).  Shapes where D/2 is not a multiple of the packet width use a scalar kernel.
 #include "ag_common.cuh"
 
 namespace {
 
 constexpr int ROPE_THREADS = 256;
-constexpr int ROPE_MAX_BYTES = 64;  // bytes of each half a thread keeps in flight (4 fp32 / 2 bf16 packets)
+constexpr int ROPE_HEADS = 4;  // heads per work item
 
 template <typename T>
 __global__ void __launch_bounds__(ROPE_THREADS)
@@ -20,54 +22,54 @@ rope_kernel(T* q, T* k, const float* __restrict__ cos_tab, const float* __restri
   ag_pdl_wait();
   ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
-  constexpr int ROPE_MAX_ITEMS = ROPE_MAX_BYTES / 16 * 4 / NV;  // 4 packet pairs for fp32, 2 for bf16
   const int d2 = D >> 1;
-  const int ppd = d2 / NV;                     // packets per half head
-  const int items = (H + HKV) * ppd;           // packet pairs per token
-  const int64_t total = tokens * items;        // packet pairs of the whole call, token-major
-  // A CTA covers ROPE_THREADS * ROPE_MAX_ITEMS consecutive packet pairs; a thread takes every
-  // ROPE_THREADS-th of them, so a warp touches 32 consecutive packets (512 contiguous bytes per
-  // half) and every thread has ROPE_MAX_ITEMS independent load groups in flight.
-  const int64_t base = (int64_t)blockIdx.x * (ROPE_THREADS * ROPE_MAX_ITEMS) + threadIdx.x;
-  float lo[ROPE_MAX_ITEMS][NV], hi[ROPE_MAX_ITEMS][NV], c[ROPE_MAX_ITEMS][NV], s[ROPE_MAX_ITEMS][NV];
-  T* ptr[ROPE_MAX_ITEMS];
+  const int ppd = d2 / NV;                                  // packets per half head
+  const int groups = (H + HKV + ROPE_HEADS - 1) / ROPE_HEADS;
+  const int64_t total = tokens * groups * ppd;              // work items, token-major
+  const int64_t g = (int64_t)blockIdx.x * ROPE_THREADS + threadIdx.x;
+  if (g >= total) return;
+  const int col = (int)(g % ppd) * NV;
+  const int64_t rest = g / ppd;
+  const int group = (int)(rest % groups);
+  const int64_t tok = rest / groups;
+  const int t = (int)(tok % T_len);
+  typename Pack<T>::Raw lo[ROPE_HEADS], hi[ROPE_HEADS];  // kept as loaded: bf16 packets are widened one head at a time
+  float c[NV], s[NV];
+  T* ptr[ROPE_HEADS];
 #pragma unroll
-  for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
-    const int64_t g = base + (int64_t)u * ROPE_THREADS;
+  for (int u = 0; u < ROPE_HEADS; ++u) {
+    const int head = group * ROPE_HEADS + u;
     ptr[u] = nullptr;
-    if (g < total) {
-      const int64_t tok = g / items;
-      const int it = (int)(g - tok * items);
-      const int head = it / ppd;
-      const int col = (it - head * ppd) * NV;
-      const int t = (int)(tok % T_len);
+    if (head < H + HKV) {
       T* hp = head < H ? q + tok * q_stride + (int64_t)head * D : k + tok * k_stride + (int64_t)(head - H) * D;
       ptr[u] = hp + col;
-      Pack<T>::load(ptr[u], lo[u]);
-      Pack<T>::load(ptr[u] + d2, hi[u]);
-      const float* crow = cos_tab + (int64_t)t * d2 + col;   // L2-resident tables (T * D/2 floats)
-      const float* srow = sin_tab + (int64_t)t * d2 + col;
+      lo[u] = Pack<T>::load_raw(ptr[u]);
+      hi[u] = Pack<T>::load_raw(ptr[u] + d2);
+    }
+  }
+  {
+    const float* crow = cos_tab + (int64_t)t * d2 + col;   // L2-resident tables (T * D/2 floats)
+    const float* srow = sin_tab + (int64_t)t * d2 + col;
 #pragma unroll
-      for (int e = 0; e < NV; e += 4) {
-        const float4 cv = __ldg(reinterpret_cast<const float4*>(crow + e));
-        const float4 sv = __ldg(reinterpret_cast<const float4*>(srow + e));
-        c[u][e] = cv.x; c[u][e + 1] = cv.y; c[u][e + 2] = cv.z; c[u][e + 3] = cv.w;
-        s[u][e] = sv.x; s[u][e + 1] = sv.y; s[u][e + 2] = sv.z; s[u][e + 3] = sv.w;
-      }
+    for (int e = 0; e < NV; e += 4) {
+      const float4 cv = __ldg(reinterpret_cast<const float4*>(crow + e));
+      const float4 sv = __ldg(reinterpret_cast<const float4*>(srow + e));
+      c[e] = cv.x; c[e + 1] = cv.y; c[e + 2] = cv.z; c[e + 3] = cv.w;
+      s[e] = sgn * sv.x; s[e + 1] = sgn * sv.y; s[e + 2] = sgn * sv.z; s[e + 3] = sgn * sv.w;
     }
   }
 #pragma unroll
-  for (int u = 0; u < ROPE_MAX_ITEMS; ++u) {
+  for (int u = 0; u < ROPE_HEADS; ++u) {
     if (ptr[u]) {
-      float olo[NV], ohi[NV];
+      float vlo[NV], vhi[NV], olo[NV], ohi[NV];
+      Pack<T>::unpack_raw(lo[u], vlo);
+      Pack<T>::unpack_raw(hi[u], vhi);
 #pragma unroll
       for (int e = 0; e < NV; ++e) {
-        const float cc = c[u][e];
-        const float ss = sgn * s[u][e];
         // sgn=+1: lo*c - hi*s , lo*s + hi*c   (backend.py:1413-1414)
         // sgn=-1: lo*c + hi*s , -lo*s + hi*c  (backend.py:1396-1397)
-        olo[e] = lo[u][e] * cc - hi[u][e] * ss;
-        ohi[e] = lo[u][e] * ss + hi[u][e] * cc;
+        olo[e] = vlo[e] * c[e] - vhi[e] * s[e];
+        ohi[e] = vlo[e] * s[e] + vhi[e] * c[e];
       }
       Pack<T>::store(ptr[u], olo);
       Pack<T>::store(ptr[u] + d2, ohi);
@@ -109,9 +111,8 @@ int rope_t(ag_ctx* ctx, void* qv, void* kv, const float* cos_tab, const float* s
                       ag_aligned16(cos_tab) && ag_aligned16(sin_tab);
   if (vec_ok) {
     const int hkv = k ? HKV : 0;
-    const int64_t total = tokens * (int64_t)((H + hkv) * (d2 / NV));
-    const int64_t per_cta = (int64_t)ROPE_THREADS * (ROPE_MAX_BYTES / 16 * 4 / NV);
-    AG_LAUNCH_PDL(ctx, "rope_kernel", rope_kernel<T>, (unsigned)((total + per_cta - 1) / per_cta), ROPE_THREADS, 0, q, k,
+    const int64_t total = tokens * (int64_t)((H + hkv + ROPE_HEADS - 1) / ROPE_HEADS) * (d2 / NV);
+    AG_LAUNCH_PDL(ctx, "rope_kernel", rope_kernel<T>, (unsigned)((total + ROPE_THREADS - 1) / ROPE_THREADS), ROPE_THREADS, 0, q, k,
                   cos_tab, sin_tab, tokens, T_len, H, hkv, D, qs, ks, sgn);
   } else {
     rope_scalar_kernel<T><<<(unsigned)tokens, ROPE_THREADS, 0, ctx->stream>>>(q, k, cos_tab, sin_tab, T_len, H,

@@ -406,3 +406,51 @@ def test_lse_side_buffers_are_bounded_and_released():
         be.get_backward_kernel(losses[0][1].op)(losses[0][1].inputs, losses[0][1].outputs)
     be.release_side_buffers()
     assert not be._side
+
+
+def test_host_cost_of_the_backend_layer_per_step():
+    """The benchmark's end-to-end arm drives the C ABI directly; a graph runtime goes through the backend's
+    callables, which add Python work per call (shape arithmetic, gradient targets, scratch slots, the CE
+    descriptor).  This replays the callable sequence of one fused-layer step of the depth-20 model on a
+    recording context - 1 gather, 41 LayerNorm, 20 GELU, 1 fused linear + CE, forward and backward, plus the
+    runtime's zero-fills - and bounds the host time: it has to stay far below the 67-69 ms the GPU needs for
+    the step, so that launches stay ahead of the device."""
+    import time
+    ctx, alloc, be = _fake_env()
+    B, T, C, V, L, I = 16, 2048, 1280, 32768, 20, 5120
+    ids, tg = _t(alloc, (B, T), np.int32, requires_grad=False), _t(alloc, (B, T), np.int32, requires_grad=False)
+    table = _t(alloc, (V, C), grad=True)
+    x0 = _t(alloc, (B, T, C), grad=True)
+    nodes = [hg.make_node(hg.make_op("GatherOp"), (ids, table), (x0,))]
+    h = x0
+    for _ in range(2 * L + 1):
+        g, b, y = _t(alloc, (C,), grad=True), _t(alloc, (C,), grad=True), _t(alloc, (B, T, C), grad=True)
+        nodes.append(hg.make_node(hg.make_op("LayerNormOp", eps=1e-5, normalized_dim=-1), (h, g, b), (y,)))
+        h = y
+    for _ in range(L):
+        u, a = _t(alloc, (B, T, I), grad=True), _t(alloc, (B, T, I), grad=True)
+        nodes.append(hg.make_node(hg.make_op("GELUOp"), (u,), (a,)))
+    loss = _t(alloc, (1,), grad=True)
+    nodes.append(hg.make_node(hg.make_op("FusedLinearCrossEntropyOp", ignore_index=-1), (h, table, tg), (loss,)))
+    fwd = [be.get_forward_kernel(n.op) for n in nodes]
+    bwd = [be.get_backward_kernel(n.op) for n in nodes]
+    grads = [t.grad for n in nodes for t in n.inputs + n.outputs if t.grad is not None]
+
+    def step():
+        for g_ in grads:                       # the runtime's zero_grad / clear lists (runtime.py:828-854)
+            be.fill(g_, 0.0)
+        for n, f in zip(nodes, fwd):
+            f(n.inputs, n.outputs)
+        for n, f in zip(reversed(nodes), reversed(bwd)):
+            f(n.inputs, n.outputs)
+
+    step()
+    ctx.calls.clear(); ctx.kwargs.clear()
+    t0 = time.perf_counter()
+    for _ in range(5):
+        step()
+    per_step_ms = 1e3 * (time.perf_counter() - t0) / 5
+    launches = sum(1 for c in ctx.calls if c[0] not in ("free",)) / 5
+    print(f"host time of the backend layer: {per_step_ms:.2f} ms per step for {launches:.0f} C-ABI calls")
+    assert launches >= 2 * (1 + 41 + 20 + 1)
+    assert per_step_ms < 20.0, per_step_ms
