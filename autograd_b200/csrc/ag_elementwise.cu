@@ -163,6 +163,9 @@ struct GeluFwd {
 
 __global__ void __launch_bounds__(EW_THREADS) gelu_forward_kernel(GeluFwd f, int64_t n, int early) { ew_drive<4>(n, f, early); }
 
+// HAS_RES: dx = dres + local (the accumulate-into-grad form); without it no registers are held for dres,
+// which lets a third CTA share the SM (more loads in flight).
+template <bool HAS_RES>
 struct GeluBwd {
   const float* x;
   const float* dy;
@@ -170,30 +173,34 @@ struct GeluBwd {
   float* dx;
   template <int U>
   __device__ __forceinline__ void packets(int64_t i, int64_t stride) {
-    float a[U][4], g[U][4], r[U][4];
+    float a[U][4], g[U][4], r[HAS_RES ? U : 1][4];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       Pack<float>::load_stream(x + (i + u * stride) * 4, a[u]);
       Pack<float>::load_stream(dy + (i + u * stride) * 4, g[u]);
-      if (dres) Pack<float>::load(dres + (i + u * stride) * 4, r[u]);
+      if constexpr (HAS_RES) Pack<float>::load(dres + (i + u * stride) * 4, r[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float local = g[u][e] * gelu_grad1(a[u][e]);
-        a[u][e] = dres ? r[u][e] + local : local;
+        const float local = g[u][e] * gelu_grad1(a[u][e]);
+        if constexpr (HAS_RES) a[u][e] = r[u][e] + local;
+        else a[u][e] = local;
       }
       Pack<float>::store(dx + (i + u * stride) * 4, a[u]);
     }
   }
   __device__ __forceinline__ void scalar(int64_t j) {
-    float local = dy[j] * gelu_grad1(x[j]);
-    dx[j] = dres ? dres[j] + local : local;
+    const float local = dy[j] * gelu_grad1(x[j]);
+    dx[j] = HAS_RES ? dres[j] + local : local;
   }
 };
 
-__global__ void __launch_bounds__(EW_THREADS) gelu_backward_kernel(GeluBwd f, int64_t n, int early) { ew_drive<4>(n, f, early); }
+template <bool HAS_RES>
+__global__ void __launch_bounds__(EW_THREADS) gelu_backward_kernel(GeluBwd<HAS_RES> f, int64_t n, int early) {
+  ew_drive<4>(n, f, early);
+}
 
 // ---------------------------------------------------------------------------- SwiGLU
 // backend.py:1117-1120: 1 / (exp(-g) + 1).  FAST: ex2-based __expf and the approximate reciprocal,
@@ -566,7 +573,12 @@ extern "C" int ag_gelu_backward(ag_ctx* ctx, const float* x, const float* dy, co
   AG_REQUIRE(ctx, all_aligned16(x, dy, dres, dx), "ag_gelu_backward: pointers must be 16-byte aligned");
   {
     const int grid = ew_grid(ctx, n / 4, 8);
-    AG_LAUNCH_PDL(ctx, "gelu_backward_kernel", gelu_backward_kernel, grid, EW_THREADS, 0, GeluBwd{x, dy, dres, dx}, n, ew_early(ctx, grid));
+    if (dres)
+      AG_LAUNCH_PDL(ctx, "gelu_backward_kernel", gelu_backward_kernel<true>, grid, EW_THREADS, 0,
+                    GeluBwd<true>{x, dy, dres, dx}, n, ew_early(ctx, grid));
+    else
+      AG_LAUNCH_PDL(ctx, "gelu_backward_kernel", gelu_backward_kernel<false>, grid, EW_THREADS, 0,
+                    GeluBwd<false>{x, dy, dres, dx}, n, ew_early(ctx, grid));
   }
   return AG_OK;
 }

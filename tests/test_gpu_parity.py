@@ -1109,3 +1109,62 @@ def test_staging_wait_that_gives_up_takes_the_plain_load_path():
     ctx.synchronize()
     assert ctx.status() == 0
     G.free(x, r, gamma, beta, h, y)
+
+
+@pytest.mark.parametrize("ring", ["0", "1"])
+def test_norm_kernels_with_one_design_forced(ring, monkeypatch):
+    """By default the norm kernels choose between rows in registers and the shared-memory row ring per
+    shape; AG_B200_NORM_RING (read when a context is created) forces one of them.  Both designs must agree
+    with the oracle on every shape the ring can take: fp32 and bf16 storage, with and without gamma, a
+    single row, fewer rows than consumer warps, many rounds through the ring, the residual-gradient add."""
+    import autograd_b200 as ag
+    from autograd_b200 import hostgraph as hg
+    monkeypatch.setenv("AG_B200_NORM_RING", ring)
+    ctx, alloc, be = ag.create(0)
+    try:
+        rng = np.random.default_rng(1246)
+
+        def dev(a, dtype=np.float32):
+            t = hg.HostTensor(a.shape, dtype, requires_grad=False)
+            t.storage = alloc.alloc(t.shape, dtype)
+            be.copy_from_host(t, a)
+            return t
+
+        for N, C, bf, with_gamma in ((1, 384, False, True), (5, 1280, False, True), (4097, 1536, False, True),
+                                     (3001, 256, True, True), (7, 1536, True, False), (2500, 640, False, False)):
+            st = np.uint16 if bf else np.float32
+            tol_f, tol_b = (TOL_BF16, TOL_BF16) if bf else (TOL_FWD, TOL_BWD)
+            prep = _bf16 if bf else (lambda a: a)
+            x_, dz_, res_ = (prep(rng.standard_normal((N, C), dtype=np.float32)) for _ in range(3))
+            g_ = (1 + 0.02 * rng.standard_normal(C)).astype(np.float32) if with_gamma else None
+            x, dz, dx = dev(x_, st), dev(dz_, st), dev(res_, st)
+            gamma = dev(g_) if with_gamma else None
+            dgam = dev(np.zeros(C, np.float32)) if with_gamma else None
+            y, inv = dev(np.zeros((N, C), np.float32), st), dev(np.zeros(N, np.float32))
+            be.rmsnorm_forward(x, gamma, y, 1e-6, inv)
+            z_ref, inv_ref = O.rmsnorm_forward(x_, g_, 1e-6)
+            assert_close(be.copy_to_host(inv), inv_ref, TOL_FWD, f"inv_rms N={N} C={C} bf16={bf}")
+            assert_close(be.copy_to_host(y), z_ref, tol_f, f"rmsnorm y N={N} C={C} bf16={bf}")
+            be.rmsnorm_backward(dz, x, gamma, 1e-6, dx, dgam, dres=dx)
+            dx_ref, dg_ref = O.rmsnorm_backward(x_, g_, dz_, 1e-6, res_, np.zeros(C, np.float32) if with_gamma else None)
+            assert_close(be.copy_to_host(dx), dx_ref, tol_b, f"rmsnorm dx N={N} C={C} bf16={bf}")
+            if with_gamma:
+                assert_close(be.copy_to_host(dgam), dg_ref, tol_b, f"rmsnorm dgamma N={N} C={C} bf16={bf}")
+            if not bf and with_gamma:      # LayerNorm with the fused residual add, same shape
+                r_, b_ = rng.standard_normal((N, C), dtype=np.float32), (0.02 * rng.standard_normal(C)).astype(np.float32)
+                r, beta, h = dev(r_), dev(b_), dev(np.zeros((N, C), np.float32))
+                be.fused_add_layernorm_forward(x, r, gamma, beta, h, y, 1e-5)
+                h_ref, y_ref, _, _ = O.add_layernorm_forward(x_, r_, g_, b_, 1e-5)
+                assert np.array_equal(be.copy_to_host(h), h_ref)
+                assert_close(be.copy_to_host(y), y_ref, TOL_FWD, f"layernorm y N={N} C={C}")
+                for t in (r, beta, h):
+                    alloc.free(t.storage)
+            ctx.synchronize()
+            for t in (x, dz, dx, gamma, dgam, y, inv):
+                if t is not None:
+                    alloc.free(t.storage)
+        assert ctx.status() == 0
+    finally:
+        ctx.synchronize()
+        alloc.free()
+        ctx.close()
