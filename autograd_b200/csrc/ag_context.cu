@@ -69,6 +69,10 @@ extern "C" int ag_ctx_create(int device, void* stream, ag_ctx** out) {
     e = getenv("AG_B200_NORM_RING");
     c->norm_ring = !e ? 2 : (e[0] == '0' ? 0 : 1);
     c->debug_stage_expire = 0;
+    // AG_B200_NORM_PAIR: norm backward with two warps per row: 0 never, 1 whenever the shape fits, unset =
+    // fp32 rows of 1024 columns and more (diagnostics, A/B measurements)
+    e = getenv("AG_B200_NORM_PAIR");
+    c->norm_pair = !e ? 2 : (e[0] == '0' ? 0 : 1);
     // AG_B200_LINEAR_K_CHUNK: longest tensor-core accumulation chain (contraction elements) in the forward
     // of the linear + bias + residual op; shorter chains = smaller error, more launches.  A multiple of 32.
     e = getenv("AG_B200_LINEAR_K_CHUNK");

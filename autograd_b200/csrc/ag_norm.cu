@@ -414,6 +414,332 @@ norm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// backward, two warps per row
+// ---------------------------------------------------------------------------------------
+// Same arithmetic as norm_backward_kernel, but a row is shared by a pair of warps: each lane holds
+// half as many packets of x, dy and the residual gradient, so the kernel needs about 100 registers
+// instead of 170 and two CTAs fit an SM - twice the warps, each with half the dependent work per row.
+// The three row reductions go through the pair: warp sums, two words of shared memory, a named
+// barrier of 64 threads, and both warps add the two halves in the same order.  With wide rows the
+// one-warp kernel is bound by its per-row dependency chains once the SM clock drops under the power
+// cap (0.73 of the copy rate inside the benchmark step against 0.91 alone); this one is for those rows.
+constexpr int PAIR_TEAMS = NORM_WARPS / 2;
+
+// Sum of `v` over the 64 lanes of a warp pair.  `slot` alternates between consecutive calls, so a
+// warp that runs one reduction ahead never overwrites words its partner is still reading.
+__device__ __forceinline__ float pair_sum(float v, float* s_red, int team, int half, int lane, int slot) {
+  v = ag_warp_sum(v);
+  float* w = s_red + (team * 2 + slot) * 2;
+  if (lane == 0) w[half] = v;
+  asm volatile("bar.sync %0, 64;" ::"r"(team + 1) : "memory");
+  return w[0] + w[1];
+}
+
+template <typename T, int KP2, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS, 2)
+norm_backward_pair_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
+                          const T* dres, T* dx, float* __restrict__ partials, int want_dgamma, int want_dbeta,
+                          int64_t N, int C, float eps, uint32_t stage_poll_limit, int* status, int pdl_early) {
+  ag_pdl_wait();
+  if (pdl_early) ag_pdl_trigger();
+  constexpr int NV = Pack<T>::N;
+  constexpr int SLOTS = norm_bwd_slots<KIND>();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* s_gamma = reinterpret_cast<float*>(smem_raw);  // C floats
+  float* s_acc = s_gamma + C;                           // PAIR_TEAMS * SLOTS * C floats: column sums per team
+  __shared__ __align__(8) uint64_t s_bar;
+  __shared__ float s_red[PAIR_TEAMS * 2 * 2];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int team = warp >> 1, half = warp & 1;
+  const int tl = half * 32 + lane;  // lane of the pair, 0..63
+  const float inv_c = 1.0f / (float)C;
+  if (gamma) ag_stage_vectors(s_gamma, gamma, nullptr, nullptr, C, &s_bar, status, stage_poll_limit);
+  float* my_g = s_acc + (size_t)team * SLOTS * C;
+  float* my_b = my_g + C;  // LayerNorm only
+  // each lane zeroes exactly the columns it will accumulate into: no cross-lane hazard
+#pragma unroll
+  for (int p = 0; p < KP2; ++p) {
+    const int col = (p * 64 + tl) * NV;
+    if (col < C) {
+#pragma unroll
+      for (int e = 0; e < NV; ++e) {
+        my_g[col + e] = 0.0f;
+        if (KIND == kLayerNorm) my_b[col + e] = 0.0f;
+      }
+    }
+  }
+  int red = 0;  // parity of the next pair reduction
+  for (int64_t row = (int64_t)blockIdx.x * PAIR_TEAMS + team; row < N; row += (int64_t)gridDim.x * PAIR_TEAMS) {
+    float v[KP2][NV], g[KP2][NV], o[KP2][NV];
+    const T* xr = x + row * C;
+    const T* gr = dy + row * C;
+    const T* drr = (dres && dx) ? dres + row * C : nullptr;
+    {
+      // the row this pair visits next is requested into L2 now
+      const int64_t nxt = row + (int64_t)gridDim.x * PAIR_TEAMS;
+      if (tl == 0 && nxt < N) {
+        const uint32_t rb = (uint32_t)C * (uint32_t)sizeof(T);
+        ag_prefetch_l2_bulk(x + nxt * C, rb);
+        ag_prefetch_l2_bulk(dy + nxt * C, rb);
+        if (drr) ag_prefetch_l2_bulk(dres + nxt * C, rb);
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < KP2; ++p) {
+      const int col = (p * 64 + tl) * NV;
+      if (col < C) {
+        Pack<T>::load_stream(xr + col, v[p]);
+        Pack<T>::load_stream(gr + col, g[p]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) v[p][e] = g[p][e] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < KP2; ++p) {
+      const int col = (p * 64 + tl) * NV;
+      if (drr && col < C) {
+        Pack<T>::load(drr + col, o[p]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) o[p][e] = 0.0f;
+      }
+    }
+    // statistics, recomputed from the saved input exactly as in forward
+    float scale;
+    if (KIND == kLayerNorm) {
+      float s = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) s += v[p][e];
+      const float mean = pair_sum(s, s_red, team, half, lane, red) * inv_c;
+      red ^= 1;
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p) {
+        const int col = (p * 64 + tl) * NV;
+        if (col < C) {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) {
+            v[p][e] -= mean;
+            q += v[p][e] * v[p][e];
+          }
+        }
+      }
+      scale = 1.0f / sqrtf(pair_sum(q, s_red, team, half, lane, red) * inv_c + eps);
+      red ^= 1;
+    } else {
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) q += v[p][e] * v[p][e];
+      scale = 1.0f / sqrtf(pair_sum(q, s_red, team, half, lane, red) * inv_c + eps);
+      red ^= 1;
+    }
+    // v <- xhat ; column sums ; g <- dy*gamma ; row sums
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int p = 0; p < KP2; ++p) {
+      const int col = (p * 64 + tl) * NV;
+      if (col < C) {
+#pragma unroll
+        for (int e4 = 0; e4 < NV; e4 += 4) {
+          float4 ag = *reinterpret_cast<float4*>(my_g + col + e4);
+          float4 ab = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (KIND == kLayerNorm) ab = *reinterpret_cast<float4*>(my_b + col + e4);
+          float4 gg = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (gamma) gg = *reinterpret_cast<const float4*>(s_gamma + col + e4);
+          float* agp = reinterpret_cast<float*>(&ag);
+          float* abp = reinterpret_cast<float*>(&ab);
+          const float* gp = reinterpret_cast<const float*>(&gg);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = e4 + j;
+            const float xh = v[p][e] * scale;
+            v[p][e] = xh;
+            agp[j] += g[p][e] * xh;
+            if (KIND == kLayerNorm) abp[j] += g[p][e];
+            const float dg = gamma ? g[p][e] * gp[j] : g[p][e];
+            g[p][e] = dg;
+            s1 += dg;
+            s2 += dg * xh;
+          }
+          *reinterpret_cast<float4*>(my_g + col + e4) = ag;
+          if (KIND == kLayerNorm) *reinterpret_cast<float4*>(my_b + col + e4) = ab;
+        }
+      }
+    }
+    float m1 = 0.0f;
+    if (KIND == kLayerNorm) {
+      m1 = (pair_sum(s1, s_red, team, half, lane, red) * inv_c) * scale;
+      red ^= 1;
+    }
+    const float m2 = (pair_sum(s2, s_red, team, half, lane, red) * inv_c) * scale;
+    red ^= 1;
+    if (dx == nullptr) continue;  // only the column sums were asked for
+    T* dxr = dx + row * C;
+#pragma unroll
+    for (int p = 0; p < KP2; ++p) {
+      const int col = (p * 64 + tl) * NV;
+      if (col < C) {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          // backend.py:475-487: xg += dyg*rstd; xg -= m1; xg -= xhat*m2
+          float t = o[p][e] + g[p][e] * scale;
+          if (KIND == kLayerNorm) t = t - m1;
+          o[p][e] = t - v[p][e] * m2;
+        }
+        Pack<T>::store(dxr + col, o[p]);
+      }
+    }
+  }
+
+  // fold the teams' column sums in team order
+  __syncthreads();
+  for (int slot = 0; slot < SLOTS; ++slot) {
+    const bool wanted = slot == 0 ? (want_dgamma != 0) : (want_dbeta != 0);
+    if (!wanted) continue;  // uniform across the CTA
+    float* out = partials + ((int64_t)blockIdx.x * 2 + slot) * C;
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) {
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < PAIR_TEAMS; ++w) t += s_acc[((size_t)w * SLOTS + slot) * C + c];
+      out[c] = t;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// forward, two warps per row
+// ---------------------------------------------------------------------------------------
+// norm_forward_kernel with a row shared by a pair of warps (see norm_backward_pair_kernel): half the
+// registers per lane, so more CTAs per SM and half the dependent work per row and warp.
+template <typename T, int KP2, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_forward_pair_kernel(const T* x, const T* r, const float* __restrict__ gamma, const float* __restrict__ beta, T* h,
+                         T* __restrict__ y, float* __restrict__ stat0, float* __restrict__ stat1, int64_t N, int C,
+                         float eps, uint32_t stage_poll_limit, int* status, int pdl_early) {
+  ag_pdl_wait();
+  if (pdl_early) ag_pdl_trigger();
+  constexpr int NV = Pack<T>::N;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* s_gamma = reinterpret_cast<float*>(smem_raw);
+  float* s_beta = s_gamma + C;
+  __shared__ __align__(8) uint64_t s_bar;
+  __shared__ float s_red[PAIR_TEAMS * 2 * 2];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int team = warp >> 1, half = warp & 1;
+  const int tl = half * 32 + lane;
+  const float inv_c = 1.0f / (float)C;
+  if (gamma)
+    ag_stage_vectors(s_gamma, gamma, s_beta, (KIND == kLayerNorm) ? beta : nullptr, C, &s_bar, status, stage_poll_limit);
+  int red = 0;
+  for (int64_t row = (int64_t)blockIdx.x * PAIR_TEAMS + team; row < N; row += (int64_t)gridDim.x * PAIR_TEAMS) {
+    float v[KP2][NV];
+    const T* xr = x + row * C;
+#pragma unroll
+    for (int p = 0; p < KP2; ++p) {
+      const int col = (p * 64 + tl) * NV;
+      if (col < C) {
+        Pack<T>::load_stream(xr + col, v[p]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < NV; ++e) v[p][e] = 0.0f;
+      }
+    }
+    if (r) {
+      const T* rr = r + row * C;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p) {
+        const int col = (p * 64 + tl) * NV;
+        if (col < C) {
+          float t[NV];
+          Pack<T>::load_stream(rr + col, t);
+#pragma unroll
+          for (int e = 0; e < NV; ++e) v[p][e] += t[e];
+        }
+      }
+    }
+    if (h) {
+      T* hr = h + row * C;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p) {
+        const int col = (p * 64 + tl) * NV;
+        if (col < C) Pack<T>::store(hr + col, v[p]);
+      }
+    }
+    float mean = 0.0f, scale;
+    if (KIND == kLayerNorm) {
+      float s = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) s += v[p][e];
+      mean = pair_sum(s, s_red, team, half, lane, red) * inv_c;
+      red ^= 1;
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p) {
+        const int col = (p * 64 + tl) * NV;
+        if (col < C) {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) {
+            v[p][e] -= mean;
+            q += v[p][e] * v[p][e];
+          }
+        }
+      }
+      scale = 1.0f / sqrtf(pair_sum(q, s_red, team, half, lane, red) * inv_c + eps);
+      red ^= 1;
+    } else {
+      float q = 0.0f;
+#pragma unroll
+      for (int p = 0; p < KP2; ++p)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) q += v[p][e] * v[p][e];
+      scale = 1.0f / sqrtf(pair_sum(q, s_red, team, half, lane, red) * inv_c + eps);
+      red ^= 1;
+    }
+    if (tl == 0) {
+      if (KIND == kLayerNorm) {
+        if (stat0) stat0[row] = mean;
+        if (stat1) stat1[row] = scale;
+      } else if (stat0) {
+        stat0[row] = scale;
+      }
+    }
+    T* yr = y + row * C;
+#pragma unroll
+    for (int p = 0; p < KP2; ++p) {
+      const int col = (p * 64 + tl) * NV;
+      if (col < C) {
+        float o[NV];
+#pragma unroll
+        for (int e4 = 0; e4 < NV; e4 += 4) {
+          float4 gg = make_float4(1.f, 1.f, 1.f, 1.f), bb = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (gamma) gg = *reinterpret_cast<const float4*>(s_gamma + col + e4);
+          if (KIND == kLayerNorm) bb = *reinterpret_cast<const float4*>(s_beta + col + e4);
+          const float* gp = reinterpret_cast<const float*>(&gg);
+          const float* bp = reinterpret_cast<const float*>(&bb);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float t = v[p][e4 + k] * scale;
+            if (gamma) t = t * gp[k];
+            if (KIND == kLayerNorm) t = t + bp[k];
+            o[e4 + k] = t;
+          }
+        }
+        Pack<T>::store_stream(yr + col, o);
+      }
+    }
+  }
+}
+
 // CTA-per-row fallback: per-thread column accumulators for columns c = tid + k*THREADS are
 // kept in shared memory rows (one per CTA), rows visited grid-stride.
 template <typename T, int KIND>
@@ -1031,6 +1357,18 @@ inline uint32_t take_stage_poll_limit(ag_ctx* ctx) {
   return limit;
 }
 
+// Two warps per row (see norm_backward_pair_kernel).  ctx->norm_pair: 0 never, 1 whenever the shape fits,
+// 2 (default): fp32 rows of at least 1024 columns in backward, where the one-warp kernel needs 140-175
+// registers (inside the benchmark step, 32768 x 1280: 0.85 of the copy rate against 0.70-0.75; 8192 x 1536
+// alone: 0.75 against 0.70), and fp32 rows of at least 1536 columns in forward (8192 x 1536: 0.85 against
+// 0.80; at 1280 columns the one-warp forward is as fast or faster, 0.92 against 0.90 alone).
+inline bool pair_applies(const ag_ctx* ctx, int packets_per_row, int nv, bool backward) {
+  const int kp2 = (packets_per_row + 63) / 64;
+  if (!ctx->norm_pair || kp2 * nv > 24) return false;  // up to 24 row elements per lane: no register spills
+  if (ctx->norm_pair == 1) return true;
+  return nv == 4 && packets_per_row >= (backward ? 256 : 384);
+}
+
 inline int pick_kp(int packets_per_row) {
   const int need = (packets_per_row + 31) / 32;
   static const int kChoices[] = {1, 2, 3, 4, 5, 6, 8, 10, 12, 16};
@@ -1044,8 +1382,9 @@ inline int pick_kp(int packets_per_row) {
 // When every warp would visit only a few rows, a resident-sized grid quantises badly (2.3 rows
 // per warp costs 3 iterations); then one CTA per 8 rows is launched instead and the hardware
 // scheduler fills SMs as CTAs retire.  `max_grid` bounds the grid where each CTA owns a partial row.
-inline int persistent_grid(const ag_ctx* ctx, int64_t N, int ctas_per_sm, int64_t max_grid = (1ll << 30)) {
-  int64_t want = (N + NORM_WARPS - 1) / NORM_WARPS;
+inline int persistent_grid(const ag_ctx* ctx, int64_t N, int ctas_per_sm, int64_t max_grid = (1ll << 30),
+                           int rows_per_cta = NORM_WARPS) {
+  int64_t want = (N + rows_per_cta - 1) / rows_per_cta;
   if (ctas_per_sm < 1) ctas_per_sm = 1;
   if (ctas_per_sm > 8) ctas_per_sm = 8;
   int64_t cap = (int64_t)ctx->sm_count * ctas_per_sm;
@@ -1087,17 +1426,18 @@ int launch_fwd_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const
 }
 
 // Which shapes take the row ring.  Measured on B200 (back-to-back launches, operands rotated through
-// more buffers than fit in L2): with fp32 storage both designs reach the same HBM rate on long
-// inputs (32768 x 1280: 0.92 / 0.91 of the copy rate forward / backward with rows in registers, 0.86 /
-// 0.92 through the ring) and the register kernels win on short ones (16384 x 384 backward 0.68 vs
-// 0.60), so fp32 keeps them except for the widest rows in backward (C 1536: 0.71 vs 0.69).  With bf16
-// storage a lane's 16-byte packet holds half as many bytes per element in flight; there the ring wins
-// (8192 x 1536: forward 0.57 vs 0.53, backward 0.48 vs 0.38).  ctx->norm_ring: 0 never, 1 always where
-// the shape fits, 2 (default) this policy.
+// more buffers than fit in L2): with fp32 storage the ring and the register kernels reach the same HBM
+// rate on long inputs (32768 x 1280: 0.92 / 0.91 of the copy rate forward / backward with rows in
+// registers, 0.86 / 0.92 through the ring) and the register kernels win on short ones (16384 x 384
+// backward 0.68 vs 0.60; 8192 x 1536 backward 0.745 with two warps per row vs 0.70), so fp32 keeps its
+// rows in registers.  With bf16 storage a lane's 16-byte packet holds half as many bytes per element in
+// flight; there the ring wins (8192 x 1536: forward 0.57 vs 0.53, backward 0.48 vs 0.38).
+// ctx->norm_ring: 0 never, 1 always where the shape fits, 2 (default) this policy.
 inline bool ring_applies(const ag_ctx* ctx, int kp, int nv, int64_t N, bool backward) {
   if (!ctx->norm_ring || kp <= 0 || kp * nv > RING_MAX_PER_LANE || N >= (1ll << 31)) return false;
   if (ctx->norm_ring == 1) return true;
-  return nv == 8 || (backward && kp * nv >= 48);
+  (void)backward;
+  return nv == 8;
 }
 
 template <typename T, int KIND, int KP>
@@ -1125,6 +1465,22 @@ int launch_fwd_ring_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, 
   }
 }
 
+template <typename T, int KIND, int KP2>
+int launch_fwd_pair_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const float* beta, T* h, T* y, float* s0,
+                       float* s1, int64_t N, int C, float eps) {
+  const size_t smem = (size_t)2 * C * sizeof(float);
+  auto kern = norm_forward_pair_kernel<T, KP2, KIND>;
+  static int occ_cache[AG_MAX_DEVICES] = {};
+  static size_t occ_smem[AG_MAX_DEVICES] = {};
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache[ag_dev_slot(ctx)], &occ_smem[ag_dev_slot(ctx)]);
+  if (occ < 0)
+    AG_FAIL(ctx, AG_ERR_CUDA, "norm_forward_pair_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
+  const int grid = persistent_grid(ctx, N, occ, (1ll << 30), PAIR_TEAMS);
+  AG_LAUNCH_PDL(ctx, "norm_forward_pair_kernel", kern, grid, NORM_THREADS, smem, x, r, gamma, beta, h, y, s0, s1, N, C, eps,
+                take_stage_poll_limit(ctx), ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
+  return AG_OK;
+}
+
 template <typename T, int KIND>
 int launch_fwd(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const float* beta, T* h, T* y, float* s0,
                float* s1, int64_t N, int C, float eps) {
@@ -1145,6 +1501,18 @@ int launch_fwd(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const fl
     }
 #undef AG_FWD_RING_CASE
     if (rc >= 0) return rc;  // -1: the ring does not take this shape, the register kernels do
+  }
+  if (vec_ok && pair_applies(ctx, C / NV, NV, false)) {
+#define AG_FWD_PAIR_CASE(K) \
+  case K:                   \
+    return launch_fwd_pair_kp<T, KIND, K>(ctx, x, r, gamma, beta, h, y, s0, s1, N, C, eps);
+    switch ((C / NV + 63) / 64) {
+      AG_FWD_PAIR_CASE(1) AG_FWD_PAIR_CASE(2) AG_FWD_PAIR_CASE(3) AG_FWD_PAIR_CASE(4) AG_FWD_PAIR_CASE(5)
+      AG_FWD_PAIR_CASE(6)
+      default:
+        break;
+    }
+#undef AG_FWD_PAIR_CASE
   }
 #define AG_FWD_CASE(K) \
   case K:              \
@@ -1183,6 +1551,26 @@ int launch_bwd_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, cons
   const int grid = persistent_grid(ctx, N, occ, max_grid);
   AG_LAUNCH_PDL(ctx, "norm_backward_kernel", kern, grid, NORM_THREADS, smem, dy, x, gamma, dres, dx, partials, wg, wb, N, C,
                 eps, take_stage_poll_limit(ctx), ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
+  *grid_out = grid;
+  return AG_OK;
+}
+
+template <int KIND>
+size_t norm_bwd_pair_smem(int C) { return (size_t)(1 + PAIR_TEAMS * norm_bwd_slots<KIND>()) * C * sizeof(float); }
+
+template <typename T, int KIND, int KP2>
+int launch_bwd_pair_kp(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T* dres, T* dx, float* partials,
+                       int wg, int wb, int64_t N, int C, float eps, int max_grid, int* grid_out) {
+  const size_t smem = norm_bwd_pair_smem<KIND>(C);
+  auto kern = norm_backward_pair_kernel<T, KP2, KIND>;
+  static int occ_cache[AG_MAX_DEVICES] = {};
+  static size_t occ_smem[AG_MAX_DEVICES] = {};
+  const int occ = resident_ctas(ctx, kern, smem, &occ_cache[ag_dev_slot(ctx)], &occ_smem[ag_dev_slot(ctx)]);
+  if (occ < 0)
+    AG_FAIL(ctx, AG_ERR_CUDA, "norm_backward_pair_kernel: occupancy query failed: %s", cudaGetErrorString(cudaGetLastError()));
+  const int grid = persistent_grid(ctx, N, occ, max_grid, PAIR_TEAMS);
+  AG_LAUNCH_PDL(ctx, "norm_backward_pair_kernel", kern, grid, NORM_THREADS, smem, dy, x, gamma, dres, dx, partials, wg, wb, N,
+                C, eps, take_stage_poll_limit(ctx), ctx->d_status, grid <= ctx->sm_count * occ ? 1 : 0);
   *grid_out = grid;
   return AG_OK;
 }
@@ -1250,6 +1638,19 @@ int launch_bwd(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T
         break;
     }
 #undef AG_BWD_RING_CASE
+  }
+  if (rc < 0 && vec_ok && pair_applies(ctx, C / NV, NV, true)) {
+#define AG_BWD_PAIR_CASE(K)                                                                                          \
+  case K:                                                                                                            \
+    rc = launch_bwd_pair_kp<T, KIND, K>(ctx, dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, max_grid, &grid);  \
+    break;
+    switch ((C / NV + 63) / 64) {
+      AG_BWD_PAIR_CASE(1) AG_BWD_PAIR_CASE(2) AG_BWD_PAIR_CASE(3) AG_BWD_PAIR_CASE(4) AG_BWD_PAIR_CASE(5)
+      AG_BWD_PAIR_CASE(6)
+      default:
+        break;
+    }
+#undef AG_BWD_PAIR_CASE
   }
   if (rc < 0) {
 #define AG_BWD_CASE(K)                                                                                            \

@@ -1111,15 +1111,17 @@ def test_staging_wait_that_gives_up_takes_the_plain_load_path():
     G.free(x, r, gamma, beta, h, y)
 
 
-@pytest.mark.parametrize("ring", ["0", "1"])
-def test_norm_kernels_with_one_design_forced(ring, monkeypatch):
-    """By default the norm kernels choose between rows in registers and the shared-memory row ring per
-    shape; AG_B200_NORM_RING (read when a context is created) forces one of them.  Both designs must agree
-    with the oracle on every shape the ring can take: fp32 and bf16 storage, with and without gamma, a
-    single row, fewer rows than consumer warps, many rounds through the ring, the residual-gradient add."""
+@pytest.mark.parametrize("design", ["registers", "ring", "pair"])
+def test_norm_kernels_with_one_design_forced(design, monkeypatch):
+    """By default the norm kernels choose per shape between a row per warp in registers, the shared-memory
+    row ring, and (backward) a row per pair of warps; AG_B200_NORM_RING / AG_B200_NORM_PAIR (read when a
+    context is created) force one of them wherever the shape fits.  Every design must agree with the oracle
+    on the same shapes: fp32 and bf16 storage, with and without gamma, a single row, fewer rows than warps,
+    many rows per warp, the residual-gradient add."""
     import autograd_b200 as ag
     from autograd_b200 import hostgraph as hg
-    monkeypatch.setenv("AG_B200_NORM_RING", ring)
+    monkeypatch.setenv("AG_B200_NORM_RING", "1" if design == "ring" else "0")
+    monkeypatch.setenv("AG_B200_NORM_PAIR", "1" if design == "pair" else "0")
     ctx, alloc, be = ag.create(0)
     try:
         rng = np.random.default_rng(1246)
