@@ -126,6 +126,7 @@ struct Pack<float> {
   // a packet as it lies in memory, for kernels that keep many packets in flight before widening them
   using Raw = float4;
   __device__ __forceinline__ static Raw load_raw(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ static Raw load_raw_stream(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
   __device__ __forceinline__ static void unpack_raw(const Raw& t, float (&v)[4]) {
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
   }
@@ -153,6 +154,9 @@ struct Pack<__nv_bfloat16> {
   static constexpr int N = 8;
   using Raw = uint4;
   __device__ __forceinline__ static Raw load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ static Raw load_raw_stream(const __nv_bfloat16* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+  }
   __device__ __forceinline__ static void unpack_raw(const Raw& t, float (&v)[8]) { unpack(t, v); }
   __device__ __forceinline__ static void unpack(const uint4& t, float (&v)[8]) {
     const uint32_t w[4] = {t.x, t.y, t.z, t.w};

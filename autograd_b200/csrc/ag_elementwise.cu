@@ -29,14 +29,14 @@ inline int ew_early(const ag_ctx* ctx, int grid) { return grid <= ctx->sm_count 
 // Generic driver: F is a functor with
 //   template<int NV> void packet(int64_t elem_index)   - process one 16-byte packet
 //   void scalar(int64_t elem_index)                    - process one element (ragged tail)
-template <int NV, typename F>
+template <int NV, int UNROLL = EW_UNROLL, typename F>
 __device__ __forceinline__ void ew_drive(int64_t n, F& f, int early) {
   ag_pdl_wait();
   if (early) ag_pdl_trigger();
   const int64_t packets = n / NV;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  for (; i + (EW_UNROLL - 1) * stride < packets; i += EW_UNROLL * stride) f.template packets<EW_UNROLL>(i, stride);
+  for (; i + (UNROLL - 1) * stride < packets; i += UNROLL * stride) f.template packets<UNROLL>(i, stride);
   for (; i < packets; i += stride) f.template packets<1>(i, stride);
   const int64_t tail = packets * NV;
   for (int64_t j = tail + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride) f.scalar(j);
@@ -234,43 +234,49 @@ struct RowWalk {
   }
 };
 
-// One thread handles packets of the same column range in the gate and up halves of a row.
+// One thread handles packets of the same column range in the gate and up halves of a row.  Packets stay
+// as loaded (16 bytes = 4 registers) until they are used, so that bf16 storage, whose packets widen to 8
+// floats, can keep four packet pairs in flight per thread instead of two at the same register count.
 template <typename T>
 __global__ void __launch_bounds__(EW_THREADS) swiglu_forward_kernel(const T* __restrict__ gu, T* __restrict__ hidden,
                                                                     int64_t N, int I, int early) {
   ag_pdl_wait();
   if (early) ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
+  constexpr int K = NV == 8 ? 4 : 2;  // packet pairs in flight per thread
   const int ppr = I / NV;  // packets per row (I % NV == 0 on this path)
   const int64_t packets = N * (int64_t)ppr;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  // (row, packet-in-row) of the two packets of an iteration advance by a fixed step: one 64-bit
-  // division per thread instead of two per iteration (they would cost as much as the activation)
+  // (row, packet-in-row) of the packets of an iteration advance by a fixed step: one 64-bit
+  // division per thread instead of one per packet (they would cost as much as the activation)
   const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  RowWalk w[2];
-  w[0].init(i0, ppr, 2 * stride);
-  w[1].init(i0 + stride, ppr, 2 * stride);
-  for (int64_t i = i0; i < packets; i += 2 * stride) {
-    float g[2][NV], u[2][NV];
-    bool live[2];
+  RowWalk w[K];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+  for (int k = 0; k < K; ++k) w[k].init(i0 + k * stride, ppr, K * stride);
+  for (int64_t i = i0; i < packets; i += K * stride) {
+    typename Pack<T>::Raw g[K], u[K];
+    bool live[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
       const int64_t p = i + k * stride;
       live[k] = p < packets;
       if (live[k]) {
         const int64_t row = w[k].row;
         const int col = w[k].col * NV;
-        Pack<T>::load_stream(gu + row * 2 * I + col, g[k]);
-        Pack<T>::load_stream(gu + row * 2 * I + I + col, u[k]);
+        g[k] = Pack<T>::load_raw_stream(gu + row * 2 * I + col);
+        u[k] = Pack<T>::load_raw_stream(gu + row * 2 * I + I + col);
       }
       w[k].step(ppr);
     }
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < K; ++k) {
       if (live[k]) {
+        float gv[NV], uv[NV];
+        Pack<T>::unpack_raw(g[k], gv);
+        Pack<T>::unpack_raw(u[k], uv);
 #pragma unroll
-        for (int e = 0; e < NV; ++e) g[k][e] = (g[k][e] * sigmoid_ref<true>(g[k][e])) * u[k][e];
-        Pack<T>::store(hidden + (i + k * stride) * NV, g[k]);
+        for (int e = 0; e < NV; ++e) gv[e] = (gv[e] * sigmoid_ref<true>(gv[e])) * uv[e];
+        Pack<T>::store(hidden + (i + k * stride) * NV, gv);
       }
     }
   }
@@ -309,41 +315,46 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_backward_kernel(T* __restri
   ag_pdl_wait();
   if (early) ag_pdl_trigger();
   constexpr int NV = Pack<T>::N;
+  constexpr int K = NV == 8 ? 4 : 2;  // packet triples (gate, up, dh) in flight per thread, kept as loaded
   const int ppr = I / NV;
   const int64_t packets = N * (int64_t)ppr;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  RowWalk w[2];
-  w[0].init(i0, ppr, 2 * stride);
-  w[1].init(i0 + stride, ppr, 2 * stride);
-  for (int64_t i = i0; i < packets; i += 2 * stride) {
-    float g[2][NV], u[2][NV], d[2][NV];
-    bool live[2];
-    int64_t goff[2];
+  RowWalk w[K];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+  for (int k = 0; k < K; ++k) w[k].init(i0 + k * stride, ppr, K * stride);
+  for (int64_t i = i0; i < packets; i += K * stride) {
+    typename Pack<T>::Raw g[K], u[K], d[K];
+    bool live[K];
+    int64_t goff[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
       const int64_t p = i + k * stride;
       live[k] = p < packets;
       if (live[k]) {
         goff[k] = w[k].row * 2 * I + w[k].col * NV;
-        Pack<T>::load(gu + goff[k], g[k]);
-        Pack<T>::load(gu + goff[k] + I, u[k]);
-        Pack<T>::load_stream(dh + p * NV, d[k]);
+        g[k] = Pack<T>::load_raw(gu + goff[k]);
+        u[k] = Pack<T>::load_raw(gu + goff[k] + I);
+        d[k] = Pack<T>::load_raw_stream(dh + p * NV);
       }
       w[k].step(ppr);
     }
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < K; ++k) {
       if (live[k]) {
+        float gv[NV], uv[NV], dv[NV];
+        Pack<T>::unpack_raw(g[k], gv);
+        Pack<T>::unpack_raw(u[k], uv);
+        Pack<T>::unpack_raw(d[k], dv);
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
           float dg, du;
-          swiglu_bwd1<true>(g[k][e], u[k][e], d[k][e], dg, du);
-          g[k][e] = dg;
-          u[k][e] = du;
+          swiglu_bwd1<true>(gv[e], uv[e], dv[e], dg, du);
+          gv[e] = dg;
+          uv[e] = du;
         }
-        Pack<T>::store(gu + goff[k], g[k]);
-        Pack<T>::store(gu + goff[k] + I, u[k]);
+        Pack<T>::store(gu + goff[k], gv);
+        Pack<T>::store(gu + goff[k] + I, uv);
       }
     }
   }
@@ -422,8 +433,10 @@ struct AdamW {
   }
 };
 
+// Two packets of p, g, m, v per thread (eight loads in flight) rather than four: half the registers, so
+// three CTAs share an SM instead of one and more bytes are in flight per SM.
 template <typename GT>
-__global__ void __launch_bounds__(EW_THREADS) adamw_kernel(AdamW<GT> f, int64_t n, int early) { ew_drive<4>(n, f, early); }
+__global__ void __launch_bounds__(EW_THREADS) adamw_kernel(AdamW<GT> f, int64_t n, int early) { ew_drive<4, 2>(n, f, early); }
 
 // ------------------------------------------------------- fp32 <-> bf16 gradient storage
 // Round to nearest, ties to even; Inf kept, NaN stays NaN after the cut (utils.py:20-27,
@@ -647,7 +660,7 @@ int adamw_launch(ag_ctx* ctx, float* p, const GT* g, float* m, float* v, int64_t
   f.one_minus_b2 = (float)(1.0 - b2);
   f.eps = (float)eps; f.grad_scale = (float)grad_scale;
   f.decay = weight_decay > 0.0;
-  const int grid = ew_grid(ctx, n / 4, 4);
+  const int grid = ew_grid(ctx, n / 4, 8);
   AG_LAUNCH_PDL(ctx, "adamw_kernel", adamw_kernel<GT>, grid, EW_THREADS, 0, f, n, ew_early(ctx, grid));
   return AG_OK;
 }

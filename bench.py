@@ -457,7 +457,7 @@ def run_b200(a):
         config_lines = []
         a_k = argparse.Namespace(**vars(a))
         a_k.only = "cfg1,cfg3,cfg4,cfg2"
-        run_kernels(a_k, env=(ctx, alloc, be), dev_index=local, collect=config_lines, steps=10, warmup=3,
+        run_kernels(a_k, env=(ctx, alloc, be), dev_index=local, collect=config_lines, steps=30, warmup=10,
                     cfg2_modes=("3xtf32",))
 
     if rank == 0:
