@@ -27,6 +27,7 @@ struct ag_ctx {
   int tc_pair;          // 1: the split-operand tensor-core GEMMs run on CTA pairs (cta_group::2)
   int norm_ring;        // norm kernels stream rows through a shared-memory ring: 0 never, 1 always, 2 per shape
   int norm_pair;        // norm backward with two warps per row: 0 never, 1 always, 2 per shape
+  int scatter_group;    // sorted entries per group of the scatter-add: 32, 64, or 0 = by the number of ids
   int debug_stage_expire;  // ag_debug_expire_staging: the next staging wait gives up at once (tests)
   int linear_k_chunk;   // contraction elements per accumulation chain, forward of the linear+bias+residual op
   int tc_timing;        // ag_tc_timing: bracket tensor-core GEMM launches with pool events

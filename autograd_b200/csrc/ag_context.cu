@@ -73,6 +73,10 @@ extern "C" int ag_ctx_create(int device, void* stream, ag_ctx** out) {
     // fp32 rows of 1024 columns and more (diagnostics, A/B measurements)
     e = getenv("AG_B200_NORM_PAIR");
     c->norm_pair = !e ? 2 : (e[0] == '0' ? 0 : 1);
+    // AG_B200_SCATTER_GROUP: 32, 64 or 128 sorted entries per group of the scatter-add; unset = by the number of ids
+    e = getenv("AG_B200_SCATTER_GROUP");
+    c->scatter_group = 0;
+    if (e && (atoi(e) == 32 || atoi(e) == 64 || atoi(e) == 128)) c->scatter_group = atoi(e);
     // AG_B200_LINEAR_K_CHUNK: longest tensor-core accumulation chain (contraction elements) in the forward
     // of the linear + bias + residual op; shorter chains = smaller error, more launches.  A multiple of 32.
     e = getenv("AG_B200_LINEAR_K_CHUNK");

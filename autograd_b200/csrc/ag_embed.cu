@@ -325,7 +325,7 @@ sort_scatter_fused_kernel(const int32_t* __restrict__ ids, const uint32_t* __res
 }
 
 // ------------------------------------------------------------------------------ scatter-add
-constexpr int SEG_GROUP = 32;       // sorted entries per group
+constexpr int SEG_GROUP_MIN = 32;   // sorted entries per group: 32 or 64 (template parameter G of the two kernels)
 constexpr int SEG_THREADS = 128;    // one float4 per thread: 512 columns per CTA
 constexpr int SEG_COLS = SEG_THREADS * 4;
 
@@ -366,7 +366,7 @@ __device__ __forceinline__ void seg_store1(uint16_t* p, float v) { *p = (uint16_
 constexpr uint32_t RUN_BEGIN = 1u, RUN_END = 2u, RUN_COMPLETE = 4u, RUN_SLOT1 = 8u, RUN_VALID = 16u;
 constexpr int SEG_BATCH = 8;  // sorted entries whose rows are requested together
 
-template <bool VEC, typename TT>
+template <bool VEC, typename TT, int SEG_GROUP>
 __global__ void __launch_bounds__(SEG_THREADS)
 scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ pos,
                       const float* __restrict__ dout, TT* dtable, float* __restrict__ partials,
@@ -379,17 +379,16 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
   __shared__ uint32_t s_info[SEG_GROUP];
   const int64_t g0 = (int64_t)blockIdx.x * SEG_GROUP;
   const int cnt = (int)((n - g0) < SEG_GROUP ? (n - g0) : SEG_GROUP);
-  if (threadIdx.x < SEG_GROUP + 2) {
-    const int64_t j = g0 - 1 + threadIdx.x;
+  for (int t = threadIdx.x; t < SEG_GROUP + 2; t += SEG_THREADS) {
+    const int64_t j = g0 - 1 + t;
     // sentinel 0xffffffff never equals a key (keys are <= V)
-    s_key[threadIdx.x] = (j >= 0 && j < n && (int)threadIdx.x <= cnt + 1) ? keys[j] : 0xffffffffu;
+    s_key[t] = (j >= 0 && j < n && t <= cnt + 1) ? keys[j] : 0xffffffffu;
   }
-  if (threadIdx.x < SEG_GROUP) s_pos[threadIdx.x] = threadIdx.x < cnt ? pos[g0 + threadIdx.x] : 0u;
+  for (int t = threadIdx.x; t < SEG_GROUP; t += SEG_THREADS) s_pos[t] = t < cnt ? pos[g0 + t] : 0u;
   __syncthreads();
-  if ((int)threadIdx.x < cnt) {
+  for (int j = threadIdx.x; j < cnt; j += SEG_THREADS) {
     // the run (equal keys) around entry j: where it begins and ends inside the group, whether it is cut
     // by the group boundary on either side
-    const int j = threadIdx.x;
     const uint32_t key = s_key[j + 1];
     int rb = j, re = j;
     while (rb > 0 && s_key[rb] == key) --rb;
@@ -409,26 +408,28 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
   const int col = blockIdx.y * SEG_COLS + threadIdx.x * (VEC ? 4 : 1);
   if (VEC) {
     if (col < C) {
-    // Rows of SEG_BATCH entries, and the dtable rows of the complete runs that begin among them, are
-    // requested together; the adds then run in sorted (= position) order, each complete run starting
-    // from its dtable row: the same sequence of additions as an unbuffered add-at.
+    // A ring of SEG_BATCH row requests per thread: the row of entry j + SEG_BATCH (and the dtable row of
+    // a complete run that begins there) is requested as soon as entry j has been added, so that a
+    // thread always has SEG_BATCH - 1 or SEG_BATCH rows in flight.  The adds run in sorted (= position)
+    // order, each complete run starting from its dtable row: the same sequence of additions as an
+    // unbuffered add-at.
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j0 = 0; j0 < cnt; j0 += SEG_BATCH) {
-      float4 v[SEG_BATCH], d[SEG_BATCH];
-#pragma unroll
-      for (int u = 0; u < SEG_BATCH; ++u) {
-        const int j = j0 + u;
-        v[u] = d[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (j < cnt) {
-          const uint32_t info = s_info[j];
-          if (info & RUN_VALID) {
-            v[u] = __ldcs(reinterpret_cast<const float4*>(dout + (int64_t)s_pos[j] * C + col));
-            if ((info & (RUN_BEGIN | RUN_COMPLETE)) == (RUN_BEGIN | RUN_COMPLETE))
-              d[u] = seg_load4(dtable + (int64_t)s_key[j + 1] * C + col);
-          }
+    float4 v[SEG_BATCH], d[SEG_BATCH];
+    auto request = [&](int u, int j) {
+      v[u] = d[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < cnt) {
+        const uint32_t info = s_info[j];
+        if (info & RUN_VALID) {
+          v[u] = __ldcs(reinterpret_cast<const float4*>(dout + (int64_t)s_pos[j] * C + col));
+          if ((info & (RUN_BEGIN | RUN_COMPLETE)) == (RUN_BEGIN | RUN_COMPLETE))
+            d[u] = seg_load4(dtable + (int64_t)s_key[j + 1] * C + col);
         }
       }
+    };
+#pragma unroll
+    for (int u = 0; u < SEG_BATCH; ++u) request(u, u);
+    for (int j0 = 0; j0 < cnt; j0 += SEG_BATCH) {
 #pragma unroll
       for (int u = 0; u < SEG_BATCH; ++u) {
         const int j = j0 + u;
@@ -448,6 +449,7 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
             }
           }
         }
+        request(u, j + SEG_BATCH);
       }
     }
     }
@@ -504,6 +506,7 @@ scatter_groups_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restr
   }
 }
 
+constexpr int64_t SEG_GROUP64_MIN_IDS = 49152;  // ids from which groups of 64 entries are used
 constexpr int SEG_SPLIT = 4;  // sub-ranges of a segment's groups summed side by side in the combine kernel
 
 // Block (SEG_THREADS, SEG_SPLIT), grid (about one resident wave, column slices): a CTA takes entries
@@ -513,7 +516,7 @@ constexpr int SEG_SPLIT = 4;  // sub-ranges of a segment's groups summed side by
 // row y adds its sub-range in group order (8 loads in flight), then row 0 adds
 // dtable row + head partial + sub-sum 0 + ... + sub-sum 3 and writes the dtable row.  Fixed order; a
 // table row is written by exactly one CTA.
-template <bool VEC, typename TT>
+template <bool VEC, typename TT, int SEG_GROUP>
 __global__ void __launch_bounds__(SEG_THREADS * SEG_SPLIT)
 scatter_combine_kernel(const uint32_t* __restrict__ keys, const long long* __restrict__ heads,
                        const uint32_t* __restrict__ head_count, const uint32_t* __restrict__ head_list, TT* dtable,
@@ -581,10 +584,10 @@ struct ScatterPlan {
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
-inline ScatterPlan scatter_plan(int64_t n, int C) {
+inline ScatterPlan scatter_plan(int64_t n, int C, int group = SEG_GROUP_MIN) {
   ScatterPlan p;
   p.n_tiles = (n + SORT_TILE - 1) / SORT_TILE;
-  p.n_groups = (n + SEG_GROUP - 1) / SEG_GROUP;
+  p.n_groups = (n + group - 1) / group;
   size_t off = 0;
   for (int b = 0; b < 2; ++b) {
     p.off_keys[b] = off; off += align256((size_t)n * 4);
@@ -631,6 +634,36 @@ extern "C" size_t ag_scatter_add_scratch_bytes(int64_t n_ids, int C, int V) {
 }
 
 namespace {
+// The segmented sum over groups of G sorted entries and the combine over the listed head groups.
+template <typename TT, int G>
+int launch_groups_combine(ag_ctx* ctx, const ScatterPlan& p, const uint32_t* keys, const uint32_t* pos, const float* dout,
+                           TT* dtable, float* partials, long long* heads, uint32_t* head_count, uint32_t* head_list,
+                           int64_t n_ids, int C, int V, bool vec) {
+  dim3 grid((unsigned)p.n_groups, (unsigned)((C + SEG_COLS - 1) / SEG_COLS));
+  // combine: about one resident wave of 512-thread CTAs (four per SM) over all column slices
+  int64_t cx = (int64_t)ctx->sm_count * 4 / grid.y;
+  cx = cx < 1 ? 1 : (cx > p.n_groups ? p.n_groups : cx);
+  dim3 cgrid((unsigned)cx, grid.y);
+  if (vec) {
+    auto groups_vec = scatter_groups_kernel<true, TT, G>;
+    auto combine_vec = scatter_combine_kernel<true, TT, G>;
+    AG_LAUNCH_PDL(ctx, "scatter_groups_kernel", groups_vec, grid, SEG_THREADS, 0, keys, pos, dout, dtable, partials, heads,
+                  head_count, head_list, (int)p.n_groups, n_ids, C, V);
+    AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", combine_vec, cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0, keys,
+                  (const long long*)heads, (const uint32_t*)head_count, (const uint32_t*)head_list, dtable,
+                  (const float*)partials, n_ids, C);
+  } else {
+    scatter_groups_kernel<false, TT, G><<<grid, SEG_THREADS, 0, ctx->stream>>>(keys, pos, dout, dtable, partials, heads,
+                                                                               head_count, head_list, (int)p.n_groups,
+                                                                               n_ids, C, V);
+    AG_LAUNCHED(ctx, "scatter_groups_kernel");
+    scatter_combine_kernel<false, TT, G><<<cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(
+        keys, heads, head_count, head_list, dtable, partials, n_ids, C);
+    AG_LAUNCHED(ctx, "scatter_combine_kernel");
+  }
+  return AG_OK;
+}
+
 template <typename TT>
 int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dtable, void* scratch,
                       size_t scratch_bytes, int64_t n_ids, int C, int V) {
@@ -639,7 +672,10 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
   AG_REQUIRE(ctx, ids && dout && dtable, "ag_gather_backward: null pointer");
   AG_REQUIRE(ctx, n_ids > 0 && C > 0 && V > 0, "ag_gather_backward: bad shape n=%lld C=%d V=%d", (long long)n_ids, C, V);
   AG_REQUIRE(ctx, n_ids < (1ll << 31) && (int64_t)V < (1ll << 31) - 1, "ag_gather_backward: sizes exceed 32-bit keys");
-  const ScatterPlan p = scatter_plan(n_ids, C);
+  // Groups of 64 entries halve the partial rows a long segment leaves for the combine kernel; they pay
+  // once the groups still fill the GPU several times over.  The scratch size is the one of groups of 32.
+  const int group = ctx->scatter_group ? ctx->scatter_group : (n_ids >= SEG_GROUP64_MIN_IDS ? 64 : 32);
+  const ScatterPlan p = scatter_plan(n_ids, C, group);
   if (!scratch || scratch_bytes < p.total)
     AG_FAIL(ctx, AG_ERR_SCRATCH, "ag_gather_backward: scratch has %zu bytes, needs %zu", scratch_bytes, p.total);
   AG_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "ag_gather_backward: scratch not 256-byte aligned");
@@ -693,31 +729,14 @@ int gather_backward_t(ag_ctx* ctx, const int32_t* ids, const float* dout, TT* dt
   }
   // 4-element packets of a table row: 16 bytes in fp32, 8 bytes in bf16 storage
   const bool vec = (C % 4 == 0) && ag_aligned16(dout) && ag_aligned16(dtable);
-  dim3 grid((unsigned)p.n_groups, (unsigned)((C + SEG_COLS - 1) / SEG_COLS));
-  // combine: about one resident wave of 512-thread CTAs (four per SM) over all column slices
-  int64_t cx = (int64_t)ctx->sm_count * 4 / grid.y;
-  cx = cx < 1 ? 1 : (cx > p.n_groups ? p.n_groups : cx);
-  dim3 cgrid((unsigned)cx, grid.y);
-  auto groups_vec = scatter_groups_kernel<true, TT>;
-  auto combine_vec = scatter_combine_kernel<true, TT>;
-  auto groups_scalar = scatter_groups_kernel<false, TT>;
-  auto combine_scalar = scatter_combine_kernel<false, TT>;
-  if (vec) {
-    AG_LAUNCH_PDL(ctx, "scatter_groups_kernel", groups_vec, grid, SEG_THREADS, 0,
-                  (const uint32_t*)keys[cur], (const uint32_t*)vals[cur], dout, dtable, partials, heads, head_count,
-                  head_list, (int)p.n_groups, n_ids, C, V);
-    AG_LAUNCH_PDL(ctx, "scatter_combine_kernel", combine_vec, cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0,
-                  (const uint32_t*)keys[cur], (const long long*)heads, (const uint32_t*)head_count,
-                  (const uint32_t*)head_list, dtable, (const float*)partials, n_ids, C);
-  } else {
-    groups_scalar<<<grid, SEG_THREADS, 0, ctx->stream>>>(keys[cur], vals[cur], dout, dtable, partials, heads, head_count,
-                                                         head_list, (int)p.n_groups, n_ids, C, V);
-    AG_LAUNCHED(ctx, "scatter_groups_kernel");
-    combine_scalar<<<cgrid, dim3(SEG_THREADS, SEG_SPLIT), 0, ctx->stream>>>(keys[cur], heads, head_count, head_list, dtable,
-                                                                            partials, n_ids, C);
-    AG_LAUNCHED(ctx, "scatter_combine_kernel");
-  }
-  return AG_OK;
+  if (group == 128)
+    return launch_groups_combine<TT, 128>(ctx, p, keys[cur], vals[cur], dout, dtable, partials, heads, head_count,
+                                          head_list, n_ids, C, V, vec);
+  if (group == 64)
+    return launch_groups_combine<TT, 64>(ctx, p, keys[cur], vals[cur], dout, dtable, partials, heads, head_count,
+                                         head_list, n_ids, C, V, vec);
+  return launch_groups_combine<TT, 32>(ctx, p, keys[cur], vals[cur], dout, dtable, partials, heads, head_count, head_list,
+                                       n_ids, C, V, vec);
 }
 }  // namespace
 

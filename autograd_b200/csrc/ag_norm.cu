@@ -471,30 +471,76 @@ norm_backward_pair_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
     }
   }
   int red = 0;  // parity of the next pair reduction
-  for (int64_t row = (int64_t)blockIdx.x * PAIR_TEAMS + team; row < N; row += (int64_t)gridDim.x * PAIR_TEAMS) {
+  // bf16 storage: a row's packets are 4 registers per 8 elements, so the x and dy packets of the row
+  // the pair visits NEXT are requested before the current row is computed and wait in registers;
+  // the row's latency then overlaps the arithmetic of its predecessor.  (fp32 rows would need twice
+  // the registers and lose the second CTA of an SM.)
+  constexpr bool AHEAD = NV == 8;
+  using Raw = typename Pack<T>::Raw;
+  Raw nx[AHEAD ? KP2 : 1], ng[AHEAD ? KP2 : 1];
+  const int64_t row_step = (int64_t)gridDim.x * PAIR_TEAMS;
+  const int64_t row0 = (int64_t)blockIdx.x * PAIR_TEAMS + team;
+  if constexpr (AHEAD) {
+    if (row0 < N) {
+#pragma unroll
+      for (int p = 0; p < KP2; ++p) {
+        const int col = (p * 64 + tl) * NV;
+        if (col < C) {
+          nx[p] = Pack<T>::load_raw_stream(x + row0 * C + col);
+          ng[p] = Pack<T>::load_raw_stream(dy + row0 * C + col);
+        }
+      }
+    }
+  }
+  for (int64_t row = row0; row < N; row += row_step) {
     float v[KP2][NV], g[KP2][NV], o[KP2][NV];
     const T* xr = x + row * C;
     const T* gr = dy + row * C;
     const T* drr = (dres && dx) ? dres + row * C : nullptr;
     {
-      // the row this pair visits next is requested into L2 now
-      const int64_t nxt = row + (int64_t)gridDim.x * PAIR_TEAMS;
+      // a row this pair visits later is requested into L2 now
+      const int64_t nxt = row + (AHEAD ? 2 : 1) * row_step;
       if (tl == 0 && nxt < N) {
         const uint32_t rb = (uint32_t)C * (uint32_t)sizeof(T);
         ag_prefetch_l2_bulk(x + nxt * C, rb);
         ag_prefetch_l2_bulk(dy + nxt * C, rb);
-        if (drr) ag_prefetch_l2_bulk(dres + nxt * C, rb);
       }
+      if (tl == 0 && drr && row + row_step < N) ag_prefetch_l2_bulk(dres + (row + row_step) * C, (uint32_t)C * (uint32_t)sizeof(T));
     }
+    if constexpr (AHEAD) {
 #pragma unroll
-    for (int p = 0; p < KP2; ++p) {
-      const int col = (p * 64 + tl) * NV;
-      if (col < C) {
-        Pack<T>::load_stream(xr + col, v[p]);
-        Pack<T>::load_stream(gr + col, g[p]);
-      } else {
+      for (int p = 0; p < KP2; ++p) {
+        const int col = (p * 64 + tl) * NV;
+        if (col < C) {
+          Pack<T>::unpack_raw(nx[p], v[p]);
+          Pack<T>::unpack_raw(ng[p], g[p]);
+        } else {
 #pragma unroll
-        for (int e = 0; e < NV; ++e) v[p][e] = g[p][e] = 0.0f;
+          for (int e = 0; e < NV; ++e) v[p][e] = g[p][e] = 0.0f;
+        }
+      }
+      const int64_t nxt = row + row_step;
+      if (nxt < N) {
+#pragma unroll
+        for (int p = 0; p < KP2; ++p) {
+          const int col = (p * 64 + tl) * NV;
+          if (col < C) {
+            nx[p] = Pack<T>::load_raw_stream(x + nxt * C + col);
+            ng[p] = Pack<T>::load_raw_stream(dy + nxt * C + col);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int p = 0; p < KP2; ++p) {
+        const int col = (p * 64 + tl) * NV;
+        if (col < C) {
+          Pack<T>::load_stream(xr + col, v[p]);
+          Pack<T>::load_stream(gr + col, g[p]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) v[p][e] = g[p][e] = 0.0f;
+        }
       }
     }
 #pragma unroll
@@ -1366,6 +1412,8 @@ inline bool pair_applies(const ag_ctx* ctx, int packets_per_row, int nv, bool ba
   const int kp2 = (packets_per_row + 63) / 64;
   if (!ctx->norm_pair || kp2 * nv > 24) return false;  // up to 24 row elements per lane: no register spills
   if (ctx->norm_pair == 1) return true;
+  // bf16 storage, backward: the pair kernel holds the next row's packets in registers (a row ahead)
+  if (nv == 8) return backward && ctx->norm_ring != 1;
   return nv == 4 && packets_per_row >= (backward ? 256 : 384);
 }
 
@@ -1433,11 +1481,11 @@ int launch_fwd_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const
 // rows in registers.  With bf16 storage a lane's 16-byte packet holds half as many bytes per element in
 // flight; there the ring wins (8192 x 1536: forward 0.57 vs 0.53, backward 0.48 vs 0.38).
 // ctx->norm_ring: 0 never, 1 always where the shape fits, 2 (default) this policy.
-inline bool ring_applies(const ag_ctx* ctx, int kp, int nv, int64_t N, bool backward) {
+inline bool ring_applies(const ag_ctx* ctx, int kp, int nv, int64_t N, bool backward, int packets_per_row) {
   if (!ctx->norm_ring || kp <= 0 || kp * nv > RING_MAX_PER_LANE || N >= (1ll << 31)) return false;
   if (ctx->norm_ring == 1) return true;
-  (void)backward;
-  return nv == 8;
+  // bf16 storage: forward always; backward only for rows too wide for the pair kernel
+  return nv == 8 && !(backward && pair_applies(ctx, packets_per_row, nv, true));
 }
 
 template <typename T, int KIND, int KP>
@@ -1487,7 +1535,7 @@ int launch_fwd(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const fl
   constexpr int NV = Pack<T>::N;
   const bool vec_ok = (C % NV == 0) && ag_aligned16(x) && ag_aligned16(r) && ag_aligned16(h) && ag_aligned16(y);
   const int kp = vec_ok ? pick_kp(C / NV) : 0;
-  if (ring_applies(ctx, kp, NV, N, false)) {
+  if (ring_applies(ctx, kp, NV, N, false, C / NV)) {
     int rc = -1;
 #define AG_FWD_RING_CASE(K)                                                                   \
   case K:                                                                                     \
@@ -1626,7 +1674,7 @@ int launch_bwd(ag_ctx* ctx, const T* dy, const T* x, const float* gamma, const T
   const int kp = vec_ok ? pick_kp(C / NV) : 0;
   int grid = 0;
   int rc = -1;
-  if (ring_applies(ctx, kp, NV, N, true)) {
+  if (ring_applies(ctx, kp, NV, N, true, C / NV)) {
 #define AG_BWD_RING_CASE(K)                                                                                          \
   case K:                                                                                                            \
     rc = launch_bwd_ring_kp<T, KIND, K>(ctx, dy, x, gamma, dres, dx, partials, wg, wb, N, C, eps, max_grid, &grid);  \
