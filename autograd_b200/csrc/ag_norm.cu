@@ -877,18 +877,21 @@ norm_partials_reduce_kernel(const float* __restrict__ partials, int P, int C, fl
   float* out = slot == 0 ? dgamma : dbeta;
   if (!out) return;  // uniform per block
   float t = 0.0f;
+  float prev = 0.0f;
   if (c < C) {
-    // eight loads in flight per thread, added in row order; rows past the end contribute +0, which
-    // leaves the sum's bits as they are
-    for (int p = threadIdx.y; p < P; p += 8 * 32) {
-      float v[8];
+    // the accumulator's old value travels with the partial rows instead of after them
+    if (threadIdx.y == 0) prev = out[c];
+    // sixteen loads in flight per thread (one round for up to 512 partial rows), added in row order;
+    // rows past the end contribute +0, which leaves the sum's bits as they are
+    for (int p = threadIdx.y; p < P; p += 16 * 32) {
+      float v[16];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 16; ++j) {
         const int q = p + j * 32;
         v[j] = q < P ? partials[((int64_t)q * 2 + slot) * C + c] : 0.0f;
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) t += v[j];
+      for (int j = 0; j < 16; ++j) t += v[j];
     }
   }
   s[threadIdx.y][threadIdx.x] = t;
@@ -897,7 +900,7 @@ norm_partials_reduce_kernel(const float* __restrict__ partials, int P, int C, fl
     float tot = 0.0f;
 #pragma unroll
     for (int y = 0; y < 32; ++y) tot += s[y][threadIdx.x];
-    out[c] += tot;
+    out[c] = prev + tot;
   }
 }
 
