@@ -1411,6 +1411,8 @@ inline uint32_t take_stage_poll_limit(ag_ctx* ctx) {
 // registers (inside the benchmark step, 32768 x 1280: 0.85 of the copy rate against 0.70-0.75; 8192 x 1536
 // alone: 0.75 against 0.70), and fp32 rows of at least 1536 columns in forward (8192 x 1536: 0.85 against
 // 0.80; at 1280 columns the one-warp forward is as fast or faster, 0.92 against 0.90 alone).
+// bf16 storage, backward: the pair kernel with a row ahead in registers (8192 x 1536: 0.52 against 0.48
+// through the ring), for rows of up to 24 elements per lane.
 inline bool pair_applies(const ag_ctx* ctx, int packets_per_row, int nv, bool backward) {
   const int kp2 = (packets_per_row + 63) / 64;
   if (!ctx->norm_pair || kp2 * nv > 24) return false;  // up to 24 row elements per lane: no register spills
@@ -1482,7 +1484,8 @@ int launch_fwd_kp(ag_ctx* ctx, const T* x, const T* r, const float* gamma, const
 // registers, 0.86 / 0.92 through the ring) and the register kernels win on short ones (16384 x 384
 // backward 0.68 vs 0.60; 8192 x 1536 backward 0.745 with two warps per row vs 0.70), so fp32 keeps its
 // rows in registers.  With bf16 storage a lane's 16-byte packet holds half as many bytes per element in
-// flight; there the ring wins (8192 x 1536: forward 0.57 vs 0.53, backward 0.48 vs 0.38).
+// flight; there the ring wins over the one-warp kernels (8192 x 1536: forward 0.57 vs 0.53, backward 0.48 vs
+// 0.38); the bf16 backward is taken by the pair kernel first where the row fits it (see pair_applies).
 // ctx->norm_ring: 0 never, 1 always where the shape fits, 2 (default) this policy.
 inline bool ring_applies(const ag_ctx* ctx, int kp, int nv, int64_t N, bool backward, int packets_per_row) {
   if (!ctx->norm_ring || kp <= 0 || kp * nv > RING_MAX_PER_LANE || N >= (1ll << 31)) return false;
