@@ -248,6 +248,21 @@ sort_scatter_fused_kernel(const int32_t* __restrict__ ids, const uint32_t* __res
   __shared__ uint32_t s_wsum[SORT_DIGITS / 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int d = lane; d < SORT_DIGITS; d += 32) s_cnt[warp][d] = 0;
+  // the tile's own key and position are requested first; they arrive while the offsets are computed
+  const int64_t i = (int64_t)blockIdx.x * SORT_TILE + threadIdx.x;
+  const bool live = i < n;
+  uint32_t key = 0, val = 0;
+  int digit = 0;
+  if (live) {
+    if (FIRST) {
+      key = sort_key_of(ids[i], V);
+      val = (uint32_t)i;
+    } else {
+      key = keys_in[i];
+      val = vals_in[i];
+    }
+    digit = (key >> shift) & (SORT_DIGITS - 1);
+  }
 
   // ---- offsets: total[d] = count of digit d over all tiles, before[d] = over the tiles before this one.
   // Thread (half, d) walks digit d down one half of the tiles; a warp's loads are 32 consecutive counters.
@@ -289,20 +304,6 @@ sort_scatter_fused_kernel(const int32_t* __restrict__ ids, const uint32_t* __res
     s_base[threadIdx.x] += wbase;
   }
 
-  const int64_t i = (int64_t)blockIdx.x * SORT_TILE + threadIdx.x;
-  const bool live = i < n;
-  uint32_t key = 0, val = 0;
-  int digit = 0;
-  if (live) {
-    if (FIRST) {
-      key = sort_key_of(ids[i], V);
-      val = (uint32_t)i;
-    } else {
-      key = keys_in[i];
-      val = vals_in[i];
-    }
-    digit = (key >> shift) & (SORT_DIGITS - 1);
-  }
   const uint32_t live_mask = __ballot_sync(0xffffffffu, live);
   uint32_t peers = 0;
   if (live) peers = __match_any_sync(live_mask, digit);

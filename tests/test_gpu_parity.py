@@ -398,6 +398,49 @@ def test_gather_scatter_full_size(V, C, n):
     G.free(ids, table, out)
 
 
+@pytest.mark.parametrize("group", [32, 64, 128])
+def test_scatter_add_group_sizes_agree(group, monkeypatch):
+    """The segmented sum cuts the sorted ids into groups of 32 entries, or 64 from 49152 ids on;
+    AG_B200_SCATTER_GROUP (read when a context is created) forces 32, 64 or 128.  Every size must give
+    the np.add.at result: Zipf ids (segments that span many groups), a ragged last group, the scalar
+    path (odd C), accumulation on top of an existing gradient."""
+    import autograd_b200 as ag
+    from autograd_b200 import hostgraph as hg
+    monkeypatch.setenv("AG_B200_SCATTER_GROUP", str(group))
+    ctx, alloc, be = ag.create(0)
+    try:
+        rng = np.random.default_rng(1251)
+
+        def dev(a, requires_grad=False):
+            t = hg.HostTensor(a.shape, a.dtype.type, requires_grad=requires_grad)
+            t.storage = alloc.alloc(t.shape, t.dtype)
+            be.copy_from_host(t, np.ascontiguousarray(a))
+            return t
+
+        for V, C, n in ((3000, 256, 20011), (50, 101, 777), (100000, 64, 60000)):
+            ids_ = _zipf_ids(rng, V, n).reshape(1, n)
+            dout_ = rng.standard_normal((1, n, C), dtype=np.float32)
+            base_ = (0.01 * rng.standard_normal((V, C), dtype=np.float32)).astype(np.float32)
+            ids, table = dev(ids_), dev(base_, requires_grad=True)
+            table.grad = dev(base_)
+            out = dev(np.zeros((1, n, C), np.float32), requires_grad=True)
+            out.grad = dev(dout_)
+            node = hg.make_node(hg.make_op("GatherOp"), (ids, table), (out,))
+            be.get_backward_kernel(node.op)(node.inputs, node.outputs)
+            got = be.copy_to_host(table.grad)
+            ref = O.gather_backward(ids_, dout_, base_.copy())
+            _assert_rows_close(got, ref, TOL_BWD, f"dtable group={group} V={V} C={C} n={n}")
+            counts = np.bincount(ids_.ravel(), minlength=V)
+            assert np.array_equal(got[counts == 0], base_[counts == 0])
+            assert ctx.status() == 0
+            for t in (ids, table, table.grad, out, out.grad):
+                alloc.free(t.storage)
+    finally:
+        ctx.synchronize()
+        alloc.free()
+        ctx.close()
+
+
 def test_gather_bad_index_sets_status_not_fault():
     ctx, alloc, be = G.env()
     table_ = np.arange(12, dtype=np.float32).reshape(3, 4)
