@@ -88,6 +88,7 @@ extern "C" int ag_ctx_create(int device, void* stream, ag_ctx** out) {
   }
   CREATE_CUDA(cudaMalloc(&c->d_status, sizeof(int)));
   CREATE_CUDA(cudaMemset(c->d_status, 0, sizeof(int)));
+  CREATE_CUDA(cudaDeviceSynchronize());  // the memset ran on the default stream, the kernels use the context's own
   CREATE_CUDA(cudaMallocHost(&c->h_status, sizeof(int)));
   CREATE_CUDA(cudaEventCreate(&c->ev_begin));
   CREATE_CUDA(cudaEventCreate(&c->ev_end));
