@@ -8,8 +8,9 @@
 //   1. stable LSD radix sort of (id, position) pairs, 9 bits per pass, so that equal ids end
 //      up adjacent and in ascending position order (up to 262144 ids: one histogram launch and
 //      one launch per pass; beyond that a histogram, a scan and a scatter launch per pass);
-//   2. the sorted list is cut into groups of SEG_GROUP consecutive entries.  A CTA walks one
-//      group (for one 512-column slice), summing each run of equal ids in list order.  A run
+//   2. the sorted list is cut into groups of 32 consecutive entries (64 from 49152 ids on: half as
+//      many partial slots for step 3).  A CTA walks one group (for one 512-column slice), every
+//      thread keeping a ring of 8 row requests in flight, summing each run of equal ids in list order.  A run
 //      that is a complete segment (its id neither continues from the previous group nor
 //      into the next one) starts from the current dtable row and is written back directly:
 //      for such rows the result is bit-identical to numpy's sequential np.add.at.  A run cut
