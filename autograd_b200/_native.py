@@ -101,7 +101,70 @@ def load_library(path: str = LIB_PATH) -> C.CDLL:
     return lib
 
 
-lib = load_library()
+class _PybindLibrary:
+    """The call surface of the ctypes library object over the pybind11 module `cuda_ext`
+    (csrc/cuda_ext.cpp): `lib.ag_xxx(*args)` with the same ctypes-typed arguments.  Pointer
+    arguments (c_void_p values, `byref(...)` out-parameters, ctypes structures, ints, None) become
+    integer addresses, which is what the module takes; everything else is passed as a Python number."""
+
+    def __init__(self, module):
+        self._module = module
+        for name, (res, argtypes) in SIGNATURES.items():
+            setattr(self, name, self._adapt(getattr(module, name), argtypes))  # AttributeError if not exported
+
+    @staticmethod
+    def _address(a):
+        if a is None:
+            return 0
+        if isinstance(a, int):
+            return a
+        if isinstance(a, C.c_void_p):
+            return a.value or 0
+        inner = getattr(a, "_obj", None)      # byref(x)
+        if inner is not None:
+            return C.addressof(inner)
+        if isinstance(a, C._Pointer):
+            return C.cast(a, C.c_void_p).value or 0
+        return C.addressof(a)                 # a structure or a simple ctypes object passed by address
+
+    @classmethod
+    def _adapt(cls, fn, argtypes):
+        is_ptr = [t is _ptr or t is _ctx or (isinstance(t, type) and issubclass(t, C._Pointer)) for t in argtypes]
+        is_float = [t in (_f32, _f64) for t in argtypes]
+
+        def call(*args):
+            if len(args) != len(argtypes):
+                raise TypeError(f"{fn.__name__} takes {len(argtypes)} arguments, got {len(args)}")
+            conv = []
+            for a, p, f in zip(args, is_ptr, is_float):
+                if p:
+                    conv.append(cls._address(a))
+                else:
+                    a = getattr(a, "value", a)
+                    conv.append(float(a) if f else int(a))
+            return fn(*conv)
+        return call
+
+
+def load_binding():
+    """The library object the package calls: ctypes by default; AG_B200_BINDING=pybind11 selects the
+    compiled pybind11 module (built by `python setup.py build_ext --inplace` / build.py where pybind11
+    and the Python headers are present).  Either way the same libautograd_b200.so does the work."""
+    which = os.environ.get("AG_B200_BINDING", "ctypes").lower()
+    cdll = load_library()
+    if which == "ctypes":
+        return cdll, "ctypes"
+    if which != "pybind11":
+        raise ImportError(f"AG_B200_BINDING={which!r}: choose ctypes or pybind11")
+    try:
+        from . import cuda_ext
+    except ImportError as e:
+        raise ImportError(f"AG_B200_BINDING=pybind11 but autograd_b200.cuda_ext does not import ({e}); "
+                          "build it with `python setup.py build_ext --inplace`") from e
+    return _PybindLibrary(cuda_ext), "pybind11"
+
+
+lib, BINDING = load_binding()
 
 
 class AgError(RuntimeError):

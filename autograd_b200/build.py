@@ -76,5 +76,39 @@ def build(force=False, verbose=False, ptxas_info=False):
     return LIB
 
 
+def pybind_module_path():
+    import sysconfig
+    return os.path.join(HERE, "cuda_ext" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_pybind(force=False, verbose=False):
+    """Compile csrc/cuda_ext.cpp (the pybind11 form of the binding; host C++ only, links against the library
+    next to it).  Returns the module path, or None where pybind11 or the Python headers are absent - the ctypes
+    binding, which needs neither, is the default."""
+    import sysconfig
+    try:
+        import pybind11
+    except ImportError:
+        return None
+    py_inc = sysconfig.get_paths()["include"]
+    if not os.path.exists(os.path.join(py_inc, "Python.h")):
+        return None
+    src = os.path.join(CSRC, "cuda_ext.cpp")
+    out = pybind_module_path()
+    deps = [src, LIB] + [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
+    if not force and os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps):
+        return out
+    cmd = [shutil.which("g++") or "g++", "-O2", "-shared", "-fPIC", "-std=c++17", "-fvisibility=hidden",
+           "-I", py_inc, "-I", pybind11.get_include(), "-I", INCLUDE, src, "-o", out,
+           "-L", HERE, "-lautograd_b200", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed for {src}:\n{r.stdout}\n{r.stderr}")
+    if verbose and r.stderr:
+        sys.stderr.write(r.stderr)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv))
+    print(build_pybind(force="--force" in sys.argv, verbose=True) or "pybind11 module skipped (pybind11 or Python.h absent)")

@@ -1,7 +1,9 @@
 """Build entry point in the style of the reference's own native extension (its setup.py builds
 metal_ext.mm): `python setup.py build_ext --inplace` compiles the CUDA sources for sm_100a into
-autograd_b200/libautograd_b200.so with nvcc.  The library is a plain C-ABI shared object (no Python
-or torch symbols); the package binds it with ctypes, so there is no per-Python-version artefact."""
+autograd_b200/libautograd_b200.so with nvcc, and csrc/cuda_ext.cpp into the pybind11 module
+autograd_b200/cuda_ext*.so with g++.  The library is a plain C-ABI shared object (no Python or torch
+symbols); the package binds it with ctypes by default (no per-Python-version artefact needed) and
+through the pybind11 module with AG_B200_BINDING=pybind11."""
 import importlib.util
 import os
 
@@ -30,7 +32,9 @@ class BuildCuda(Command):
         pass
 
     def run(self):
-        print(_load_builder().build(force=bool(self.force), verbose=True))
+        builder = _load_builder()
+        print(builder.build(force=bool(self.force), verbose=True))
+        print(builder.build_pybind(force=bool(self.force), verbose=True) or "pybind11 module skipped (pybind11 or Python.h absent)")
 
 
 setup(
@@ -38,6 +42,6 @@ setup(
     version="0.1.0",
     description="B200-native CUDA backend for the fused layer kernels of tuzbing/autograd",
     packages=["autograd_b200"],
-    package_data={"autograd_b200": ["libautograd_b200.so", "csrc/*"]},
+    package_data={"autograd_b200": ["libautograd_b200.so", "cuda_ext*.so", "csrc/*"]},
     cmdclass={"build_ext": BuildCuda},
 )

@@ -36,6 +36,32 @@ def test_library_exports_every_declared_symbol():
     assert sorted(_native.SIGNATURES) == names
 
 
+def test_pybind11_module_covers_the_header_and_agrees_with_ctypes():
+    """The pybind11 form of the binding (csrc/cuda_ext.cpp, the shape of the reference's metal_ext
+    module) exposes every declared entry point; its adapter takes the same ctypes-typed arguments as
+    the ctypes library object.  Host-only entry points are called through both."""
+    from autograd_b200 import build as agbuild
+    if agbuild.build_pybind() is None:
+        pytest.skip("pybind11 or the Python headers are not installed")
+    from autograd_b200 import cuda_ext
+    names = _header_symbols()
+    for n in names:
+        assert hasattr(cuda_ext, n), f"{n} declared in the header but not bound by cuda_ext"
+    pyb = _native._PybindLibrary(cuda_ext)
+    cdll = _native.load_library()
+    desc = _native.FlceDesc(16384, 1280, 32768, 4096, _native.AG_CE_3XTF32, 0, 0)
+    assert pyb.ag_flce_scratch_bytes(ctypes.byref(desc)) == cdll.ag_flce_scratch_bytes(ctypes.byref(desc)) > 0
+    assert pyb.ag_scatter_add_scratch_bytes(65536, 1536, 151936) == cdll.ag_scatter_add_scratch_bytes(65536, 1536, 151936)
+    assert pyb.ag_linear_add_scratch_bytes(16384, 1280, 1280, 1) == cdll.ag_linear_add_scratch_bytes(16384, 1280, 1280, 1)
+    # a failing call reports through the same channel: no device here, or an invalid one
+    h = ctypes.c_void_p()
+    rc = pyb.ag_ctx_create(4096, None, ctypes.byref(h))
+    assert rc != 0 and h.value is None
+    assert isinstance(pyb.ag_last_error(None), bytes) and pyb.ag_last_error(None)
+    with pytest.raises(TypeError):
+        pyb.ag_synchronize()
+
+
 def test_context_creation_fails_loudly_without_gpu():
     """No CPU fallback: without a CUDA device the product path raises."""
     import torch
