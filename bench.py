@@ -209,11 +209,11 @@ def run_reference(a):
 class ClockSampler:
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, gpu_index):
         self.proc = None
-        self.gpu_index = gpu_index
+        self.gpu_index = gpu_index      # an index in nvidia-smi's order, or a "GPU-<uuid>" string
         self.path = f"/tmp/ag_clocks_{os.getpid()}.csv"
 
     def start(self):
@@ -234,7 +234,7 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.out.close()
-        sm, mx, reasons = [], [], set()
+        sm, mx, util, reasons = [], [], [], set()
         try:
             with open(self.path) as f:
                 for ln in f:
@@ -245,6 +245,10 @@ class ClockSampler:
                         sm.append(float(p[1])); mx.append(float(p[2]))
                     except ValueError:
                         continue
+                    try:
+                        util.append(float(p[9]))
+                    except (ValueError, IndexError):
+                        util.append(-1.0)
                     for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
                                        p[5:9]):
                         if v.lower().startswith("active"):
@@ -252,10 +256,13 @@ class ClockSampler:
             os.remove(self.path)
         except Exception:
             pass
-        # the busiest half of the samples is "under load"
-        load = sorted(sm)[len(sm) // 2:] if sm else []
+        # "under load" = the samples at which the GPU reported at least half utilisation (the sampler also runs
+        # through set-up and through the CPU baseline); without such a reading, all samples
+        load = [c for c, u in zip(sm, util) if u >= 50.0]
+        if len(load) < 3:
+            load = sm
         return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_under_load": len(load)}
 
 
 # --------------------------------------------------------------------------------------
@@ -330,7 +337,17 @@ def run_b200(a):
     # The clock sampler starts before the warm-up steps: nvidia-smi takes the driver's lock while it
     # initialises, which would otherwise stall this process's launches inside the timed region.  The
     # warm-up steps run the same kernels, so its samples are under load as well.
-    sampler = ClockSampler(local)
+    gpu_id = local
+    try:   # nvidia-smi's order need not be CUDA's: name the device by its UUID where torch exposes it
+        u = str(torch.cuda.get_device_properties(local).uuid)
+        u = u if u.startswith("GPU-") else "GPU-" + u
+        ok = subprocess.run(["nvidia-smi", "-i", u, "--query-gpu=index", "--format=csv,noheader"],
+                            capture_output=True, text=True, timeout=20)
+        if ok.returncode == 0 and ok.stdout.strip():
+            gpu_id = u
+    except Exception:
+        pass
+    sampler = ClockSampler(gpu_id)
     sampler.start()
     load(0)
     for i in range(a.warmup):
