@@ -480,3 +480,33 @@ def test_host_cost_of_the_backend_layer_per_step():
     print(f"host time of the backend layer: {per_step_ms:.2f} ms per step for {launches:.0f} C-ABI calls")
     assert launches >= 2 * (1 + 41 + 20 + 1)
     assert per_step_ms < 20.0, per_step_ms
+
+
+def test_bench_clock_summary_uses_the_samples_under_load():
+    """bench.py's clock record: the median SM clock is taken over the nvidia-smi samples at which the GPU was
+    busy (at least half utilisation), not over idle readings before and after the timed region; throttle reasons
+    are collected over all samples."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_bench_for_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class Done:
+        def terminate(self): pass
+        def wait(self, timeout=None): return 0
+        def kill(self): pass
+
+    na = "Not Active"
+    rows = [f"0, 1965, 1965, 180.0, 0x0, {na}, {na}, {na}, {na}, 0"] * 6            # idle before the step
+    rows += [f"0, {mhz}, 1965, 990.0, 0x4, {na}, {na}, {na}, Active, 100" for mhz in (1545, 1560, 1590, 1605, 1620)]
+    rows += [f"0, 1965, 1965, 200.0, 0x0, {na}, {na}, {na}, {na}, 3"] * 4            # idle during the CPU baseline
+    s = bench.ClockSampler(0)
+    with open(s.path, "w") as f:
+        f.write("\n".join(rows) + "\n")
+    s.out = open(s.path)          # stop() closes it
+    s.proc = Done()
+    got = s.stop()
+    assert got["sm_mhz"] == 1590 and got["sm_max_mhz"] == 1965
+    assert got["samples"] == 15 and got["samples_under_load"] == 5
+    assert got["reasons"] == ["sw_power_cap"]
+    assert not os.path.exists(s.path)
