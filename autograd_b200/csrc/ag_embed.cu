@@ -615,7 +615,9 @@ extern "C" int ag_gather_forward(ag_ctx* ctx, const int32_t* ids, const float* t
   AG_REQUIRE(ctx, n_ids > 0 && C > 0 && V > 0, "ag_gather_forward: bad shape n=%lld C=%d V=%d", (long long)n_ids, C, V);
   if (C % 4 == 0 && ag_aligned16(table) && ag_aligned16(out)) {
     int64_t want = (n_ids * 32 + GATHER_THREADS - 1) / GATHER_THREADS;
-    int64_t cap = (int64_t)ctx->sm_count * 8;
+    // one row per warp up to 32 CTAs per SM: many short CTAs keep the load/store queues fuller than a resident
+    // grid whose warps loop (65536 x 1536, Zipf ids: 80.0 us against 87.4 us with 8 CTAs per SM; 16: 82.2, 64: 79.9)
+    int64_t cap = (int64_t)ctx->sm_count * 32;
     gather_forward_kernel<<<(int)(want < cap ? want : cap), GATHER_THREADS, 0, ctx->stream>>>(ids, table, out, n_ids,
                                                                                                C, V, ctx->d_status);
     AG_LAUNCHED(ctx, "gather_forward_kernel");
