@@ -56,7 +56,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-config-kernels", action="store_true",
                     help="step workload: skip the per-kernel timings at the shapes of configs 1-4 (`configs` key)")
-    ap.add_argument("--only", default="", help="--workload kernels: comma-separated sections (cfg1,gelu,cfg3,cfg4,cfg2,next)")
+    ap.add_argument("--only", default="", help="--workload kernels: comma-separated sections (cfg1,gelu,cfg3,cfg4,cfg2,next,rmsce)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=0,
                     help="token rows of the CPU sample (0: sized so that the CPU run stays within a few minutes)")
     ap.add_argument("--cpu-sample-layers", type=int, default=2, help="numpy-port fallback only")
@@ -925,8 +925,55 @@ def run_kernels(a, env=None, dev_index=0, collect=None, steps=None, warmup=None,
              alg_bytes=nid * C * f4 + 2 * uniq * C * 2, extra={"unique_rows": uniq})
         free_all()
 
+    def sec_rmsce():
+        # ---- FusedRMSNormLinearCrossEntropy with row_scale at the Qwen head shape (hidden 1536, vocabulary
+        # 151936, 8192 token rows): the launch sequence of the backend's callables - RMSNorm, the CE head on its
+        # output with per-row weights; backward: RMSNorm again, dz zero-fill, CE backward into dz and dW,
+        # RMSNorm backward with the residual-gradient add and dgamma
+        N, C, V = 8192, 1536, 151936
+        rng = np.random.default_rng(1241)
+        tg_ = rng.integers(0, V, size=N).astype(np.int32)
+        tg_[rng.random(N) < 0.05] = -1
+        tg_[rng.random(N) < 0.01] = V          # out of range: ignored like -1
+        X = dev(N * C, std=1.0); W = dev(V * C, std=0.02); gam = dev(C, std=0.02)
+        ctx.fill_f32(gam, 1.0, C)
+        rs = dev(N, std=0.0); ctx.fill_f32(rs, 1.0 / N, N)
+        dX, dW, dgam = dev(N * C), dev(V * C), dev(C)
+        z, dz = dev(N * C), dev(N * C)
+        tg = dev(N, np.int32, ints=tg_)
+        loss, dloss, lse = dev(1), dev(1), dev(N)
+        ctx.fill_f32(dloss, 1.0, 1)
+        pb = ctx.norm_partials_bytes(C); part = alloc.alloc((pb,), np.uint8); bufs.append(part)
+        cf = cb = None
+        if cpu_ref is not None:     # a 512-row sample of the 8192 rows: the cost is linear in the rows
+            tf, tb = cpu_ref[1].OpGraph(cpu_ref[0], cpu_ref[1].rmsnorm_fused_linear_ce(1, 512, C, V)).time_pair(0, 1)
+            what = f"FusedRMSNormLinearCrossEntropyOp graph with row_scale, 512 of {N} rows, C {C}, V {V}, Runtime(device='cpu')"
+            cf, cb = cpu_entry(tf, 512, what + " forward()"), cpu_entry(tb, 512, what + " backward_graph()")
+        for pname, prec in (("3xtf32", ag.AG_CE_3XTF32), ("bf16x3", ag.AG_CE_BF16X3)):
+            desc = ctx.flce_desc(N, C, V, vocab_chunk=4096, precision=prec)
+            sbytes = ctx.flce_scratch_bytes(desc); scr = alloc.alloc((sbytes,), np.uint8); bufs.append(scr)
+
+            def fwd(i):
+                ctx.rmsnorm_forward(X, gam, z, 0, N, C, 1e-6)
+                ctx.flce_forward(desc, z, W, tg, rs, loss, lse, scr.ptr.address, sbytes)
+
+            def bwd(i):
+                ctx.rmsnorm_forward(X, gam, z, 0, N, C, 1e-6)
+                ctx.fill_f32(dz, 0.0, N * C)
+                ctx.flce_backward(desc, z, W, tg, rs, dloss, lse, dz, dW, scr.ptr.address, sbytes)
+                ctx.rmsnorm_backward(dz, X, gam, dX, dX, dgam, part.ptr.address, pb, N, C, 1e-6)
+
+            ms_f = time_it(fwd, 1)
+            ms_b = time_it(bwd, 1)
+            fl = 2.0 * N * C * V
+            emit("rmsce", f"rmsnorm + fused_linear_ce(row_scale) forward N{N} C{C} V{V}", ms_f, N, useful_flops=fl, dtype=pname,
+                 extra=cf)
+            emit("rmsce", f"rmsnorm + fused_linear_ce(row_scale) backward N{N} C{C} V{V}", ms_b, N, useful_flops=2 * fl,
+                 dtype=pname, extra={"executed_flops": 3 * fl, "scratch_bytes": sbytes, **(cb or {})})
+        free_all()
+
     sections = {"cfg1": sec_cfg1, "gelu": sec_gelu, "cfg3": sec_cfg3, "cfg4": sec_cfg4, "cfg2": sec_cfg2,
-                "next": sec_next}
+                "next": sec_next, "rmsce": sec_rmsce}
     wanted = [s for s in (a.only.split(",") if a.only else sections) if s]
     for name in wanted:
         if name not in sections:

@@ -133,6 +133,23 @@ def fused_linear_ce(B, T, C, V, ignore_frac=0.05, seed=1235):
     return build
 
 
+def rmsnorm_fused_linear_ce(B, T, C, V, ignore_frac=0.05, eps=1e-6, seed=1241):
+    """FusedRMSNormLinearCrossEntropyOp with per-row weights (op.py:306-327, backend.py:716-886)."""
+    rng = np.random.default_rng(seed)
+    X = rng.standard_normal((B, T, C), dtype=F32)
+    W = (0.02 * rng.standard_normal((V, C), dtype=F32)).astype(F32)
+    g = (1 + 0.02 * rng.standard_normal(C)).astype(F32)
+    Y = rng.integers(0, V, size=(B, T)).astype(np.int32)
+    Y[rng.random((B, T)) < ignore_frac] = -1
+    rs = np.full((B, T), 1.0 / (B * T), dtype=F32)
+
+    def build(ref):
+        tx, tw, tg = _leaf(ref, X), _leaf(ref, W), _leaf(ref, g)
+        ty, trs = _leaf(ref, Y, requires_grad=False), _leaf(ref, rs, requires_grad=False)
+        return tx.fused_rmsnorm_linear_cross_entropy(tw, tg, ty, row_scale=trs, eps=eps), {"x": tx, "w": tw, "gamma": tg}
+    return build
+
+
 def rmsnorm_mlp(B, T, C, I, eps=1e-6, seed=1236):
     """FusedRMSNormMLPOp: the carrier of the RMSNorm and SwiGLU stages (backend.py:1074-1251)."""
     rng = np.random.default_rng(seed)
